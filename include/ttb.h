@@ -1,0 +1,152 @@
+/*
+ * libttb C ABI: the block-float weight path of TT-NN on NVIDIA B200 (sm_100a).
+ *
+ * Everything here is extern "C", takes plain pointers and sizes, and returns an int32 status:
+ * 0 on success, a negative TTB_E_* code on failure. No call throws or aborts; a human-readable
+ * description of the last failure on the calling thread is available from ttb_last_error().
+ * Device pointers are caller-owned; every compute call is asynchronous on the given CUDA stream
+ * (a cudaStream_t passed as void*; NULL = the default stream) unless stated otherwise.
+ *
+ * Data layouts (identical to the reference's buffers, so bytes can be exchanged with it):
+ *   - "tiled" = TILE_LAYOUT: tiles of 32x32 elements ordered row-major over (outer*H/32, W/32);
+ *     each tile is four 16x16 row-major faces in the order top-left, top-right, bottom-left,
+ *     bottom-right  (tt_metal/common/test_tiles.hpp:24-65, 124-158).
+ *   - bfloat8_b tile = 1088 bytes: 64 shared-exponent bytes (byte 16*face + row) followed by 1024
+ *     sign+7-bit-mantissa bytes in face order; bfloat4_b tile = 576 bytes: 64 exponent bytes followed
+ *     by 512 bytes of sign+3-bit-mantissa nibbles, even element in the low nibble
+ *     (tt_metal/common/blockfloat_common.hpp:174-258, tt_backend_api_types.hpp:109-132).
+ *
+ * The reference reaches this functionality through C++ templates and two pybind modules rather
+ * than a C plugin interface; each entry point cites the reference routine it stands in for.
+ */
+#ifndef TTB_H_
+#define TTB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+#define TTB_OK 0
+#define TTB_E_INVALID (-1)   /* bad argument: shape, dtype, alignment, null pointer            */
+#define TTB_E_CUDA (-2)      /* a CUDA runtime call failed; ttb_last_error() holds its message */
+#define TTB_E_UNSUPPORTED (-3)
+#define TTB_E_WORKSPACE (-4) /* workspace missing or too small                                  */
+#define TTB_E_TIMEOUT (-5)   /* a bounded device-side wait ran out (reported by ttb_check_status) */
+
+/* ---- element types: numeric values follow tt::tt_metal::DataType
+ *      (tt_eager/tensor/types.hpp:24-34) ---------------------------------------------------- */
+#define TTB_BFLOAT16 0
+#define TTB_FLOAT32 1
+#define TTB_UINT32 2
+#define TTB_BFLOAT8_B 3
+#define TTB_BFLOAT4_B 4
+#define TTB_UINT16 5
+
+/* ---- fused activation after bias (ttnn.linear's `activation`, ttnn/ttnn/operations/matmul.py:59-63) */
+#define TTB_ACT_NONE 0
+#define TTB_ACT_RELU 1
+#define TTB_ACT_GELU 2 /* erf form, the definition of the reference's torch golden (matmul.py:419-438) */
+#define TTB_ACT_SILU 3
+
+/* ---- flags for ttb_matmul ------------------------------------------------------------------ */
+#define TTB_MM_A_ROW_MAJOR 1   /* activations are row-major [batch*M, K] instead of tiled        */
+#define TTB_MM_OUT_ROW_MAJOR 2 /* write the result row-major (the reference's untilize_out)      */
+#define TTB_MM_FORCE_GENERIC 4 /* use the shape-generic CUDA-core kernel (cross-check path)      */
+
+const char *ttb_last_error(void);
+int32_t ttb_version(void);
+
+/* ---- device memory and copies (thin CUDA runtime wrappers so host code above this ABI needs no
+ *      CUDA headers). Stand in for tt_metal Buffer allocation and EnqueueWriteBuffer /
+ *      EnqueueReadBuffer (tt_eager/tensor/tensor_impl.hpp:246-269, 341-358). ------------------ */
+int32_t ttb_device_count(int32_t *count);
+int32_t ttb_set_device(int32_t device);
+int32_t ttb_get_device(int32_t *device);
+int32_t ttb_malloc(void **dev_ptr, size_t bytes);
+int32_t ttb_free(void *dev_ptr);
+int32_t ttb_host_alloc(void **host_ptr, size_t bytes); /* pinned host memory */
+int32_t ttb_host_free(void *host_ptr);
+int32_t ttb_memcpy_h2d(void *dst_dev, const void *src_host, size_t bytes, void *stream);
+int32_t ttb_memcpy_d2h(void *dst_host, const void *src_dev, size_t bytes, void *stream);
+int32_t ttb_memcpy_d2d(void *dst_dev, const void *src_dev, size_t bytes, void *stream);
+int32_t ttb_memset(void *dst_dev, int32_t value, size_t bytes, void *stream);
+int32_t ttb_stream_synchronize(void *stream);
+int32_t ttb_device_synchronize(void);
+
+/* Bytes of a buffer holding outer*Hp*Wp elements of `dtype` (Hp, Wp multiples of 32 for the
+ * block-float types). Mirrors compute_buffer_size (tt_eager/tensor/tensor_utils.hpp:34-47). */
+int64_t ttb_buffer_bytes(int32_t dtype, int64_t outer, int64_t Hp, int64_t Wp);
+
+/* ---- layout conversion ----------------------------------------------------------------------
+ * Row-major [outer, H, W] -> tiled [outer, Hp, Wp] with zero fill of the padding, Hp/Wp = H/W
+ * rounded up to 32. elem_size is 2 or 4 bytes. Replaces convert_layout(LIN_ROW_MAJOR ->
+ * TILED32_4FACES) (tt_metal/common/test_tiles.hpp:178-213) and to_layout<T>
+ * (tt_eager/tensor/tensor_impl.hpp:158-171, 428-499) plus pad (tensor_impl.hpp:508-677). */
+int32_t ttb_tilize(const void *src_dev, void *dst_dev, int32_t elem_size, int64_t outer, int64_t H, int64_t W,
+                   void *stream);
+/* Tiled [outer, Hp, Wp] -> row-major [outer, H, W] (the padding is dropped). */
+int32_t ttb_untilize(const void *src_dev, void *dst_dev, int32_t elem_size, int64_t outer, int64_t H, int64_t W,
+                     void *stream);
+
+/* ---- block-float pack / unpack --------------------------------------------------------------
+ * ttb_pack_bfp: src (TTB_FLOAT32 or TTB_BFLOAT16) -> packed tiles of `fmt` (TTB_BFLOAT8_B or
+ * TTB_BFLOAT4_B). With src_row_major != 0 the source is row-major [outer, H, W] and tilize, zero
+ * padding to 32 and packing happen in one pass; otherwise the source already is tiled
+ * [outer, H, W] (H, W multiples of 32) and is consumed sequentially. Bit-exact with
+ * pack_fp32_vec_as_bfp8_tiles / pack_fp32_vec_as_bfp4_tiles (tt_metal/common/bfloat8.hpp:102-173,
+ * bfloat4.hpp:23-25, blockfloat_common.hpp:19-258).
+ * With two_pass != 0 every group of 16 values goes through pack -> unpack -> pack, which is what
+ * ttnn.from_torch does on the host (pytensor.cpp:145-160 then tensor_impl.cpp:179-197); the bytes
+ * differ from the single pass only for non-finite or denormal inputs. */
+int32_t ttb_pack_bfp(const void *src_dev, int32_t src_dtype, void *dst_dev, int32_t fmt, int64_t outer, int64_t H,
+                     int64_t W, int32_t src_row_major, int32_t two_pass, void *stream);
+
+/* ttb_unpack_bfp: packed tiles of `fmt` holding a tiled [outer, Hp, Wp] tensor -> dst
+ * (TTB_FLOAT32 or TTB_BFLOAT16; both exact, the unpacked values have at most 8 significant bits),
+ * row-major [outer, H, W] without the padding when dst_row_major != 0, else tiled (H, W multiples
+ * of 32). Bit-exact with unpack_bfp8_tiles_into_float_vec / unpack_bfp4_tiles_into_float_vec
+ * (bfloat8.hpp:175-265, bfloat4.hpp:33-164), including the unclamped exponent arithmetic.
+ * With two_pass != 0 every group of 16 values goes through unpack -> pack -> unpack as
+ * ttnn.to_torch does (tensor_impl.cpp:179-197, pytensor.cpp:382-393). */
+int32_t ttb_unpack_bfp(const void *src_dev, int32_t fmt, void *dst_dev, int32_t dst_dtype, int64_t outer, int64_t H,
+                       int64_t W, int32_t dst_row_major, int32_t two_pass, void *stream);
+
+/* ---- matmul / linear --------------------------------------------------------------------------
+ * out[b, M, N] = act( a[b, M, K] x w[K, N] + bias[N] ), fp32 accumulation.
+ *   a:    TTB_BFLOAT16, tiled (or row-major with TTB_MM_A_ROW_MAJOR); M, K multiples of 32.
+ *   w:    TTB_BFLOAT8_B, TTB_BFLOAT4_B or TTB_BFLOAT16, tiled [K, N], shared by every batch entry.
+ *   bias: NULL, or TTB_BFLOAT16 tiled [32, N] whose first row is used (the reference's
+ *         [1,1,32,N] bias tile row, tt_eager/tt_dnn/op_library/bmm/bmm_op.cpp:859-863).
+ *   out:  TTB_BFLOAT16 or TTB_FLOAT32, tiled (or row-major with TTB_MM_OUT_ROW_MAJOR).
+ * Block-float weights are expanded to bf16 in shared memory (exact) and multiplied on the tcgen05
+ * tensor cores; shapes outside the tensor-core kernels' tiling use a CUDA-core kernel with the same
+ * arithmetic. Stands in for tt::operations::primary::matmul and the multi-core-reuse program
+ * factories (bmm_op.hpp:284-346, bmm_op.cpp:828-1303, and the multi_core_reuse program factories
+ * beside them). `workspace` is device scratch of at least ttb_matmul_workspace_bytes() bytes (may be NULL when
+ * that is 0); it is only touched between launch and completion of this call on `stream`. */
+int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags);
+int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
+                   void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                   int32_t activation, int32_t flags, void *workspace_dev, int64_t workspace_bytes, void *stream);
+
+/* Reads (and clears) the device-side status word that kernels with bounded waits set when a wait
+ * ran out. Synchronises `stream`. Returns TTB_OK or TTB_E_TIMEOUT. */
+int32_t ttb_check_status(void *stream);
+
+/* ---- all-gather helper ------------------------------------------------------------------------
+ * After a rank-major gather of G slices [rows, cols_per_rank] (what an NCCL all-gather leaves),
+ * interleave them into row-major [rows, G*cols_per_rank]. Not needed for tiled tensors whose row
+ * count is one tile (32): there the rank-major gather already is the tiled [32, G*cols] tensor.
+ * Stands in for the concat-along-dim semantics of AllGather
+ * (tt_eager/tt_dnn/op_library/all_gather/all_gather_op.cpp:18-104). */
+int32_t ttb_gather_interleave(const void *src_dev, void *dst_dev, int32_t elem_size, int32_t ranks, int64_t rows,
+                              int64_t cols_per_rank, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TTB_H_ */

@@ -1,0 +1,151 @@
+"""GPU parity of ttb_matmul against an fp32 torch matmul of the oracle-unpacked weights.
+
+Tolerances (from the task statement, written out): PCC >= 0.9999 with the reference's comp_pcc definition, and
+max|y - y_ref| / max|y_ref| <= 1e-2."""
+import numpy as np
+import pytest
+
+import cabi
+import oracle
+import vectors
+
+pytestmark = pytest.mark.gpu
+PCC_MIN = 0.9999
+MAX_REL = 1e-2
+
+
+def make_case(ttb, orc, seed, M, K, N, w_dtype, w_std=0.02):
+    import torch
+    x = vectors.randn(seed, (M, K), 1.0).bfloat16()
+    w = vectors.randn(seed + 1000, (K, N), w_std)
+    if w_dtype == cabi.BFLOAT16:
+        wq = w.bfloat16()
+        w_dev = ttb.tilize(wq.cuda(), 1, K, N)
+        w_ref = wq.float()
+    else:
+        ofmt = 0 if w_dtype == cabi.BFLOAT8_B else 1
+        packed = orc.from_torch(w.numpy(), ofmt, 1, K, N)          # weights packed by the ORACLE, not the GPU
+        w_dev = torch.from_numpy(packed).cuda()
+        w_ref = torch.from_numpy(orc.to_torch(packed, ofmt, 1, K, N).reshape(K, N).copy())
+    return x, w_dev, w_ref
+
+
+def check(y, y_ref):
+    y, y_ref = y.float().cpu().numpy(), y_ref.float().cpu().numpy()
+    pcc = oracle.comp_pcc(y_ref, y)
+    rel = np.abs(y - y_ref).max() / np.abs(y_ref).max()
+    assert pcc >= PCC_MIN, f"PCC {pcc}"
+    assert rel <= MAX_REL, f"max relative error {rel}"
+
+
+def act_ref(y, act):
+    import torch
+    if act == cabi.ACT_RELU:
+        return torch.relu(y)
+    if act == cabi.ACT_GELU:
+        return torch.nn.functional.gelu(y)
+    if act == cabi.ACT_SILU:
+        return torch.nn.functional.silu(y)
+    return y
+
+
+SHAPES_SMALL = [(32, 64, 128), (32, 128, 128), (32, 64, 256), (32, 512, 384), (64, 256, 256), (128, 192, 128), (96, 128, 128),
+                (32, 32, 32), (64, 96, 160)]
+
+
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B, cabi.BFLOAT16])
+@pytest.mark.parametrize("M,K,N", SHAPES_SMALL)
+@pytest.mark.parametrize("generic", [False, True])
+def test_matmul_small_shapes(ttb, orc, w_dtype, M, K, N, generic):
+    import torch
+    x, w_dev, w_ref = make_case(ttb, orc, 5, M, K, N, w_dtype)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    flags = cabi.MM_FORCE_GENERIC if generic else 0
+    y = ttb.untilize(ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, flags=flags), 1, M, N).reshape(M, N)
+    y_ref = x.float() @ w_ref
+    check(y, y_ref)
+
+
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
+def test_tensor_core_kernel_agrees_with_generic_kernel(ttb, orc, w_dtype):
+    """Same operands, fp32 accumulation in both: results may differ only by summation order."""
+    import torch
+    M, K, N = 32, 1024, 512
+    x, w_dev, _ = make_case(ttb, orc, 9, M, K, N, w_dtype)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y1 = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, out_fp32=True)
+    y2 = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, out_fp32=True, flags=cabi.MM_FORCE_GENERIC)
+    assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("act", [cabi.ACT_NONE, cabi.ACT_RELU, cabi.ACT_GELU, cabi.ACT_SILU])
+@pytest.mark.parametrize("generic", [False, True])
+def test_linear_bias_activation_and_layout_flags(ttb, orc, act, generic):
+    import torch
+    M, K, N = 32, 256, 384
+    x, w_dev, w_ref = make_case(ttb, orc, 21, M, K, N, cabi.BFLOAT8_B)
+    bias = vectors.randn(77, (N,), 0.5).bfloat16()
+    bias_tile = torch.zeros(32, N, dtype=torch.bfloat16)
+    bias_tile[0] = bias
+    b_dev = ttb.tilize(bias_tile.cuda(), 1, 32, N)
+    y_ref = act_ref(x.float() @ w_ref + bias.float(), act)
+    base = cabi.MM_FORCE_GENERIC if generic else 0
+    # tiled in, tiled out
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y = ttb.untilize(ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, bias=b_dev, act=act, flags=base), 1, M, N).reshape(M, N)
+    check(y, y_ref)
+    # row-major in, row-major out, fp32 out
+    y2 = ttb.matmul(x.cuda().contiguous(), w_dev, cabi.BFLOAT8_B, 1, M, K, N, bias=b_dev, act=act,
+                    flags=base | cabi.MM_A_ROW_MAJOR | cabi.MM_OUT_ROW_MAJOR, out_fp32=True).reshape(M, N)
+    check(y2, y_ref)
+
+
+@pytest.mark.parametrize("M,K,N,w_dtype,seed", [
+    (32, 4544, 18176, cabi.BFLOAT8_B, 1),      # Falcon-7B h_to_4h decode
+    (32, 4096, 4096, cabi.BFLOAT8_B, 2),       # Mistral Wq / Wo (K split over blocks)
+    (32, 4096, 1024, cabi.BFLOAT8_B, 2),       # Mistral Wk / Wv
+    (32, 4096, 14336, cabi.BFLOAT4_B, 2),      # Mistral w1 / w3
+    (32, 14336, 4096, cabi.BFLOAT8_B, 2),      # Mistral w2
+    (32, 8192, 3584, cabi.BFLOAT8_B, 4),       # Llama-70B w1 shard at 8 GPUs
+])
+def test_decode_shapes_of_the_benchmark_configurations(ttb, orc, M, K, N, w_dtype, seed):
+    import torch
+    x, w_dev, w_ref = make_case(ttb, orc, seed, M, K, N, w_dtype)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y = ttb.untilize(ttb.matmul(a, w_dev, w_dtype, 1, M, K, N), 1, M, N).reshape(M, N)
+    y_ref = (x.float().cuda() @ w_ref.cuda())
+    check(y, y_ref)
+
+
+def test_batched_activations_share_the_weight(ttb, orc):
+    import torch
+    B, M, K, N = 2, 32, 128, 256
+    x = vectors.randn(3, (B, M, K), 1.0).bfloat16()
+    _, w_dev, w_ref = make_case(ttb, orc, 3, M, K, N, cabi.BFLOAT8_B)
+    a = ttb.tilize(x.cuda(), B, M, K)
+    y = ttb.untilize(ttb.matmul(a, w_dev, cabi.BFLOAT8_B, B, M, K, N), B, M, N).reshape(B, M, N)
+    check(y, x.float() @ w_ref)
+
+
+def test_repeated_launches_reuse_scratch(ttb, orc):
+    """Split-K scratch counters must return to zero after each launch."""
+    import torch
+    M, K, N = 32, 4096, 1024
+    x, w_dev, w_ref = make_case(ttb, orc, 31, M, K, N, cabi.BFLOAT8_B)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    nbytes = ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N, 0)
+    assert nbytes > 0
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    outs = []
+    for _ in range(3):
+        out = torch.empty(M * N, dtype=torch.bfloat16, device="cuda")
+        ttb.check(ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(),
+                                      cabi.BFLOAT16, 1, M, K, N, 0, 0, ws.data_ptr(), nbytes, None))
+        outs.append(out)
+    ttb.check(ttb.check_status(None))
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    check(ttb.untilize(outs[0], 1, M, N).reshape(M, N), x.float() @ w_ref)
+    # too small a workspace is refused before anything is launched
+    rc = ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, outs[0].data_ptr(),
+                             cabi.BFLOAT16, 1, M, K, N, 0, 0, ws.data_ptr(), 16, None)
+    assert rc == -4

@@ -1,0 +1,473 @@
+// Weight-streaming matmul for small row counts (decode): out[rows, N] = act(a[rows, K] x W[K, N] + bias)
+// with W in packed bfloat8_b / bfloat4_b tiles, rows in {32, 64, 128} per block.
+//
+// The kernel is bound by reading W once from HBM (1.0625 or 0.5625 bytes per weight), so everything is
+// organised around keeping many weight bytes in flight per SM:
+//   * "swap-AB": the tensor-core M dimension (128) runs over weight columns, the MMA N dimension over the
+//     activation rows, so a 32-row batch fills the MMA instead of wasting three quarters of it;
+//   * a producer thread streams packed tiles (whole 4-tile runs of 4352 / 2304 contiguous bytes) into an
+//     8-deep shared-memory ring with cp.async.bulk, each stage completing on an mbarrier;
+//   * eight warps expand the packed codes to bf16 (exact: sign + 7-bit mantissa under an 8-bit exponent fits
+//     bf16) straight into the tensor cores' canonical no-swizzle operand layout, and stage the activation
+//     K-block next to it;
+//   * one thread issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32 in TMEM); tcgen05.commit hands operand
+//     stages back to the expanding warps;
+//   * the expanding warps then read the accumulator with tcgen05.ld and finish: either bias + activation +
+//     store, or - when K is split over several blocks so that every SM streams - an fp32 partial into scratch,
+//     where the last block to arrive for an output tile adds the partials in a fixed order and finishes.
+// Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
+#include "epilogue.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ttb {
+
+__device__ int g_status_word = 0;
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BN = 128;           // weight columns per block (UMMA M)
+constexpr int BK = 64;            // K per pipeline stage (two tiles)
+constexpr int kExpandWarps = 8;
+constexpr int kExpandThreads = 32 * kExpandWarps;
+constexpr int kThreadsDecode = 64 + kExpandThreads;  // warp 0 producer, warp 1 MMA, warps 2..9 expand + epilogue
+constexpr int kPkStages = 8;
+constexpr int kAbStages = 4;
+constexpr int kAStageBytes = BN * BK * 2;       // 16 KiB
+constexpr uint32_t kA_LBO = 2048, kA_SBO = 128;  // A (weights, N-contiguous): K-groups 2 KiB apart, N-groups adjacent
+constexpr uint32_t kB_LBO = 128, kB_SBO = 1024;  // B (activations, K-contiguous): K-groups adjacent, row-groups 1 KiB apart
+
+struct DecodeArgs {
+    const uint8_t *w;
+    const uint16_t *a;
+    const uint16_t *bias;
+    void *out;
+    float *partial;
+    int *counters;
+    int64_t K, N;
+    int Kt, Nt;
+    int nkb, kb_per_split, splits;
+    int act, out_dtype, a_row_major, out_row_major;
+};
+
+template <int FMT>
+struct Pk {
+    static constexpr int kTileBytes = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
+    static constexpr int kStageBytes = 8 * kTileBytes;
+};
+
+template <int FMT, int NB>
+struct SmemLayout {
+    static constexpr int kBStageBytes = NB * BK * 2;
+    static constexpr int pk = 0;
+    static constexpr int a = pk + kPkStages * Pk<FMT>::kStageBytes;
+    static constexpr int b = a + kAbStages * kAStageBytes;
+    static constexpr int bars = b + kAbStages * kBStageBytes;
+    // barriers: full_pk[kPkStages], empty_pk[kPkStages], full_ab[kAbStages], empty_ab[kAbStages], accum
+    static constexpr int nbars = 2 * kPkStages + 2 * kAbStages + 1;
+    static constexpr int misc = bars + 8 * nbars;  // tmem base (4), abort flag (4), last-block flag (4)
+    static constexpr int total = misc + 16;
+};
+
+// Expands one face row (16 codes sharing exponent E) into 16 bf16 values, returned as eight packed pairs.
+// value = +-m * 2^(E - 133) (bfloat8_b) or +-m * 2^(E - 129) (bfloat4_b). The integer mantissa is turned into a
+// bf16 by OR-ing it under the exponent of 128 (bits 0x4300 | m == 128 + m), then one fused multiply-add with
+// the power-of-two scale removes the 128 and applies the exponent; the sign bit is OR-ed on last.
+// Rows with E below the scale's exponent range (values under 2^-120) are flushed to zero.
+template <int FMT>
+__device__ __forceinline__ void expand_row(const uint32_t *codes, uint32_t E, uint32_t (&out)[8]) {
+    constexpr int kBiasExp = FMT == TTB_BFLOAT8_B ? 6 : 2;
+    E = min(E, 247u + kBiasExp);  // keeps 128 * scale finite; only rows holding Inf/NaN-class values are affected
+    const uint32_t sbits = E > (uint32_t)kBiasExp ? ((E - kBiasExp) << 7) : 0u;  // bf16 bits of the scale
+    const uint32_t scale2 = sbits | (sbits << 16);
+    // -128 * scale: exponent + 7, sign set.
+    const uint32_t nb = sbits ? ((sbits + (7u << 7)) | 0x8000u) : 0u;
+    const uint32_t nbias2 = nb | (nb << 16);
+    const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&scale2);
+    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162 *>(&nbias2);
+    if (FMT == TTB_BFLOAT8_B) {
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            const uint32_t w = codes[wi];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t x = __byte_perm(w, 0u, h ? 0x4342u : 0x4140u);  // [c_even, 0, c_odd, 0]
+                uint32_t mant = (x & 0x007f007fu) | 0x43004300u;
+                __nv_bfloat162 v = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&mant), s2, b2);
+                out[2 * wi + h] = *reinterpret_cast<uint32_t *>(&v) | ((x << 8) & 0x80008000u);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int wi = 0; wi < 2; ++wi) {
+            const uint32_t w = codes[wi];
+            const uint32_t ev = w & 0x0f0f0f0fu, od = (w >> 4) & 0x0f0f0f0fu;  // even / odd elements, one per byte
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const uint32_t x = __byte_perm(ev, od, (uint32_t)(p | ((4 + p) << 8)));  // [ev_p, ev_0, od_p, ev_0]
+                uint32_t mant = (x & 0x00070007u) | 0x43004300u;
+                __nv_bfloat162 v = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&mant), s2, b2);
+                out[4 * wi + p] = *reinterpret_cast<uint32_t *>(&v) | ((x << 12) & 0x80008000u);
+            }
+        }
+    }
+}
+
+// Global element offset of the 8-element activation chunk (row r, columns k..k+7).
+__device__ __forceinline__ int64_t act_chunk_offset(const DecodeArgs &p, int64_t r, int64_t k) {
+    if (p.a_row_major) return r * p.K + k;
+    return ((r >> 5) * p.Kt + (k >> 5)) * 1024 + 256 * (2 * (int)((r & 31) >> 4) + (int)((k & 31) >> 4)) + 16 * (int)(r & 15) +
+           (int)(k & 15);
+}
+
+template <int NB>
+__device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
+    const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int64_t r = row0 + col0 + j;
+        const float y = apply_activation(v[j] + bias, p.act);
+        const int64_t off = p.out_row_major ? r * p.N + n : tiled_offset(r, n, p.Nt);
+        if (p.out_dtype == TTB_FLOAT32)
+            reinterpret_cast<float *>(p.out)[off] = y;
+        else
+            reinterpret_cast<uint16_t *>(p.out)[off] = f32_to_bf16_bits(y);
+    }
+}
+
+template <int FMT, int NB>
+__global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const DecodeArgs p) {
+    using L = SmemLayout<FMT, NB>;
+    constexpr int TB = Pk<FMT>::kTileBytes;
+    constexpr int kTmemCols = NB < 32 ? 32 : NB;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + L::bars;
+    auto full_pk = [&](int s) { return bar0 + 8u * s; };
+    auto empty_pk = [&](int s) { return bar0 + 8u * (kPkStages + s); };
+    auto full_ab = [&](int s) { return bar0 + 8u * (2 * kPkStages + s); };
+    auto empty_ab = [&](int s) { return bar0 + 8u * (2 * kPkStages + kAbStages + s); };
+    const uint32_t accum_bar = bar0 + 8u * (2 * kPkStages + 2 * kAbStages);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(smem + L::misc + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntile = blockIdx.x, split = blockIdx.y, rchunk = blockIdx.z;
+    const int kb0 = split * p.kb_per_split;
+    const int kb1 = min(p.nkb, kb0 + p.kb_per_split);
+    const int nit = kb1 - kb0;
+    const int64_t row0 = (int64_t)rchunk * NB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPkStages; ++s) {
+            mbar_init(full_pk(s), 1);
+            mbar_init(empty_pk(s), kExpandWarps);
+        }
+        for (int s = 0; s < kAbStages; ++s) {
+            mbar_init(full_ab(s), kExpandWarps);
+            mbar_init(empty_ab(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(sbase + L::misc, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer: packed weight tiles -> shared-memory ring ----------------
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_first();
+            for (int it = 0; it < nit; ++it) {
+                const int s = it % kPkStages;
+                const uint32_t ph = (it / kPkStages) & 1;
+                if (!mbar_wait(empty_pk(s), ph ^ 1, abort_flag, &g_status_word, 1)) break;
+                mbar_arrive_expect_tx(full_pk(s), Pk<FMT>::kStageBytes);
+                const int64_t kt = (int64_t)(kb0 + it) * 2;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint8_t *src = p.w + ((kt + h) * p.Nt + (int64_t)ntile * 4) * TB;
+                    bulk_g2s(sbase + L::pk + s * Pk<FMT>::kStageBytes + h * 4 * TB, src, 4 * TB, full_pk(s), policy);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/true, /*b_mn_major=*/false);
+            bool ok = true;
+            for (int it = 0; it < nit && ok; ++it) {
+                const int t = it % kAbStages;
+                const uint32_t ph = (it / kAbStages) & 1;
+                if (!mbar_wait(full_ab(t), ph, abort_flag, &g_status_word, 2)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t a_addr = sbase + L::a + t * kAStageBytes;
+                const uint32_t b_addr = sbase + L::b + t * L::kBStageBytes;
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16) {
+                    const uint64_t ad = smem_desc_noswizzle(a_addr + k16 * 2 * kA_LBO, kA_LBO, kA_SBO);
+                    const uint64_t bd = smem_desc_noswizzle(b_addr + k16 * 2 * kB_LBO, kB_LBO, kB_SBO);
+                    mma_bf16_ss(tmem_base, ad, bd, idesc, (it | k16) != 0);
+                }
+                mma_commit(empty_ab(t));
+            }
+            if (ok) mma_commit(accum_bar);
+        }
+    } else {
+        // ---------------- expand warps: packed -> bf16 operands, then epilogue ----------------
+        const int tid = threadIdx.x - 64;
+        const int ew = warp - 2;
+        constexpr int kActChunks = NB * 8 / kExpandThreads;  // 16-byte activation chunks per thread per K-block
+        uint4 act_regs[kActChunks];
+        auto load_act = [&](int it) {
+#pragma unroll
+            for (int j = 0; j < kActChunks; ++j) {
+                const int c = j * kExpandThreads + tid;
+                const int m = c % NB, kc = c / NB;
+                const int64_t off = act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8);
+                act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(p.a + off));
+            }
+        };
+        if (nit > 0) load_act(0);
+        bool ok = true;
+        for (int it = 0; it < nit; ++it) {
+            const int s = it % kPkStages, t = it % kAbStages;
+            const uint32_t phs = (it / kPkStages) & 1, pht = (it / kAbStages) & 1;
+            if (!mbar_wait(empty_ab(t), pht ^ 1, abort_flag, &g_status_word, 3)) { ok = false; break; }
+            // activations for this K-block (prefetched one block ahead)
+            uint8_t *bst = smem + L::b + t * L::kBStageBytes;
+#pragma unroll
+            for (int j = 0; j < kActChunks; ++j) {
+                const int c = j * kExpandThreads + tid;
+                const int m = c % NB, kc = c / NB;
+                *reinterpret_cast<uint4 *>(bst + (m >> 3) * kB_SBO + kc * kB_LBO + (m & 7) * 16) = act_regs[j];
+            }
+            if (it + 1 < nit) load_act(it + 1);
+            if (!mbar_wait(full_pk(s), phs, abort_flag, &g_status_word, 4)) { ok = false; break; }
+            const uint8_t *pst = smem + L::pk + s * Pk<FMT>::kStageBytes;
+            uint8_t *ast = smem + L::a + t * kAStageBytes;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int R = rr * kExpandThreads + tid;  // face row within the stage
+                const int tile = R >> 6, q = R & 63;      // tile = 4 * k_tile + n_tile
+                const int f = q >> 4, i = q & 15;
+                const uint8_t *tb = pst + tile * TB;
+                const uint32_t E = tb[q];
+                uint32_t codes[4], vals[8];
+                if (FMT == TTB_BFLOAT8_B) {
+                    const uint4 cv = *reinterpret_cast<const uint4 *>(tb + 64 + q * 16);
+                    codes[0] = cv.x; codes[1] = cv.y; codes[2] = cv.z; codes[3] = cv.w;
+                } else {
+                    const uint2 cv = *reinterpret_cast<const uint2 *>(tb + 64 + q * 8);
+                    codes[0] = cv.x; codes[1] = cv.y; codes[2] = 0; codes[3] = 0;
+                }
+                expand_row<FMT>(codes, E, vals);
+                const int k_local = (tile >> 2) * 32 + (f >> 1) * 16 + i;
+                const int n_local = (tile & 3) * 32 + (f & 1) * 16;
+                uint8_t *dst = ast + (k_local >> 3) * kA_LBO + (n_local >> 3) * kA_SBO + (k_local & 7) * 16;
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+                *reinterpret_cast<uint4 *>(dst + kA_SBO) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(full_ab(t));
+                mbar_arrive(empty_pk(s));
+            }
+        }
+
+        // ---------------- epilogue ----------------
+        if (ok && nit > 0) ok = mbar_wait(accum_bar, 0, abort_flag, &g_status_word, 5);
+        tc_fence_after_sync();
+        const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31 are visible to this warp
+        const int half = ew >> 2;                  // two warps share a quadrant and split the columns
+        constexpr int kColsPerWarp = NB / 2;
+        const int64_t n = (int64_t)ntile * BN + quad * 32 + lane;
+        const int tile_id = rchunk * gridDim.x + ntile;
+        if (ok && nit > 0) {
+#pragma unroll
+            for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
+                const int col0 = half * kColsPerWarp + cc * 16;
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, r);
+                tmem_ld_wait();
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                if (p.splits == 1) {
+                    finish_and_store<NB>(p, v, row0, col0, n);
+                } else {
+                    float4 *dst = reinterpret_cast<float4 *>(
+                        p.partial + (((int64_t)tile_id * p.splits + split) * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+        }
+        if (p.splits > 1) {
+            // The last block to arrive for this output tile adds all partials in split order and finishes.
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+            if (tid == 0) *last_flag = (atomicAdd(p.counters + tile_id, 1) == p.splits - 1) ? 1 : 0;
+            asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+            if (*last_flag) {
+                __threadfence();
+#pragma unroll
+                for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
+                    const int col0 = half * kColsPerWarp + cc * 16;
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float4 *src = reinterpret_cast<const float4 *>(
+                            p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 x = __ldcg(src + j);
+                            v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                        }
+                    }
+                    finish_and_store<NB>(p, v, row0, col0, n);
+                }
+                if (tid == 0) p.counters[tile_id] = 0;  // leave the scratch ready for the next launch
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // A wait ran out: give copies and MMAs still in flight a bounded time to land before the block's
+        // shared memory and tensor memory are released.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int FMT, int NB>
+int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
+    constexpr int smem_bytes = SmemLayout<FMT, NB>::total + 128;
+    static bool configured[64] = {};
+    int dev = 0;
+    TTB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_kernel<FMT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        configured[dev] = true;
+    }
+    matmul_decode_kernel<FMT, NB><<<grid, kThreadsDecode, smem_bytes, stream>>>(p);
+    TTB_LAUNCH_CHECK("matmul_decode");
+    return TTB_OK;
+}
+
+}  // namespace
+
+// Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
+static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32; }
+
+bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
+    return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
+           K % BK == 0 && N % BN == 0;
+}
+
+// Chooses how many blocks share one output tile along K so that the grid fills the 148 SMs in whole waves.
+void decode_plan(int64_t rows, int64_t K, int64_t N, int *splits_out, int *kb_per_split_out, int *tiles_out, int *nb_out) {
+    const int nb = decode_rows_per_block(rows);
+    const int tiles = (int)(N / BN) * (int)(rows / nb);
+    const int nkb = (int)(K / BK);
+    const int sms = 148;
+    int best_s = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 32 && s <= nkb; ++s) {
+        const int kbps = (nkb + s - 1) / s;
+        const int real_s = (nkb + kbps - 1) / kbps;
+        if (real_s != s) continue;
+        if (s > 1 && kbps < 4) break;
+        const int blocks = tiles * s;
+        const int waves = (blocks + sms - 1) / sms;
+        // time model in units of one K-block: each wave costs its blocks' K-blocks plus a fixed fill/drain
+        // overhead; split partials add a small reduction cost.
+        const double cost = waves * (kbps + 6.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
+        if (cost < best_cost) { best_cost = cost; best_s = s; }
+    }
+    const int kbps = (nkb + best_s - 1) / best_s;
+    *splits_out = (nkb + kbps - 1) / kbps;
+    *kb_per_split_out = kbps;
+    *tiles_out = tiles;
+    *nb_out = nb;
+}
+
+int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
+    int s, kbps, tiles, nb;
+    decode_plan(rows, K, N, &s, &kbps, &tiles, &nb);
+    if (s == 1) return 0;
+    const int64_t counters = ((int64_t)tiles * 4 + 255) / 256 * 256;
+    return counters + (int64_t)tiles * s * BN * nb * 4;
+}
+
+int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
+                             int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
+                             int64_t workspace_bytes, bool counters_are_zero, cudaStream_t stream) {
+    DecodeArgs p;
+    int tiles, nb;
+    decode_plan(rows, K, N, &p.splits, &p.kb_per_split, &tiles, &nb);
+    p.w = (const uint8_t *)w; p.a = (const uint16_t *)a; p.bias = (const uint16_t *)bias; p.out = out;
+    p.K = K; p.N = N; p.Kt = (int)(K / 32); p.Nt = (int)(N / 32); p.nkb = (int)(K / BK);
+    p.act = act; p.out_dtype = out_dtype;
+    p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
+    p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
+    p.partial = nullptr; p.counters = nullptr;
+    if (p.splits > 1) {
+        const int64_t need = decode_workspace_bytes(rows, K, N);
+        if (!workspace || workspace_bytes < need)
+            return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
+                        (long long)workspace_bytes);
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+            return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
+        const int64_t counters = ((int64_t)tiles * 4 + 255) / 256 * 256;
+        p.counters = (int *)workspace;
+        p.partial = (float *)((uint8_t *)workspace + counters);
+        if (!counters_are_zero) TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)counters, stream));
+    }
+    dim3 grid((unsigned)(N / BN), (unsigned)p.splits, (unsigned)(rows / nb));
+#define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, stream)
+    if (w_dtype == TTB_BFLOAT8_B) {
+        if (nb == 32) TTB_DECODE(TTB_BFLOAT8_B, 32);
+        if (nb == 64) TTB_DECODE(TTB_BFLOAT8_B, 64);
+        TTB_DECODE(TTB_BFLOAT8_B, 128);
+    } else {
+        if (nb == 32) TTB_DECODE(TTB_BFLOAT4_B, 32);
+        if (nb == 64) TTB_DECODE(TTB_BFLOAT4_B, 64);
+        TTB_DECODE(TTB_BFLOAT4_B, 128);
+    }
+#undef TTB_DECODE
+}
+
+int32_t read_and_clear_status(cudaStream_t stream) {
+    TTB_CUDA_TRY(cudaStreamSynchronize(stream));
+    int v = 0;
+    TTB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)));
+    if (v != 0) {
+        int zero = 0;
+        TTB_CUDA_TRY(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int)));
+        return fail(TTB_E_TIMEOUT, "a bounded device-side wait ran out (wait site %d)", v);
+    }
+    return TTB_OK;
+}
+
+}  // namespace ttb
