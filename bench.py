@@ -1,0 +1,430 @@
+"""Benchmark of the block-float weight-matmul path on B200.
+
+Workload (all N): the Llama-2-70B decode weight matmuls, batch 32, 80 layers, every weight bfloat8_b packed from
+N(0, 0.02), column-sharded over the N GPUs, with the four per-layer output all-gathers (NCCL) of the tensor-parallel
+scheme. One "step" = one pass over all 80 layers = 32 generated tokens. Strong scaling: the model is fixed, each
+GPU streams 1/N of the weight bytes.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]            # this framework
+  python bench.py --impl reference ...                            # the reference's CPU path on the host cores
+  torchrun ... bench.py --gpus N ...                              # N > 1: one rank per GPU
+
+Prints one JSON line (rank 0). `value` is tokens/s with everything resident in HBM, the whole step replayed as one
+CUDA graph; `e2e` is the same step driven through the public ttnn API with host activations copied in and the
+result copied out every step; `roofline` is the achieved weight-streaming bandwidth of the matmul kernel.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tt-metal_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+BATCH, HIDDEN, KV, FFN, LAYERS = 32, 8192, 1024, 28672, 80
+BF16, F32, BFP8, BFP4 = 0, 1, 3, 4
+TILE_BYTES = {BFP8: 1088, BFP4: 576}
+METRIC = "decode weight-GEMM tok/s (Llama-2-70B, bfloat8_b weights, batch 32)"
+WORKLOAD = ("llama2-70b tensor-parallel decode weight matmuls: batch 32, hidden 8192, kv 1024, ffn 28672, 80 layers, "
+            "bfloat8_b weights column-sharded over the GPUs, 4 output all-gathers per layer")
+
+
+def layer_gemms(G):
+    """(name, K, N per GPU, gather output?) for one Llama-2-70B decoder layer's weight matmuls."""
+    return [("wq", HIDDEN, HIDDEN // G, True), ("wk", HIDDEN, KV // G, False), ("wv", HIDDEN, KV // G, False),
+            ("wo", HIDDEN, HIDDEN // G, True), ("w1", HIDDEN, FFN // G, True), ("w3", HIDDEN, FFN // G, False),
+            ("w2", FFN, HIDDEN // G, True)]
+
+
+class Workload:
+    """A sweep of `layers` identical groups of weight matmuls: gemms = [(name, K, N, weight format, gather?)]."""
+
+    def __init__(self, key, G):
+        self.key = key
+        if key == "c5":
+            self.metric, self.unit, self.text = METRIC, "tok/s", WORKLOAD
+            self.layers = LAYERS
+            self.gemms = [(n, K, N, BFP8, g) for n, K, N, g in layer_gemms(G)]
+            self.seed = 4
+        elif key == "c3":
+            self.metric, self.unit = "decode weight-GEMM tok/s (Mistral-7B sweep, batch 32)", "tok/s"
+            self.text = ("mistral-7b decode weight-matmul sweep: batch 32, hidden 4096, 32 layers; Wq/Wo 4096x4096, Wk/Wv 4096x1024, "
+                         "w2 14336x4096 in bfloat8_b, w1/w3 4096x14336 in bfloat4_b")
+            self.layers = 32
+            self.gemms = [("wq", 4096, 4096, BFP8, False), ("wk", 4096, 1024, BFP8, False), ("wv", 4096, 1024, BFP8, False),
+                          ("wo", 4096, 4096, BFP8, False), ("w1", 4096, 14336, BFP4, False), ("w3", 4096, 14336, BFP4, False),
+                          ("w2", 14336, 4096, BFP8, False)]
+            self.seed = 2
+        elif key == "c2":
+            self.metric, self.unit = "bfp8_b GEMM HBM GB/s (Falcon-7B h_to_4h decode linear)", "GB/s"
+            self.text = ("single decode ttnn.linear, Falcon-7B h_to_4h: activation bf16 [32, 4544], weight bfloat8_b [4544, 18176]; "
+                         "4 distinct weights used in rotation so that no launch finds its weight in L2")
+            self.layers = 4
+            self.gemms = [("h_to_4h", 4544, 18176, BFP8, False)]
+            self.seed = 1
+        else:
+            raise SystemExit(f"unknown workload {key}")
+        if key != "c5" and G != 1:
+            raise SystemExit(f"workload {key} is a single-GPU configuration")
+
+    def bytes_per_layer(self):
+        """Algorithmic bytes: packed weight + bf16 activations read + bf16 outputs written."""
+        return sum(K * N // 1024 * TILE_BYTES[f] + BATCH * K * 2 + BATCH * N * 2 for _, K, N, f, _ in self.gemms)
+
+    def weight_bytes_per_layer(self):
+        return sum(K * N // 1024 * TILE_BYTES[f] for _, K, N, f, _ in self.gemms)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own path for this workload = host bfloat8_b packing + fp32 torch matmul on the unpacked
+# weights (the golden its tests compare against), timed on the host cores on a bounded sample.
+def cpu_reference_sample(threads=None):
+    import numpy as np
+    import torch
+    import oracle
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    ref = oracle.ref()
+    impl, kind = (ref, "reference") if ref is not None else (oracle.port(), "port")
+    g = torch.Generator().manual_seed(4)
+    # packing sample: the Wk weight of one layer (8192 x 1024), the reference's from_torch sequence, one thread
+    wk = (torch.randn(HIDDEN, KV, generator=g) * 0.02).numpy()
+    t0 = time.perf_counter()
+    packed = impl.from_torch(wk, oracle.BFP8_B, 1, HIDDEN, KV)
+    t_pack = time.perf_counter() - t0
+    pack_gbs = (wk.nbytes + packed.nbytes) / t_pack / 1e9
+    # matmul sample: one full decoder layer (G = 1) in fp32 on unpacked weights
+    x_h = torch.randn(BATCH, HIDDEN, generator=g).bfloat16().float()
+    x_f = torch.randn(BATCH, FFN, generator=g).bfloat16().float()
+    weights = []
+    w_small = torch.from_numpy(impl.to_torch(packed, oracle.BFP8_B, 1, HIDDEN, KV).reshape(HIDDEN, KV).copy())
+    for _, K, N, _ in layer_gemms(1):
+        # tile the unpacked sample weight to the layer's shapes: values stay bfloat8_b-representable N(0, 0.02)
+        weights.append(w_small.repeat(-(-K // HIDDEN), -(-N // KV))[:K, :N].contiguous())
+
+    def one_layer():
+        s = 0.0
+        for (name, K, N, _), w in zip(layer_gemms(1), weights):
+            y = torch.matmul(x_f if K == FFN else x_h, w)
+            s += float(y[0, 0])
+        return s
+    return one_layer, threads, kind, t_pack, pack_gbs
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    one_layer, threads, kind, t_pack, pack_gbs = cpu_reference_sample()
+    for _ in range(max(args.warmup, 1)):
+        one_layer()
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        one_layer()
+        times.append(time.perf_counter() - t0)
+    t_layer = sum(times) / len(times)
+    t_step = t_layer * LAYERS
+    value = BATCH / t_step
+    sample = (f"one decoder layer (7 fp32 torch matmuls on unpacked bfloat8_b weights) per step, scaled x{LAYERS}; "
+              f"host packing of one 8192x1024 weight took {t_pack:.2f} s ({pack_gbs:.3f} GB/s, 1 thread)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"tp{args.gpus}"},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
+def load_lib():
+    path = os.path.join(ROOT, "tt-metal_b200", "lib", "libttb.so")
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build the extension first (python -c 'import __graft_entry__ as g; g.build()')")
+    lib = ctypes.CDLL(path)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.ttb_last_error.restype = ctypes.c_char_p
+    lib.ttb_pack_bfp.argtypes = [vp, i32, vp, i32, i64, i64, i64, i32, i32, vp]
+    lib.ttb_tilize.argtypes = [vp, vp, i32, i64, i64, i64, vp]
+    lib.ttb_matmul_workspace_bytes.argtypes = [i32, i64, i64, i64, i64, i32]
+    lib.ttb_matmul_workspace_bytes.restype = i64
+    lib.ttb_matmul.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, i64, i32, i32, vp, i64, vp]
+    lib.ttb_check_status.argtypes = [vp]
+    return lib
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run for N > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU implementation of the product path")
+    torch.cuda.set_device(local_rank)
+    dev_t = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev_t)
+    G = world
+    lib = load_lib()
+
+    def ck(rc):
+        if rc != 0:
+            raise RuntimeError(lib.ttb_last_error().decode())
+
+    ZEROED = 8
+    wl = Workload(args.workload, G)
+    import ttnn
+    device = ttnn.open_device(local_rank)
+    mesh = ttnn.open_device_mesh(ttnn.DeviceGrid(1, G), list(range(G))) if G > 1 else None
+
+    # ---- synthetic weights: distinct per layer, generated and packed on the device ---------------------------
+    gen = torch.Generator(device=dev_t).manual_seed(wl.seed + 1000 * rank)
+    gemms = wl.gemms
+    NLAYERS = wl.layers
+    weights = []          # [layer][gemm] -> packed uint8 tensor
+    t_setup = time.perf_counter()
+    for _ in range(NLAYERS):
+        row = []
+        for _, K, N, fmt, _ in gemms:
+            w = torch.randn(K, N, generator=gen, device=dev_t, dtype=torch.float32) * 0.02
+            p = torch.empty(K * N // 1024 * TILE_BYTES[fmt], dtype=torch.uint8, device=dev_t)
+            ck(lib.ttb_pack_bfp(w.data_ptr(), F32, p.data_ptr(), fmt, 1, K, N, 1, 0, None))
+            row.append(p)
+            del w
+        weights.append(row)
+    torch.cuda.synchronize()
+    t_setup = time.perf_counter() - t_setup
+
+    # ---- activations (tiled bf16), outputs, gather buffers, workspace ------------------------------------------
+    def tiled_act(K, seed):
+        x = torch.randn(BATCH, K, generator=torch.Generator().manual_seed(seed)).bfloat16()
+        xd = x.to(dev_t)
+        out = torch.empty(BATCH * K, dtype=torch.bfloat16, device=dev_t)
+        ck(lib.ttb_tilize(xd.data_ptr(), out.data_ptr(), 2, 1, BATCH, K, None))
+        return x, out
+    acts = {}             # K -> (host bf16 [32, K], tiled device copy): a fresh N(0,1) activation per distinct K
+    for _, K, _, _, _ in gemms:
+        if K not in acts:
+            acts[K] = tiled_act(K, 40 + len(acts))
+    outs = [torch.empty(BATCH * N, dtype=torch.bfloat16, device=dev_t) for _, _, N, _, _ in gemms]
+    gathered = [torch.empty(G * BATCH * N, dtype=torch.bfloat16, device=dev_t) if g else None for _, _, N, _, g in gemms]
+    ws_bytes = max(lib.ttb_matmul_workspace_bytes(f, 1, BATCH, K, N, 0) for _, K, N, f, _ in gemms)
+    ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=dev_t)
+
+    def sweep(stream_handle, with_gather=True):
+        for layer in range(NLAYERS):
+            for i, (_, K, N, fmt, g) in enumerate(gemms):
+                a = acts[K][1]
+                ck(lib.ttb_matmul(a.data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16, 1, BATCH, K, N,
+                                  0, ZEROED, ws.data_ptr(), ws_bytes, stream_handle))
+                if g and G > 1 and with_gather:
+                    # tiled [32, N/G] shards are whole tile runs: the rank-major gather is the tiled [32, N] tensor
+                    dist.all_gather_into_tensor(gathered[i], outs[i])
+
+    def capture(with_gather):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            sweep(side.cuda_stream, with_gather)      # warm-up outside capture (lazy module loading, NCCL channels)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            sweep(torch.cuda.current_stream().cuda_stream, with_gather)
+        return graph
+
+    def barrier():
+        if G > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_replays(graph, steps, warmup):
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if G > 1:
+            t = torch.tensor([ms], device=dev_t)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    graph_full = capture(True)
+    with ClockSampler(local_rank) as clocks:
+        ms_total = timed_replays(graph_full, args.steps, args.warmup)
+    ms_step = ms_total / args.steps
+
+    # ---- roofline of the dominant kernel: the matmul-only sweep (no collectives), same weights -------------------
+    if G > 1:
+        graph_mm = capture(False)
+        ms_mm = timed_replays(graph_mm, args.steps, 1) / args.steps
+    else:
+        ms_mm = ms_step
+    launches_per_step = NLAYERS * len(gemms)
+    bytes_per_step = wl.bytes_per_layer() * NLAYERS
+    achieved = bytes_per_step / (ms_mm * 1e-3) / 1e9
+    to_value = (lambda sec: BATCH / sec) if wl.unit == "tok/s" else (lambda sec: bytes_per_step / sec / 1e9)
+    value = to_value(ms_step * 1e-3)
+    peak, peak_kind = peaks()
+    ck(lib.ttb_check_status(None))
+
+    # ---- end to end through the public API: host activations in, result out, every step -------------------------
+    def wrap(t_uint8, K, N, fmt):
+        return ttnn._ttnn.wrap_device_memory(t_uint8.data_ptr(), ttnn.Shape([K, N]), ttnn.bfloat8_b if fmt == BFP8 else ttnn.bfloat4_b,
+                                             ttnn.TILE_LAYOUT, device)
+    tt_weights = [[wrap(weights[l][i], K, N, f) for i, (_, K, N, f, _) in enumerate(gemms)] for l in range(NLAYERS)]
+    pinned = {K: v[0].pin_memory() for K, v in acts.items()}
+    h2d = sum(p.numel() * 2 for p in pinned.values())
+    last_n = gemms[-1][2] * (G if gemms[-1][4] else 1)
+    d2h = BATCH * last_n * 2
+
+    def e2e_step():
+        a = {K: ttnn.from_torch(p, layout=ttnn.TILE_LAYOUT, device=device) for K, p in pinned.items()}
+        if mesh is not None:
+            a = {K: ttnn.MultiDeviceTensor(t, mesh) for K, t in a.items()}
+        y = None
+        for layer in range(NLAYERS):
+            for i, (_, K, N, _, g) in enumerate(gemms):
+                y = ttnn.linear(a[K], tt_weights[layer][i])
+                if g and mesh is not None:
+                    y = ttnn.all_gather(y, dim=-1, num_links=1)
+        return ttnn.to_torch(y.local if mesh is not None else y)
+
+    for _ in range(min(args.warmup, 3)):
+        res = e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        res = e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if G > 1:
+        t = torch.tensor([e2e_s], device=dev_t, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = t.item()
+    assert res.shape == (BATCH, last_n) and bool(torch.isfinite(res.float()).all())
+
+    line = {
+        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": wl.text, "parallelism": f"tp{G}", "l2": "per-step working set (%.1f GB per GPU) far exceeds the 126 MB L2" % (bytes_per_step / 1e9),
+                   "timed": "CUDA-graph replay of the whole step", "setup_s": round(t_setup, 2)},
+        "clocks": clocks.summary(),
+        "e2e": {"value": to_value(e2e_s), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s * 1e3,
+                "api": f"ttnn.from_torch -> ttnn.linear x{launches_per_step} (+ ttnn.all_gather) -> ttnn.to_torch"},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "matmul_decode_kernel",
+                     "launches_per_step": launches_per_step, "algorithmic_bytes_per_step": bytes_per_step,
+                     "avg_launch_us": ms_mm * 1e3 / launches_per_step},
+    }
+    if rank == 0:
+        if G == 1 and not args.no_cpu_baseline and wl.key == "c5":
+            one_layer, threads, kind, t_pack, pack_gbs = cpu_reference_sample()
+            one_layer()
+            t0 = time.perf_counter()
+            reps = 3
+            for _ in range(reps):
+                one_layer()
+            t_layer = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {"value": BATCH / (t_layer * LAYERS), "unit": "tok/s", "cores": threads, "kind": kind,
+                                    "sample": f"{reps} passes over one decoder layer of fp32 torch matmuls on unpacked weights, scaled x{LAYERS}; "
+                                              f"host bfloat8_b packing of one 8192x1024 weight: {t_pack:.2f} s = {pack_gbs:.3f} GB/s on 1 thread"}
+        print(json.dumps(line), flush=True)
+    if G > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="c5", choices=["c5", "c3", "c2"],
+                    help="c5 = Llama-2-70B TP decode sweep (default, the headline), c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

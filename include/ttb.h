@@ -44,7 +44,7 @@ extern "C" {
 #define TTB_UINT32 2
 #define TTB_BFLOAT8_B 3
 #define TTB_BFLOAT4_B 4
-#define TTB_UINT16 5
+#define TTB_UINT16 6
 
 /* ---- fused activation after bias (ttnn.linear's `activation`, ttnn/ttnn/operations/matmul.py:59-63) */
 #define TTB_ACT_NONE 0
@@ -56,6 +56,8 @@ extern "C" {
 #define TTB_MM_A_ROW_MAJOR 1   /* activations are row-major [batch*M, K] instead of tiled        */
 #define TTB_MM_OUT_ROW_MAJOR 2 /* write the result row-major (the reference's untilize_out)      */
 #define TTB_MM_FORCE_GENERIC 4 /* use the shape-generic CUDA-core kernel (cross-check path)      */
+#define TTB_MM_WORKSPACE_ZEROED 8 /* the first 64 KiB of the workspace are zero: either freshly zeroed or
+                                    last used by a completed ttb_matmul (which leaves them zero)      */
 
 const char *ttb_last_error(void);
 int32_t ttb_version(void);
@@ -127,7 +129,9 @@ int32_t ttb_unpack_bfp(const void *src_dev, int32_t fmt, void *dst_dev, int32_t 
  * arithmetic. Stands in for tt::operations::primary::matmul and the multi-core-reuse program
  * factories (bmm_op.hpp:284-346, bmm_op.cpp:828-1303, and the multi_core_reuse program factories
  * beside them). `workspace` is device scratch of at least ttb_matmul_workspace_bytes() bytes (may be NULL when
- * that is 0); it is only touched between launch and completion of this call on `stream`. */
+ * that is 0); it is only touched between launch and completion of this call on `stream`. Its head holds
+ * per-output-tile arrival counters that must be zero when the kernel starts: ttb_matmul clears them with a
+ * memset on `stream` unless TTB_MM_WORKSPACE_ZEROED is given. */
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags);
 int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
                    void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,

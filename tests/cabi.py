@@ -10,9 +10,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(ROOT, "tt-metal_b200", "lib", "libttb.so")
 HEADER = os.path.join(ROOT, "include", "ttb.h")
 
-BFLOAT16, FLOAT32, UINT32, BFLOAT8_B, BFLOAT4_B, UINT16 = 0, 1, 2, 3, 4, 5
+BFLOAT16, FLOAT32, UINT32, BFLOAT8_B, BFLOAT4_B, UINT16 = 0, 1, 2, 3, 4, 6
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
-MM_A_ROW_MAJOR, MM_OUT_ROW_MAJOR, MM_FORCE_GENERIC = 1, 2, 4
+MM_A_ROW_MAJOR, MM_OUT_ROW_MAJOR, MM_FORCE_GENERIC, MM_WORKSPACE_ZEROED = 1, 2, 4, 8
 TILE_BYTES = {BFLOAT8_B: 1088, BFLOAT4_B: 576}
 
 _vp, _i32, _i64, _sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t

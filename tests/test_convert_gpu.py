@@ -108,7 +108,7 @@ def test_tilize_untilize(ttb, orc, dtype, shape):
     raw = x.view(torch.int32 if x.element_size() == 4 else torch.int16).numpy().view(npdt)
     xp = np.zeros((o, Hp, Wp), npdt)
     xp[:, :H, :W] = raw
-    want = orc.tilize(xp, o, Hp, Wp)
+    want = orc.tilize(xp, o, Hp, Wp).reshape(-1)
     tiled = ttb.tilize(x.cuda(), o, H, W)
     got = host(tiled.view(torch.int32 if x.element_size() == 4 else torch.int16)).view(npdt)
     assert np.array_equal(got, want)

@@ -1,0 +1,166 @@
+"""Host-side logic of the ttnn surface that needs no GPU: types, shapes, validation messages, the row-major host
+path, the tensor cache format, the all-gather shape plan and the multi-process mappers over gloo."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import ttnn
+from ttnn.operations.ccl import gather_plan
+
+
+def test_enum_values_follow_the_reference():
+    # tt_eager/tensor/types.hpp:24-34
+    assert int(ttnn.DataType.BFLOAT16) == 0 and int(ttnn.DataType.FLOAT32) == 1 and int(ttnn.DataType.UINT32) == 2
+    assert int(ttnn.DataType.BFLOAT8_B) == 3 and int(ttnn.DataType.BFLOAT4_B) == 4 and int(ttnn.DataType.UINT16) == 6
+    assert int(ttnn.Layout.ROW_MAJOR) == 0 and int(ttnn.Layout.TILE) == 1
+    assert ttnn.TILE_SIZE == 32
+
+
+def test_shape_with_tile_padding():
+    s = ttnn.Shape([1, 7, 3], [1, 32, 32])
+    assert list(s) == [1, 7, 3] and len(s) == 3 and s[-1] == 3
+    assert list(s.with_tile_padding()) == [1, 32, 32]
+    assert s == ttnn.Shape([1, 7, 3], [1, 32, 32]) and not (s == ttnn.Shape([1, 7, 3]))
+    with pytest.raises(RuntimeError):
+        ttnn.Shape([4, 4], [2, 4])
+
+
+def test_row_major_host_tensors_round_trip_without_a_gpu():
+    for dt in (torch.float32, torch.bfloat16, torch.int32):
+        x = (torch.arange(2 * 3 * 5, dtype=torch.float32).reshape(2, 3, 5) - 7).to(dt)
+        t = ttnn.from_torch(x)
+        assert list(t.shape) == [2, 3, 5] and t.layout == ttnn.ROW_MAJOR_LAYOUT
+        assert t.storage_type() == ttnn.StorageType.OWNED
+        assert torch.equal(ttnn.to_torch(t), x)
+    t = ttnn.from_torch(torch.ones(1, 1, 2, 4))
+    assert ttnn.to_torch(t, torch_rank=2).shape == (2, 4)
+    with pytest.raises(RuntimeError, match="Unable to squeeze"):
+        ttnn.to_torch(ttnn.from_torch(torch.ones(2, 2, 4)), torch_rank=2)
+    # fp32 -> bfloat16 uses torch's round-to-nearest-even like the reference (pytensor.cpp:86-90)
+    x = torch.tensor([[1.00390625, 1.01171875]])
+    assert torch.equal(ttnn.to_torch(ttnn.from_torch(x, dtype=ttnn.bfloat16)), x.bfloat16())
+
+
+def test_from_torch_validation_messages():
+    with pytest.raises(RuntimeError, match="requires TILE_LAYOUT"):
+        ttnn.from_torch(torch.zeros(32, 32), dtype=ttnn.bfloat8_b)
+    with pytest.raises(RuntimeError, match="at least 2 dimensions"):
+        ttnn.from_torch(torch.zeros(32), dtype=ttnn.bfloat4_b, layout=ttnn.TILE_LAYOUT)
+    with pytest.raises(RuntimeError, match="device must be specified"):
+        ttnn.from_torch(torch.zeros(32, 32), memory_config=ttnn.DRAM_MEMORY_CONFIG)
+
+
+def test_matmul_validation_happens_before_any_device_work():
+    a = ttnn.from_torch(torch.zeros(32, 64, dtype=torch.bfloat16))
+    b = ttnn.from_torch(torch.zeros(64, 32, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="must be of layout Layout.TILE"):
+        ttnn.matmul(a, b)
+    with pytest.raises(RuntimeError, match="not supported as activation"):
+        ttnn.linear(a, b, activation="tanh")
+    with pytest.raises(RuntimeError, match="rank 2, 3 or 4"):
+        ttnn.matmul(ttnn.from_torch(torch.zeros(64, dtype=torch.bfloat16)), b)
+
+
+def test_program_and_kernel_configs_are_accepted():
+    cfg = ttnn.MatmulMultiCoreReuseMultiCast1DProgramConfig(compute_with_storage_grid_size=(8, 4), in0_block_w=2, out_subblock_h=1,
+                                                            out_subblock_w=4, per_core_M=1, per_core_N=8, fuse_batch=True,
+                                                            fused_activation=("gelu", True), mcast_in0=True)
+    assert cfg.kind == "mcast_1d" and cfg.fused_activation == "gelu" and cfg.per_core_N == 8
+    ckc = ttnn.WormholeComputeKernelConfig(math_fidelity=ttnn.MathFidelity.HiFi2, fp32_dest_acc_en=True, packer_l1_acc=True)
+    assert ckc.fp32_dest_acc_en and ckc.math_fidelity == ttnn.MathFidelity.HiFi2
+    assert ttnn.CoreGrid(x=8, y=4).num_cores == 32
+
+
+def test_tensor_cache_round_trip(tmp_path):
+    x = torch.arange(6 * 10, dtype=torch.float32).reshape(6, 10)
+    t = ttnn.from_torch(x)
+    f = tmp_path / "w.bin"
+    ttnn.dump_tensor(str(f), t)
+    u = ttnn.load_tensor(str(f))
+    assert list(u.shape) == [6, 10] and u.dtype == ttnn.float32 and torch.equal(ttnn.to_torch(u), x)
+    (tmp_path / "bad.bin").write_bytes(b"nope")
+    with pytest.raises(RuntimeError, match="not a tensor cache file"):
+        ttnn.load_tensor(str(tmp_path / "bad.bin"))
+    v = ttnn.as_tensor(x, cache_file_name=str(tmp_path / "cache" / "w"))
+    assert (tmp_path / "cache" / "w_dtype_FLOAT32_layout_ROW_MAJOR.bin").exists()
+    w = ttnn.as_tensor(torch.zeros_like(x), cache_file_name=str(tmp_path / "cache" / "w"))   # served from the cache
+    assert torch.equal(ttnn.to_torch(w), x) and torch.equal(ttnn.to_torch(v), x)
+
+
+def _emulate_gather(shards, plan):
+    interleave, rows, row_bytes, _, _ = plan
+    staged = np.concatenate(shards)
+    if not interleave:
+        return staged
+    n = len(shards)
+    return staged.reshape(n, rows, row_bytes).transpose(1, 0, 2).reshape(-1)
+
+
+@pytest.mark.parametrize("shape,dim", [((1, 1, 32, 256), 3), ((1, 1, 64, 128), 3), ((2, 1, 32, 64), -1), ((1, 1, 64, 64), 2)])
+def test_all_gather_plan_reproduces_concat_for_tiled_tensors(orc, shape, dim):
+    """The rank-major concatenation (plus the tile-row interleave where the plan asks for it) of tiled shards equals the
+    tiling of torch.cat of the shards: the reference's emulated all-gather (models/demos/llama2_70b/tt/llama_common.py:99-106)."""
+    n = 4
+    full_shape = list(shape)
+    full_shape[dim] *= n
+    x = torch.arange(int(np.prod(full_shape)), dtype=torch.float32).reshape(full_shape).to(torch.bfloat16)
+    shards = torch.chunk(x, n, dim=dim)
+
+    def tiled_bytes(t):
+        o = int(np.prod(t.shape[:-2]))
+        return orc.tilize(t.contiguous().view(torch.int16).numpy().view(np.uint16), o, t.shape[-2], t.shape[-1]).reshape(-1).view(np.uint8)
+
+    plan = gather_plan(list(shape), list(shape), ttnn.bfloat16, ttnn.TILE_LAYOUT, dim, n)
+    got = _emulate_gather([tiled_bytes(s) for s in shards], plan)
+    assert plan[3] == full_shape
+    assert np.array_equal(got, tiled_bytes(x))
+
+
+def test_all_gather_plan_rejects_unsupported_dims():
+    with pytest.raises(RuntimeError, match="not supported"):
+        gather_plan([2, 2, 32, 32], [2, 2, 32, 32], ttnn.bfloat16, ttnn.TILE_LAYOUT, 1, 2)
+    with pytest.raises(RuntimeError, match="requires input tensors to be multi-device"):
+        ttnn.all_gather(ttnn.from_torch(torch.zeros(2, 2)), dim=1, num_links=1)
+
+
+_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path[:0] = [os.environ["TTB_PKG"]]
+import ttnn
+dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
+mesh = ttnn.open_device_mesh(ttnn.DeviceGrid(1, 2), [0, 1])
+assert mesh.get_num_devices() == 2 and mesh.local_index == dist.get_rank()
+w = torch.arange(8 * 12, dtype=torch.float32).reshape(8, 12)
+shard = ttnn.from_torch(w, mesh_mapper=ttnn.ShardTensorToMesh(mesh, dim=-1))       # column-sharded like the TP weights
+assert isinstance(shard, ttnn.MultiDeviceTensor) and list(shard.shape) == [8, 6]
+assert shard.storage_type() == ttnn.StorageType.MULTI_DEVICE_HOST
+assert torch.equal(ttnn.to_torch(shard.local), torch.chunk(w, 2, dim=-1)[dist.get_rank()])
+back = ttnn.to_torch(shard, mesh_composer=ttnn.ConcatMeshToTensor(mesh, dim=-1))
+assert torch.equal(back, w)
+rep = ttnn.from_torch(w, mesh_mapper=ttnn.ReplicateTensorToMesh(mesh))
+parts = ttnn.to_torch(rep, mesh_composer=ttnn.ListMeshToTensor(mesh))
+assert len(parts) == 2 and all(torch.equal(p, w) for p in parts)
+dist.barrier()
+dist.destroy_process_group()
+print("rank", os.environ["RANK"], "ok")
+"""
+
+
+def test_mesh_mappers_over_two_gloo_ranks(tmp_path):
+    """world_size 2 on CPU: ShardTensorToMesh / ReplicateTensorToMesh / ConcatMeshToTensor / ListMeshToTensor with one
+    process per device (tests/ttnn/unit_tests/test_multi_device.py:106-222 of the reference, restated for ranks)."""
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29731",
+                   TTB_PKG=os.path.join(root, "tt-metal_b200"))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    for p in procs:
+        out, _ = p.communicate(timeout=180)
+        assert p.returncode == 0, out.decode()

@@ -1,0 +1,141 @@
+"""The ttnn Python surface on a GPU: the reference's own API tests for this path, restated
+(tests/ttnn/unit_tests/test_to_and_from_torch.py:22-43, tests/tt_eager/.../misc/test_tensor.py:27-90,
+tests/ttnn/unit_tests/operations/test_linear.py, test_matmul.py), plus bit-exact checks against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import ttnn
+import vectors
+from golden_util import digests, sha
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def device():
+    dev = ttnn.open_device(0)
+    yield dev
+    ttnn.close_device(dev)
+
+
+@pytest.mark.parametrize("dtype,ofmt,name", [(ttnn.bfloat8_b, 0, "bfp8"), (ttnn.bfloat4_b, 1, "bfp4")])
+@pytest.mark.parametrize("on_device", [False, True])
+def test_from_torch_bytes_and_to_torch_values_match_golden(device, dtype, ofmt, name, on_device):
+    d = digests()
+    x = vectors.randn(0, (2, 3, 64, 96), 0.02)
+    t = ttnn.from_torch(x, dtype=dtype, layout=ttnn.TILE_LAYOUT, device=device if on_device else None)
+    assert list(t.shape) == [2, 3, 64, 96] and t.dtype == dtype and t.layout == ttnn.TILE_LAYOUT
+    assert t.storage_type() == (ttnn.StorageType.DEVICE if on_device else ttnn.StorageType.OWNED)
+    assert sha(np.frombuffer(t.buffer(), np.uint8)) == d[f"rand_2x3x64x96_seed0_{name}_from_torch"]
+    y = ttnn.to_torch(t)
+    assert y.dtype == torch.float32 and y.shape == x.shape
+    assert sha(y.numpy().view(np.uint32)) == d[f"rand_2x3x64x96_seed0_{name}_to_torch"]
+
+
+@pytest.mark.parametrize("dtype,atol", [(ttnn.bfloat8_b, 1e-2), (ttnn.bfloat4_b, 0.2)])
+def test_rand_round_trip_tolerance(device, dtype, atol):
+    torch.manual_seed(0)
+    x = torch.rand(2, 3, 64, 96)
+    t = ttnn.from_torch(x, dtype=dtype, layout=ttnn.TILE_LAYOUT, device=device)
+    t = ttnn.from_device(t)
+    assert torch.allclose(ttnn.to_torch(t), x, atol=atol, rtol=0)
+
+
+@pytest.mark.parametrize("dtype,ofmt", [(ttnn.bfloat8_b, 0), (ttnn.bfloat4_b, 1)])
+def test_shapes_that_need_tile_padding(device, orc, dtype, ofmt):
+    """7x3 bf16, as tests/ttnn/unit_tests/test_to_and_from_torch.py: zero-padded to one tile, logical shape kept."""
+    torch.manual_seed(0)
+    x = torch.rand(7, 3, dtype=torch.bfloat16)
+    t = ttnn.from_torch(x, dtype=dtype, layout=ttnn.TILE_LAYOUT)
+    assert list(t.shape) == [7, 3] and list(t.shape.with_tile_padding()) == [32, 32]
+    xp = np.zeros((32, 32), np.float32)
+    xp[:7, :3] = x.float().numpy()
+    assert np.array_equal(np.frombuffer(t.buffer(), np.uint8), orc.from_torch(xp, ofmt, 1, 32, 32))
+    y = ttnn.to_torch(t)
+    assert y.shape == (7, 3)
+    want = orc.to_torch(orc.from_torch(xp, ofmt, 1, 32, 32), ofmt, 1, 32, 32).reshape(32, 32)[:7, :3]
+    assert np.array_equal(y.numpy(), want)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(32, 32), (1, 1, 64, 96), (3, 50, 70)])
+def test_to_layout_round_trip_plain_types(device, dt, shape):
+    x = torch.randn(shape).to(dt)
+    t = ttnn.from_torch(x, layout=ttnn.ROW_MAJOR_LAYOUT, device=device)
+    tt = ttnn.to_layout(t, ttnn.TILE_LAYOUT)
+    assert tt.layout == ttnn.TILE_LAYOUT and list(tt.shape) == list(shape)
+    assert torch.equal(ttnn.to_torch(tt), x)
+    direct = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    assert direct.buffer() == tt.buffer()
+
+
+def test_block_float_row_major_form_matches_the_reference_sequence(device, orc):
+    """to(ROW_MAJOR) of a block-float tensor packs the row-major fp32 stream (tensor_impl.cpp:179-197)."""
+    x = vectors.randn(5, (64, 96), 0.02)
+    t = ttnn.from_torch(x, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    rm = ttnn.to_layout(t, ttnn.ROW_MAJOR_LAYOUT)
+    packed = orc.from_torch(x.numpy(), 0, 1, 64, 96)
+    want = orc.pack(orc.untilize(orc.unpack(packed, 0), 1, 64, 96), 0)
+    assert np.array_equal(np.frombuffer(rm.buffer(), np.uint8), want)
+    back = ttnn.to_layout(rm, ttnn.TILE_LAYOUT)
+    assert back.buffer() == t.buffer()
+
+
+@pytest.mark.parametrize("w_dtype", [ttnn.bfloat8_b, ttnn.bfloat4_b, ttnn.bfloat16])
+@pytest.mark.parametrize("a_shape,w_shape", [((1, 1, 32, 256), (256, 384)), ((32, 128), (128, 128)), ((2, 64, 96), (96, 160)),
+                                              ((1, 1, 7, 100), (100, 60))])
+def test_matmul_against_torch(device, w_dtype, a_shape, w_shape):
+    x = vectors.randn(11, a_shape, 1.0).bfloat16()
+    w = vectors.randn(12, w_shape, 0.02)
+    a = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    b = ttnn.from_torch(w, dtype=w_dtype, layout=ttnn.TILE_LAYOUT, device=device)
+    y = ttnn.matmul(a, b)
+    assert list(y.shape) == list(a_shape[:-1]) + [w_shape[-1]] and y.dtype == ttnn.bfloat16
+    w_ref = ttnn.to_torch(b).float()
+    y_ref = x.float() @ w_ref
+    got = ttnn.to_torch(y).float()
+    assert oracle.comp_pcc(y_ref.numpy(), got.numpy()) >= 0.9999
+    assert (got - y_ref).abs().max() / y_ref.abs().max() <= 1e-2
+    assert torch.equal(ttnn.to_torch(a @ b), ttnn.to_torch(y))
+
+
+@pytest.mark.parametrize("activation", [None, "relu", "gelu", "silu"])
+def test_linear_with_bias_and_activation(device, activation):
+    x = vectors.randn(21, (1, 1, 32, 4544 // 8 // 32 * 32), 1.0).bfloat16()
+    K = x.shape[-1]
+    w = vectors.randn(22, (K, 1024), 0.02)
+    bias = vectors.randn(23, (1, 1024), 0.5).bfloat16()
+    a = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    b = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    bt = ttnn.from_torch(bias, layout=ttnn.TILE_LAYOUT, device=device)
+    y = ttnn.to_torch(ttnn.linear(a, b, bias=bt, activation=activation, core_grid=ttnn.CoreGrid(y=4, x=8),
+                                  use_1d_systolic_array=True)).float()
+    ref = x.float() @ ttnn.to_torch(b) + bias.float()
+    ref = {None: lambda v: v, "relu": torch.relu, "gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu}[activation](ref)
+    assert oracle.comp_pcc(ref.numpy(), y.numpy()) >= 0.9999
+    assert (y - ref).abs().max() / ref.abs().max() <= 1e-2
+    y32 = ttnn.linear(a, b, bias=bt, activation=activation, dtype=ttnn.float32)
+    assert y32.dtype == ttnn.float32
+
+
+def test_matmul_errors(device):
+    a = ttnn.from_torch(torch.zeros(32, 64, dtype=torch.bfloat16), layout=ttnn.TILE_LAYOUT, device=device)
+    b = ttnn.from_torch(torch.zeros(32, 64), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    with pytest.raises(RuntimeError, match="width of the first tensor must be equal to the height of the second"):
+        ttnn.matmul(a, b)
+    host = ttnn.from_torch(torch.zeros(64, 32), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT)
+    with pytest.raises(RuntimeError, match="must be on device"):
+        ttnn.matmul(a, host)
+
+
+def test_single_device_mesh_and_cache_on_device(device, tmp_path):
+    mesh = ttnn.open_device_mesh(ttnn.DeviceGrid(1, 1), [0])
+    w = vectors.randn(3, (64, 128), 0.02)
+    t = ttnn.as_tensor(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device, cache_file_name=str(tmp_path / "w"))
+    u = ttnn.as_tensor(torch.zeros_like(w), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device, cache_file_name=str(tmp_path / "w"))
+    assert u.buffer() == t.buffer() and u.storage_type() == ttnn.StorageType.DEVICE
+    s = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device, mesh_mapper=ttnn.ShardTensorToMesh(mesh, dim=-1))
+    g = ttnn.all_gather(s, dim=-1, num_links=1)
+    assert torch.equal(ttnn.to_torch(g, mesh_composer=ttnn.ConcatMeshToTensor(mesh, dim=-1)), ttnn.to_torch(t))

@@ -65,7 +65,7 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
     auto s = (cudaStream_t)stream;
     if (!(flags & TTB_MM_FORCE_GENERIC) && decode_supported(w_dtype, rows, K, N))
         return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes,
-                                    false, s);
+                                    (flags & TTB_MM_WORKSPACE_ZEROED) != 0, s);
     return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
 }
 

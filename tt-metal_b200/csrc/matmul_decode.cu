@@ -377,12 +377,15 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
 
 }  // namespace
 
+// The head of the workspace holds one arrival counter per output tile; the partial sums follow.
+static constexpr int64_t kCounterBytes = 65536;
+
 // Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
 static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32; }
 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && N % BN == 0;
+           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes;
 }
 
 // Chooses how many blocks share one output tile along K so that the grid fills the 148 SMs in whole waves.
@@ -416,8 +419,7 @@ int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
     int s, kbps, tiles, nb;
     decode_plan(rows, K, N, &s, &kbps, &tiles, &nb);
     if (s == 1) return 0;
-    const int64_t counters = ((int64_t)tiles * 4 + 255) / 256 * 256;
-    return counters + (int64_t)tiles * s * BN * nb * 4;
+    return kCounterBytes + (int64_t)tiles * s * BN * nb * 4;
 }
 
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
@@ -439,7 +441,7 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
                         (long long)workspace_bytes);
         if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
             return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
-        const int64_t counters = ((int64_t)tiles * 4 + 255) / 256 * 256;
+        const int64_t counters = kCounterBytes;
         p.counters = (int *)workspace;
         p.partial = (float *)((uint8_t *)workspace + counters);
         if (!counters_are_zero) TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)counters, stream));
