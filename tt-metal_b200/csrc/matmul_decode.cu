@@ -2,20 +2,23 @@
 // with W in packed bfloat8_b / bfloat4_b tiles, rows in {32, 64, 128} per block.
 //
 // The kernel is bound by reading W once from HBM (1.0625 or 0.5625 bytes per weight), so everything is
-// organised around keeping many weight bytes in flight per SM:
+// organised around keeping many weight bytes in flight per SM and spending few instructions per weight:
 //   * "swap-AB": the tensor-core M dimension (128) runs over weight columns, the MMA N dimension over the
 //     activation rows, so a 32-row batch fills the MMA instead of wasting three quarters of it;
-//   * a producer thread streams packed tiles (whole 4-tile runs of 4352 / 2304 contiguous bytes) into an
-//     8-deep shared-memory ring with cp.async.bulk, each stage completing on an mbarrier;
-//   * eight warps expand the packed codes to bf16 (exact: sign + 7-bit mantissa under an 8-bit exponent fits
-//     bf16) straight into the tensor cores' canonical no-swizzle operand layout, and stage the activation
-//     K-block next to it;
+//   * a producer thread streams packed tiles (a run of four tiles = 4352 / 2304 contiguous bytes per stage)
+//     into a 16-deep shared-memory ring with cp.async.bulk, each stage completing on an mbarrier;
+//   * eight expand warps each own every eighth stage: one lane polls the barriers, the warp expands the 4096
+//     packed codes of the stage to bf16 (exact: sign + 7-bit mantissa under an 8-bit exponent fits bf16) straight
+//     into the tensor cores' canonical no-swizzle operand layout and stages the activation K-block next to it.
+//     Eight stages are therefore expanded concurrently, which hides barrier and shared-memory latency;
 //   * one thread issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32 in TMEM); tcgen05.commit hands operand
-//     stages back to the expanding warps;
-//   * the expanding warps then read the accumulator with tcgen05.ld and finish: either bias + activation +
+//     stages back to their expand warp;
+//   * the expand warps then read the accumulator with tcgen05.ld and finish: either bias + activation +
 //     store, or - when K is split over several blocks so that every SM streams - an fp32 partial into scratch,
 //     where the last block to arrive for an output tile adds the partials in a fixed order and finishes.
 // Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
+#include <type_traits>
+
 #include "epilogue.cuh"
 #include "sm100_ptx.cuh"
 
@@ -28,15 +31,30 @@ namespace {
 using namespace ptx;
 
 constexpr int BN = 128;           // weight columns per block (UMMA M)
-constexpr int BK = 64;            // K per pipeline stage (two tiles)
-constexpr int kExpandWarps = 8;
-constexpr int kExpandThreads = 32 * kExpandWarps;
-constexpr int kThreadsDecode = 64 + kExpandThreads;  // warp 0 producer, warp 1 MMA, warps 2..9 expand + epilogue
-constexpr int kPkStages = 8;
-constexpr int kAbStages = 4;
-constexpr int kAStageBytes = BN * BK * 2;       // 16 KiB
+constexpr int BK = 32;            // K per pipeline stage (one row of four tiles)
+// Twelve warps. A warp's scheduler is warp % 4: the two single-thread roles (warp 0 producer, warp 4 MMA issuer)
+// and an idle warp 8 share scheduler 0, so the MMA issuer never competes with expand warps for issue slots.
+// The nine warps with warp % 4 != 0 expand; warps 0..7 run the epilogue (TMEM lane quadrant = warp % 4).
+constexpr int kWarps = 12;
+constexpr int kThreadsDecode = 32 * kWarps;
+constexpr int kExpandWarps = 9;
+constexpr int kProducerWarp = 0, kMmaWarp = 4;
+constexpr int kEpilogueThreads = 256;
+// Stages are handled in groups of three consecutive K-blocks, one per warp of an expand-warp triplet, with one
+// mbarrier per group: the producer and the MMA issuer then pay their per-iteration latencies (barrier wait,
+// tcgen05 fence, commit) once per three stages.
+constexpr int kGroup = 3;
+constexpr int kPkGroups = 5;                    // packed ring: 15 stages
+constexpr int kPkStages = kGroup * kPkGroups;
+template <int NB>
+struct Ab {
+    // bf16 operand ring (per stage: A 8 KiB + B NB*64 bytes), in groups of three stages
+    static constexpr int kGroups = NB == 128 ? 3 : 4;
+    static constexpr int kStages = kGroup * kGroups;
+};
+constexpr int kAStageBytes = BN * BK * 2;       // 8 KiB
 constexpr uint32_t kA_LBO = 2048, kA_SBO = 128;  // A (weights, N-contiguous): K-groups 2 KiB apart, N-groups adjacent
-constexpr uint32_t kB_LBO = 128, kB_SBO = 1024;  // B (activations, K-contiguous): K-groups adjacent, row-groups 1 KiB apart
+constexpr uint32_t kB_LBO = 128, kB_SBO = 512;   // B (activations, K-contiguous): K-groups adjacent, row-groups 512 B apart
 
 struct DecodeArgs {
     const uint8_t *w;
@@ -54,7 +72,7 @@ struct DecodeArgs {
 template <int FMT>
 struct Pk {
     static constexpr int kTileBytes = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
-    static constexpr int kStageBytes = 8 * kTileBytes;
+    static constexpr int kStageBytes = 4 * kTileBytes;
 };
 
 template <int FMT, int NB>
@@ -62,54 +80,61 @@ struct SmemLayout {
     static constexpr int kBStageBytes = NB * BK * 2;
     static constexpr int pk = 0;
     static constexpr int a = pk + kPkStages * Pk<FMT>::kStageBytes;
+    static constexpr int kAbStages = Ab<NB>::kStages;
     static constexpr int b = a + kAbStages * kAStageBytes;
     static constexpr int bars = b + kAbStages * kBStageBytes;
-    // barriers: full_pk[kPkStages], empty_pk[kPkStages], full_ab[kAbStages], empty_ab[kAbStages], accum
-    static constexpr int nbars = 2 * kPkStages + 2 * kAbStages + 1;
+    // barriers: full_pk[kPkGroups], empty_pk[kPkGroups], full_ab[kAbGroups], empty_ab[kAbGroups], accum
+    static constexpr int kAbGroups = Ab<NB>::kGroups;
+    static constexpr int nbars = 2 * kPkGroups + 2 * kAbGroups + 1;
     static constexpr int misc = bars + 8 * nbars;  // tmem base (4), abort flag (4), last-block flag (4)
     static constexpr int total = misc + 16;
 };
 
 // Expands one face row (16 codes sharing exponent E) into 16 bf16 values, returned as eight packed pairs.
-// value = +-m * 2^(E - 133) (bfloat8_b) or +-m * 2^(E - 129) (bfloat4_b). The integer mantissa is turned into a
-// bf16 by OR-ing it under the exponent of 128 (bits 0x4300 | m == 128 + m), then one fused multiply-add with
-// the power-of-two scale removes the 128 and applies the exponent; the sign bit is OR-ed on last.
-// Rows with E below the scale's exponent range (values under 2^-120) are flushed to zero.
-template <int FMT>
+// value = +-m * 2^(E - 133) (bfloat8_b) or +-m * 2^(E - 129) (bfloat4_b). A bf16 with a zero exponent field and
+// mantissa bits m is the subnormal m * 2^-133, so the halfword (sign << 15) | m (bfloat8_b) or
+// (sign << 15) | (m << 4) (bfloat4_b) already is the weight up to the factor 2^E: one packed multiply by the
+// power of two finishes it, exactly. 2^E is a bf16 only up to E = 127 (rows whose largest magnitude is below 2);
+// larger exponents take a second multiply (BIG; chosen per stage by a warp vote so that the common path has no
+// divergent branch).
+template <int FMT, bool BIG>
 __device__ __forceinline__ void expand_row(const uint32_t *codes, uint32_t E, uint32_t (&out)[8]) {
-    constexpr int kBiasExp = FMT == TTB_BFLOAT8_B ? 6 : 2;
-    E = min(E, 247u + kBiasExp);  // keeps 128 * scale finite; only rows holding Inf/NaN-class values are affected
-    const uint32_t sbits = E > (uint32_t)kBiasExp ? ((E - kBiasExp) << 7) : 0u;  // bf16 bits of the scale
-    const uint32_t scale2 = sbits | (sbits << 16);
-    // -128 * scale: exponent + 7, sign set.
-    const uint32_t nb = sbits ? ((sbits + (7u << 7)) | 0x8000u) : 0u;
-    const uint32_t nbias2 = nb | (nb << 16);
+    const uint32_t e1 = min(E, 127u);
+    const uint32_t sb = (e1 + 127u) << 7;
+    const uint32_t scale2 = sb | (sb << 16);
     const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&scale2);
-    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162 *>(&nbias2);
     if (FMT == TTB_BFLOAT8_B) {
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
             const uint32_t w = codes[wi];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t x = __byte_perm(w, 0u, h ? 0x4342u : 0x4140u);  // [c_even, 0, c_odd, 0]
-                uint32_t mant = (x & 0x007f007fu) | 0x43004300u;
-                __nv_bfloat162 v = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&mant), s2, b2);
-                out[2 * wi + h] = *reinterpret_cast<uint32_t *>(&v) | ((x << 8) & 0x80008000u);
+                uint32_t x = __byte_perm(w, 0u, h ? 0x3322u : 0x1100u) & 0x807f807fu;  // [c, c] per halfword -> sign | mantissa
+                __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&x), s2);
+                out[2 * wi + h] = *reinterpret_cast<uint32_t *>(&v);
             }
         }
     } else {
 #pragma unroll
         for (int wi = 0; wi < 2; ++wi) {
             const uint32_t w = codes[wi];
-            const uint32_t ev = w & 0x0f0f0f0fu, od = (w >> 4) & 0x0f0f0f0fu;  // even / odd elements, one per byte
+            const uint32_t ev = (w << 4) & 0xf0f0f0f0u, od = w & 0xf0f0f0f0u;  // even / odd elements: [s m m m 0 0 0 0] per byte
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                const uint32_t x = __byte_perm(ev, od, (uint32_t)(p | ((4 + p) << 8)));  // [ev_p, ev_0, od_p, ev_0]
-                uint32_t mant = (x & 0x00070007u) | 0x43004300u;
-                __nv_bfloat162 v = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&mant), s2, b2);
-                out[4 * wi + p] = *reinterpret_cast<uint32_t *>(&v) | ((x << 12) & 0x80008000u);
+                uint32_t x = __byte_perm(ev, od, (uint32_t)(p | (p << 4) | ((4 + p) << 8) | ((4 + p) << 12))) & 0x80708070u;
+                __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&x), s2);
+                out[4 * wi + p] = *reinterpret_cast<uint32_t *>(&v);
             }
+        }
+    }
+    if (BIG) {
+        const uint32_t tb = max(min(E, 254u), 127u) << 7;  // 2^(E - 127), 1 for rows at or below 127
+        const uint32_t t2v = tb | (tb << 16);
+        const __nv_bfloat162 t2 = *reinterpret_cast<const __nv_bfloat162 *>(&t2v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&out[i]), t2);
+            out[i] = *reinterpret_cast<uint32_t *>(&v);
         }
     }
 }
@@ -140,16 +165,18 @@ template <int FMT, int NB>
 __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const DecodeArgs p) {
     using L = SmemLayout<FMT, NB>;
     constexpr int TB = Pk<FMT>::kTileBytes;
-    constexpr int kTmemCols = NB < 32 ? 32 : NB;
+    constexpr int kAcc = NB == 32 ? 4 : NB == 64 ? 4 : 2;  // independent accumulators, used round-robin over K steps
+    constexpr int kTmemCols = NB * kAcc < 32 ? 32 : NB * kAcc;
+    constexpr int kAbGroups = Ab<NB>::kGroups;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::bars;
     auto full_pk = [&](int s) { return bar0 + 8u * s; };
-    auto empty_pk = [&](int s) { return bar0 + 8u * (kPkStages + s); };
-    auto full_ab = [&](int s) { return bar0 + 8u * (2 * kPkStages + s); };
-    auto empty_ab = [&](int s) { return bar0 + 8u * (2 * kPkStages + kAbStages + s); };
-    const uint32_t accum_bar = bar0 + 8u * (2 * kPkStages + 2 * kAbStages);
+    auto empty_pk = [&](int s) { return bar0 + 8u * (kPkGroups + s); };
+    auto full_ab = [&](int s) { return bar0 + 8u * (2 * kPkGroups + s); };
+    auto empty_ab = [&](int s) { return bar0 + 8u * (2 * kPkGroups + kAbGroups + s); };
+    const uint32_t accum_bar = bar0 + 8u * (2 * kPkGroups + 2 * kAbGroups);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
     volatile int *last_flag = reinterpret_cast<volatile int *>(smem + L::misc + 8);
@@ -159,15 +186,16 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(p.nkb, kb0 + p.kb_per_split);
     const int nit = kb1 - kb0;
+    const int ngroups = (nit + kGroup - 1) / kGroup;
     const int64_t row0 = (int64_t)rchunk * NB;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPkStages; ++s) {
+        for (int s = 0; s < kPkGroups; ++s) {
             mbar_init(full_pk(s), 1);
-            mbar_init(empty_pk(s), kExpandWarps);
+            mbar_init(empty_pk(s), kGroup);
         }
-        for (int s = 0; s < kAbStages; ++s) {
-            mbar_init(full_ab(s), kExpandWarps);
+        for (int s = 0; s < kAbGroups; ++s) {
+            mbar_init(full_ab(s), kGroup);
             mbar_init(empty_ab(s), 1);
         }
         mbar_init(accum_bar, 1);
@@ -175,7 +203,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         *last_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         tmem_alloc(sbase + L::misc, kTmemCols);
         tmem_relinquish();
     }
@@ -183,114 +211,156 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
 
-    if (warp == 0) {
+    if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles -> shared-memory ring ----------------
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
-            for (int it = 0; it < nit; ++it) {
-                const int s = it % kPkStages;
-                const uint32_t ph = (it / kPkStages) & 1;
-                if (!mbar_wait(empty_pk(s), ph ^ 1, abort_flag, &g_status_word, 1)) break;
-                mbar_arrive_expect_tx(full_pk(s), Pk<FMT>::kStageBytes);
-                const int64_t kt = (int64_t)(kb0 + it) * 2;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint8_t *src = p.w + ((kt + h) * p.Nt + (int64_t)ntile * 4) * TB;
-                    bulk_g2s(sbase + L::pk + s * Pk<FMT>::kStageBytes + h * 4 * TB, src, 4 * TB, full_pk(s), policy);
+            const uint8_t *src = p.w + ((int64_t)kb0 * p.Nt + (int64_t)ntile * 4) * TB;
+            const int64_t src_step = (int64_t)p.Nt * TB;
+            int gs = 0;
+            uint32_t ph = 0;
+            for (int g = 0; g < ngroups; ++g) {
+                const int r = min(kGroup, nit - g * kGroup);  // stages in this group (the last one may be short)
+                if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, &g_status_word, 1)) { ok = false; break; }
+                mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
+                for (int j = 0; j < r; ++j) {
+                    bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
+                    src += src_step;
                 }
+                if (++gs == kPkGroups) { gs = 0; ph ^= 1; }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/true, /*b_mn_major=*/false);
-            bool ok = true;
-            for (int it = 0; it < nit && ok; ++it) {
-                const int t = it % kAbStages;
-                const uint32_t ph = (it / kAbStages) & 1;
-                if (!mbar_wait(full_ab(t), ph, abort_flag, &g_status_word, 2)) { ok = false; break; }
+            // descriptors differ between stages and K steps only in the 14-bit start-address field (units of 16 B)
+            const uint64_t a_desc0 = smem_desc_noswizzle(sbase + L::a, kA_LBO, kA_SBO);
+            const uint64_t b_desc0 = smem_desc_noswizzle(sbase + L::b, kB_LBO, kB_SBO);
+            int gt = 0, acc = 0, steps = 0;
+            uint32_t ph = 0;
+            for (int g = 0; g < ngroups; ++g) {
+                const int r = min(kGroup, nit - g * kGroup);
+                for (int j = r; j < kGroup; ++j) mbar_arrive(full_ab(gt));  // stand in for the stages a short last group lacks
+                if (!mbar_wait(full_ab(gt), ph, abort_flag, &g_status_word, 2)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t a_addr = sbase + L::a + t * kAStageBytes;
-                const uint32_t b_addr = sbase + L::b + t * L::kBStageBytes;
+                for (int j = 0; j < r; ++j) {
+                    const int t = gt * kGroup + j;
+                    const uint64_t ad = a_desc0 + (uint64_t)((t * kAStageBytes) >> 4);
+                    const uint64_t bd = b_desc0 + (uint64_t)((t * L::kBStageBytes) >> 4);
 #pragma unroll
-                for (int k16 = 0; k16 < BK / 16; ++k16) {
-                    const uint64_t ad = smem_desc_noswizzle(a_addr + k16 * 2 * kA_LBO, kA_LBO, kA_SBO);
-                    const uint64_t bd = smem_desc_noswizzle(b_addr + k16 * 2 * kB_LBO, kB_LBO, kB_SBO);
-                    mma_bf16_ss(tmem_base, ad, bd, idesc, (it | k16) != 0);
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        // consecutive K steps go to different accumulators; each one's first use overwrites
+                        mma_bf16_ss(tmem_base + (uint32_t)(acc * NB), ad + (uint64_t)((k16 * 2 * kA_LBO) >> 4),
+                                    bd + (uint64_t)((k16 * 2 * kB_LBO) >> 4), idesc, steps >= kAcc);
+                        acc = acc + 1 == kAcc ? 0 : acc + 1;
+                        ++steps;
+                    }
                 }
-                mma_commit(empty_ab(t));
+                mma_commit(empty_ab(gt));
+                if (++gt == kAbGroups) { gt = 0; ph ^= 1; }
             }
             if (ok) mma_commit(accum_bar);
         }
-    } else {
-        // ---------------- expand warps: packed -> bf16 operands, then epilogue ----------------
-        const int tid = threadIdx.x - 64;
-        const int ew = warp - 2;
-        constexpr int kActChunks = NB * 8 / kExpandThreads;  // 16-byte activation chunks per thread per K-block
+    } else if ((warp & 3) != 0) {
+        // ---------------- expand warps: packed -> bf16 operands ----------------
+        const int ew = (warp >> 2) * 3 + (warp & 3) - 1;
+        constexpr int kActChunks = NB / 8;  // 16-byte activation chunks per lane per K-block (NB rows x 4 chunks)
         uint4 act_regs[kActChunks];
         auto load_act = [&](int it) {
 #pragma unroll
             for (int j = 0; j < kActChunks; ++j) {
-                const int c = j * kExpandThreads + tid;
+                const int c = j * 32 + lane;
                 const int m = c % NB, kc = c / NB;
                 const int64_t off = act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8);
                 act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(p.a + off));
             }
         };
-        if (nit > 0) load_act(0);
-        bool ok = true;
-        for (int it = 0; it < nit; ++it) {
-            const int s = it % kPkStages, t = it % kAbStages;
-            const uint32_t phs = (it / kPkStages) & 1, pht = (it / kAbStages) & 1;
-            if (!mbar_wait(empty_ab(t), pht ^ 1, abort_flag, &g_status_word, 3)) { ok = false; break; }
-            // activations for this K-block (prefetched one block ahead)
-            uint8_t *bst = smem + L::b + t * L::kBStageBytes;
+        if (ew < nit) load_act(ew);  // this warp's first stage is K-block ew (group ew / 3, member ew % 3)
+        // lane-constant parts of the addressing: lanes 0-15 take the left face of a tile, 16-31 the right one
+        const int lane_pk = lane * (FMT == TTB_BFLOAT8_B ? 16 : 8);
+        const int lane_a = ((lane & 15) >> 3) * kA_LBO + (lane >> 4) * 2 * kA_SBO + (lane & 7) * 16;
+        // triplet ew / 3 takes every third group; within a group this warp expands stage ew % 3
+        for (int g = ew / kGroup; g < ngroups; g += kExpandWarps / kGroup) {
+            const int it = g * kGroup + ew % kGroup;
+            if (it >= nit) break;  // short last group: the MMA issuer arrives in this warp's place
+            const int gs = g % kPkGroups, gt = g % kAbGroups;
+            const int s = gs * kGroup + ew % kGroup, t = gt * kGroup + ew % kGroup;
+            const uint32_t phs = (g / kPkGroups) & 1, pht = (g / kAbGroups) & 1;
+            int good = 1;
+            if (lane == 0)
+                good = mbar_wait(empty_ab(gt), pht ^ 1, abort_flag, &g_status_word, 3) &&
+                       mbar_wait(full_pk(gs), phs, abort_flag, &g_status_word, 4);
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) { ok = false; break; }
+            const uint8_t *pst = smem + L::pk + s * Pk<FMT>::kStageBytes;
+            uint8_t *const ast = smem + L::a + t * kAStageBytes + lane_a;
+            uint8_t *const bst = smem + L::b + t * L::kBStageBytes;
+            // all shared-memory loads of the stage first, so that their latency is paid once
+            uint32_t Es[8];
+            uint32_t codes[8][4];
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+                // face row R = rr * 32 + lane of the stage: tile rr / 2, faces 2 * (rr & 1) (+1 for lanes 16-31), row lane & 15
+                const uint8_t *tb = pst + (rr >> 1) * TB;
+                Es[rr] = tb[(rr & 1) * 32 + lane];
+                if (FMT == TTB_BFLOAT8_B) {
+                    const uint4 cv = *reinterpret_cast<const uint4 *>(tb + 64 + (rr & 1) * 512 + lane_pk);
+                    codes[rr][0] = cv.x; codes[rr][1] = cv.y; codes[rr][2] = cv.z; codes[rr][3] = cv.w;
+                } else {
+                    const uint2 cv = *reinterpret_cast<const uint2 *>(tb + 64 + (rr & 1) * 256 + lane_pk);
+                    codes[rr][0] = cv.x; codes[rr][1] = cv.y; codes[rr][2] = 0; codes[rr][3] = 0;
+                }
+            }
+            uint32_t emax = Es[0];
+#pragma unroll
+            for (int rr = 1; rr < 8; ++rr) emax = max(emax, Es[rr]);
+            auto expand_stage = [&](auto big) {
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    uint32_t vals[8];
+                    expand_row<FMT, decltype(big)::value>(codes[rr], Es[rr], vals);
+                    // k_local = (rr & 1) * 16 + (lane & 15), n_local = (rr / 2) * 32 + (lane / 16) * 16
+                    uint8_t *dst = ast + (rr & 1) * 2 * kA_LBO + (rr >> 1) * 4 * kA_SBO;
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+                    *reinterpret_cast<uint4 *>(dst + kA_SBO) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
+                }
+            };
+            if (__any_sync(0xffffffffu, emax > 127u))
+                expand_stage(std::true_type{});
+            else
+                expand_stage(std::false_type{});
+            // activations of this K-block: loaded from global one turn ahead, stored last so the load has landed
 #pragma unroll
             for (int j = 0; j < kActChunks; ++j) {
-                const int c = j * kExpandThreads + tid;
+                const int c = j * 32 + lane;
                 const int m = c % NB, kc = c / NB;
                 *reinterpret_cast<uint4 *>(bst + (m >> 3) * kB_SBO + kc * kB_LBO + (m & 7) * 16) = act_regs[j];
-            }
-            if (it + 1 < nit) load_act(it + 1);
-            if (!mbar_wait(full_pk(s), phs, abort_flag, &g_status_word, 4)) { ok = false; break; }
-            const uint8_t *pst = smem + L::pk + s * Pk<FMT>::kStageBytes;
-            uint8_t *ast = smem + L::a + t * kAStageBytes;
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-                const int R = rr * kExpandThreads + tid;  // face row within the stage
-                const int tile = R >> 6, q = R & 63;      // tile = 4 * k_tile + n_tile
-                const int f = q >> 4, i = q & 15;
-                const uint8_t *tb = pst + tile * TB;
-                const uint32_t E = tb[q];
-                uint32_t codes[4], vals[8];
-                if (FMT == TTB_BFLOAT8_B) {
-                    const uint4 cv = *reinterpret_cast<const uint4 *>(tb + 64 + q * 16);
-                    codes[0] = cv.x; codes[1] = cv.y; codes[2] = cv.z; codes[3] = cv.w;
-                } else {
-                    const uint2 cv = *reinterpret_cast<const uint2 *>(tb + 64 + q * 8);
-                    codes[0] = cv.x; codes[1] = cv.y; codes[2] = 0; codes[3] = 0;
-                }
-                expand_row<FMT>(codes, E, vals);
-                const int k_local = (tile >> 2) * 32 + (f >> 1) * 16 + i;
-                const int n_local = (tile & 3) * 32 + (f & 1) * 16;
-                uint8_t *dst = ast + (k_local >> 3) * kA_LBO + (n_local >> 3) * kA_SBO + (k_local & 7) * 16;
-                *reinterpret_cast<uint4 *>(dst) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
-                *reinterpret_cast<uint4 *>(dst + kA_SBO) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(full_ab(t));
-                mbar_arrive(empty_pk(s));
+                mbar_arrive(full_ab(gt));
+                mbar_arrive(empty_pk(gs));
             }
+            if (it + kExpandWarps < nit) load_act(it + kExpandWarps);
         }
+    }
 
-        // ---------------- epilogue ----------------
-        if (ok && nit > 0) ok = mbar_wait(accum_bar, 0, abort_flag, &g_status_word, 5);
+    if (warp < 8) {
+        // ---------------- epilogue: warps 0..7, TMEM lane quadrant warp % 4, column half warp / 4 ----------------
+        const int tid = threadIdx.x;
+        {
+            int good = ok ? 1 : 0;
+            good = __shfl_sync(0xffffffffu, good, 0);   // lane 0 ran the single-thread roles
+            if (lane == 0 && good && nit > 0) good = mbar_wait(accum_bar, 0, abort_flag, &g_status_word, 5);
+            ok = __shfl_sync(0xffffffffu, good, 0) != 0;
+        }
         tc_fence_after_sync();
-        const int quad = warp & 3;                 // TMEM lanes 32*quad .. 32*quad+31 are visible to this warp
-        const int half = ew >> 2;                  // two warps share a quadrant and split the columns
+        const int quad = warp & 3;
+        const int half = warp >> 2;
         constexpr int kColsPerWarp = NB / 2;
         const int64_t n = (int64_t)ntile * BN + quad * 32 + lane;
         const int tile_id = rchunk * gridDim.x + ntile;
@@ -298,12 +368,17 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
 #pragma unroll
             for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
                 const int col0 = half * kColsPerWarp + cc * 16;
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, r);
-                tmem_ld_wait();
                 float v[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                const int nacc = min(kAcc, nit * (BK / 16));  // accumulators that received at least one K step
+                for (int ac = 0; ac < nacc; ++ac) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ac * NB + col0), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
+                }
                 if (p.splits == 1) {
                     finish_and_store<NB>(p, v, row0, col0, n);
                 } else {
@@ -317,9 +392,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         if (p.splits > 1) {
             // The last block to arrive for this output tile adds all partials in split order and finishes.
             __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
             if (tid == 0) *last_flag = (atomicAdd(p.counters + tile_id, 1) == p.splits - 1) ? 1 : 0;
-            asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
             if (*last_flag) {
                 __threadfence();
 #pragma unroll
@@ -354,7 +429,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -400,12 +475,12 @@ void decode_plan(int64_t rows, int64_t K, int64_t N, int *splits_out, int *kb_pe
         const int kbps = (nkb + s - 1) / s;
         const int real_s = (nkb + kbps - 1) / kbps;
         if (real_s != s) continue;
-        if (s > 1 && kbps < 4) break;
+        if (s > 1 && kbps < 8) break;
         const int blocks = tiles * s;
         const int waves = (blocks + sms - 1) / sms;
         // time model in units of one K-block: each wave costs its blocks' K-blocks plus a fixed fill/drain
         // overhead; split partials add a small reduction cost.
-        const double cost = waves * (kbps + 6.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
+        const double cost = waves * (kbps + 16.0) + (s > 1 ? 2.0 + 0.5 * s : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     const int kbps = (nkb + best_s - 1) / best_s;
