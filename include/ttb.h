@@ -56,6 +56,8 @@ extern "C" {
 #define TTB_MM_A_ROW_MAJOR 1   /* activations are row-major [batch*M, K] instead of tiled        */
 #define TTB_MM_OUT_ROW_MAJOR 2 /* write the result row-major (the reference's untilize_out)      */
 #define TTB_MM_FORCE_GENERIC 4 /* use the shape-generic CUDA-core kernel (cross-check path)      */
+#define TTB_MM_DECODE_TMEM_OPERAND 16 /* bfloat8_b decode shapes: feed the expanded weights to the MMA through
+                                         tensor memory (ldmatrix.trans + tcgen05.st) instead of shared memory */
 #define TTB_MM_WORKSPACE_ZEROED 8 /* the first 64 KiB of the workspace are zero: either freshly zeroed or
                                     last used by a completed ttb_matmul (which leaves them zero)      */
 

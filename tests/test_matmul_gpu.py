@@ -117,6 +117,31 @@ def test_decode_shapes_of_the_benchmark_configurations(ttb, orc, M, K, N, w_dtyp
     check(y, y_ref)
 
 
+@pytest.mark.parametrize("M,K,N", [(32, 64, 128), (32, 96, 128), (32, 416, 256), (64, 256, 256), (128, 192, 128), (32, 4544, 18176), (32, 4096, 1024)])
+def test_tensor_memory_operand_kernel(ttb, orc, M, K, N):
+    """The bfloat8_b decode kernel that feeds weights to the MMA through tensor memory: same operands, fp32 accumulation,
+    so it must agree with the CUDA-core kernel up to summation order, including rows with exponents above 127."""
+    import torch
+    x, w_dev, w_ref = make_case(ttb, orc, 17, M, K, N, cabi.BFLOAT8_B, w_std=0.02 if K != 96 else 3.0)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y1 = ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, out_fp32=True, flags=cabi.MM_DECODE_TMEM_OPERAND)
+    y2 = ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, out_fp32=True, flags=cabi.MM_FORCE_GENERIC)
+    scale = y2.abs().max().item()
+    assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-4 * scale)
+    check(ttb.untilize(y1, 1, M, N).reshape(M, N), x.float().cuda() @ w_ref.cuda())
+
+
+def test_weights_with_large_magnitudes(ttb, orc):
+    """Rows whose shared exponent exceeds 127 (values of 2 and above) take the second-multiply path of the expanders."""
+    import torch
+    M, K, N = 32, 256, 256
+    for w_dtype in (cabi.BFLOAT8_B, cabi.BFLOAT4_B):
+        x, w_dev, w_ref = make_case(ttb, orc, 23, M, K, N, w_dtype, w_std=40.0)
+        a = ttb.tilize(x.cuda(), 1, M, K)
+        y = ttb.untilize(ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, out_fp32=True), 1, M, N).reshape(M, N)
+        check(y, x.float() @ w_ref)
+
+
 def test_batched_activations_share_the_weight(ttb, orc):
     import torch
     B, M, K, N = 2, 32, 128, 256

@@ -19,8 +19,7 @@
 // Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include <type_traits>
 
-#include "epilogue.cuh"
-#include "sm100_ptx.cuh"
+#include "decode_common.cuh"
 
 namespace ttb {
 
@@ -53,21 +52,8 @@ struct Ab {
     static constexpr int kStages = kGroup * kGroups;
 };
 constexpr int kAStageBytes = BN * BK * 2;       // 8 KiB
-constexpr uint32_t kA_LBO = 2048, kA_SBO = 128;  // A (weights, N-contiguous): K-groups 2 KiB apart, N-groups adjacent
+constexpr uint32_t kA_LBO = 128, kA_SBO = 512;   // A (weights, N-contiguous): the four K-groups of a stage adjacent, N-groups 512 B apart
 constexpr uint32_t kB_LBO = 128, kB_SBO = 512;   // B (activations, K-contiguous): K-groups adjacent, row-groups 512 B apart
-
-struct DecodeArgs {
-    const uint8_t *w;
-    const uint16_t *a;
-    const uint16_t *bias;
-    void *out;
-    float *partial;
-    int *counters;
-    int64_t K, N;
-    int Kt, Nt;
-    int nkb, kb_per_split, splits;
-    int act, out_dtype, a_row_major, out_row_major;
-};
 
 template <int FMT>
 struct Pk {
@@ -139,33 +125,11 @@ __device__ __forceinline__ void expand_row(const uint32_t *codes, uint32_t E, ui
     }
 }
 
-// Global element offset of the 8-element activation chunk (row r, columns k..k+7).
-__device__ __forceinline__ int64_t act_chunk_offset(const DecodeArgs &p, int64_t r, int64_t k) {
-    if (p.a_row_major) return r * p.K + k;
-    return ((r >> 5) * p.Kt + (k >> 5)) * 1024 + 256 * (2 * (int)((r & 31) >> 4) + (int)((k & 31) >> 4)) + 16 * (int)(r & 15) +
-           (int)(k & 15);
-}
-
-template <int NB>
-__device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
-    const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int64_t r = row0 + col0 + j;
-        const float y = apply_activation(v[j] + bias, p.act);
-        const int64_t off = p.out_row_major ? r * p.N + n : tiled_offset(r, n, p.Nt);
-        if (p.out_dtype == TTB_FLOAT32)
-            reinterpret_cast<float *>(p.out)[off] = y;
-        else
-            reinterpret_cast<uint16_t *>(p.out)[off] = f32_to_bf16_bits(y);
-    }
-}
-
 template <int FMT, int NB>
 __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const DecodeArgs p) {
     using L = SmemLayout<FMT, NB>;
     constexpr int TB = Pk<FMT>::kTileBytes;
-    constexpr int kAcc = NB == 32 ? 4 : NB == 64 ? 4 : 2;  // independent accumulators, used round-robin over K steps
+    constexpr int kAcc = BK / 16;  // one accumulator per K step of a stage (two); summed in the epilogue
     constexpr int kTmemCols = NB * kAcc < 32 ? 32 : NB * kAcc;
     constexpr int kAbGroups = Ab<NB>::kGroups;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -223,7 +187,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
             uint32_t ph = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);  // stages in this group (the last one may be short)
-                if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, &g_status_word, 1)) { ok = false; break; }
+                if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
                 mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
                 for (int j = 0; j < r; ++j) {
                     bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
@@ -239,24 +203,28 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
             // descriptors differ between stages and K steps only in the 14-bit start-address field (units of 16 B)
             const uint64_t a_desc0 = smem_desc_noswizzle(sbase + L::a, kA_LBO, kA_SBO);
             const uint64_t b_desc0 = smem_desc_noswizzle(sbase + L::b, kB_LBO, kB_SBO);
-            int gt = 0, acc = 0, steps = 0;
+            // The loop below is one thread's dependent instruction stream, so it is kept short: descriptors are
+            // formed by a 32-bit add into the low word, the accumulator of each K step is fixed at compile time.
+            const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
+            const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+            auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
+            int gt = 0;
             uint32_t ph = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);
                 for (int j = r; j < kGroup; ++j) mbar_arrive(full_ab(gt));  // stand in for the stages a short last group lacks
-                if (!mbar_wait(full_ab(gt), ph, abort_flag, &g_status_word, 2)) { ok = false; break; }
+                if (!mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after_sync();
-                for (int j = 0; j < r; ++j) {
-                    const int t = gt * kGroup + j;
-                    const uint64_t ad = a_desc0 + (uint64_t)((t * kAStageBytes) >> 4);
-                    const uint64_t bd = b_desc0 + (uint64_t)((t * L::kBStageBytes) >> 4);
+                const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4);
+                const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16) {
-                        // consecutive K steps go to different accumulators; each one's first use overwrites
-                        mma_bf16_ss(tmem_base + (uint32_t)(acc * NB), ad + (uint64_t)((k16 * 2 * kA_LBO) >> 4),
-                                    bd + (uint64_t)((k16 * 2 * kB_LBO) >> 4), idesc, steps >= kAcc);
-                        acc = acc + 1 == kAcc ? 0 : acc + 1;
-                        ++steps;
+                for (int j = 0; j < kGroup; ++j) {
+                    if (j < r) {
+#pragma unroll
+                        for (int k16 = 0; k16 < BK / 16; ++k16)
+                            mma_bf16_ss(tmem_base + (uint32_t)(k16 * NB),
+                                        mk(a_lo + ((j * kAStageBytes + k16 * 2 * kA_LBO) >> 4), a_hi),
+                                        mk(b_lo + ((j * L::kBStageBytes + k16 * 2 * kB_LBO) >> 4), b_hi), idesc, j > 0 || g > 0);
                     }
                 }
                 mma_commit(empty_ab(gt));
@@ -291,8 +259,8 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
             const uint32_t phs = (g / kPkGroups) & 1, pht = (g / kAbGroups) & 1;
             int good = 1;
             if (lane == 0)
-                good = mbar_wait(empty_ab(gt), pht ^ 1, abort_flag, &g_status_word, 3) &&
-                       mbar_wait(full_pk(gs), phs, abort_flag, &g_status_word, 4);
+                good = mbar_wait(empty_ab(gt), pht ^ 1, abort_flag, p.status, 3) &&
+                       mbar_wait(full_pk(gs), phs, abort_flag, p.status, 4);
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) { ok = false; break; }
             const uint8_t *pst = smem + L::pk + s * Pk<FMT>::kStageBytes;
@@ -355,7 +323,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         {
             int good = ok ? 1 : 0;
             good = __shfl_sync(0xffffffffu, good, 0);   // lane 0 ran the single-thread roles
-            if (lane == 0 && good && nit > 0) good = mbar_wait(accum_bar, 0, abort_flag, &g_status_word, 5);
+            if (lane == 0 && good && nit > 0) good = mbar_wait(accum_bar, 0, abort_flag, p.status, 5);
             ok = __shfl_sync(0xffffffffu, good, 0) != 0;
         }
         tc_fence_after_sync();
@@ -371,8 +339,8 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                const int nacc = min(kAcc, nit * (BK / 16));  // accumulators that received at least one K step
-                for (int ac = 0; ac < nacc; ++ac) {
+#pragma unroll
+                for (int ac = 0; ac < kAcc; ++ac) {
                     uint32_t r[16];
                     tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ac * NB + col0), r);
                     tmem_ld_wait();
@@ -455,6 +423,23 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
 // The head of the workspace holds one arrival counter per output tile; the partial sums follow.
 static constexpr int64_t kCounterBytes = 65536;
 
+int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, cudaStream_t stream);
+
+// Device address of the status word on the current device (looked up once per device).
+static int32_t status_word_address(int **out) {
+    static int *cached[64] = {};
+    int dev = 0;
+    TTB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 64 || !cached[dev % 64]) {
+        void *ptr = nullptr;
+        TTB_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_status_word));
+        if (dev >= 64) { *out = (int *)ptr; return TTB_OK; }
+        cached[dev] = (int *)ptr;
+    }
+    *out = cached[dev];
+    return TTB_OK;
+}
+
 // Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
 static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32; }
 
@@ -509,6 +494,7 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.partial = nullptr; p.counters = nullptr;
+    if (int32_t rc = status_word_address(&p.status)) return rc;
     if (p.splits > 1) {
         const int64_t need = decode_workspace_bytes(rows, K, N);
         if (!workspace || workspace_bytes < need)
@@ -524,6 +510,7 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     dim3 grid((unsigned)(N / BN), (unsigned)p.splits, (unsigned)(rows / nb));
 #define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, stream)
     if (w_dtype == TTB_BFLOAT8_B) {
+        if (flags & TTB_MM_DECODE_TMEM_OPERAND) return launch_decode_tmem(p, nb, grid, stream);
         if (nb == 32) TTB_DECODE(TTB_BFLOAT8_B, 32);
         if (nb == 64) TTB_DECODE(TTB_BFLOAT8_B, 64);
         TTB_DECODE(TTB_BFLOAT8_B, 128);
