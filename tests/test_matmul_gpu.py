@@ -142,6 +142,63 @@ def test_weights_with_large_magnitudes(ttb, orc):
         check(y, x.float() @ w_ref)
 
 
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
+@pytest.mark.parametrize("M,K,N", [(512, 64, 128), (512, 256, 256), (640, 96, 128), (1024, 160, 384), (2048, 512, 256)])
+def test_prefill_kernel_small_shapes(ttb, orc, w_dtype, M, K, N):
+    """Row counts of 512 and more take the compute-bound tensor-core kernel (one or two 128-row accumulators per block)."""
+    import torch
+    x, w_dev, w_ref = make_case(ttb, orc, 41, M, K, N, w_dtype)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, out_fp32=True)
+    y2 = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, out_fp32=True, flags=cabi.MM_FORCE_GENERIC)
+    assert torch.allclose(y, y2, rtol=1e-4, atol=1e-4 * y2.abs().max().item())
+    check(ttb.untilize(y, 1, M, N).reshape(M, N), x.float() @ w_ref)
+
+
+@pytest.mark.parametrize("act", [cabi.ACT_NONE, cabi.ACT_GELU])
+def test_prefill_kernel_bias_activation_layouts(ttb, orc, act):
+    import torch
+    M, K, N = 512, 128, 256
+    x, w_dev, w_ref = make_case(ttb, orc, 43, M, K, N, cabi.BFLOAT8_B)
+    bias = vectors.randn(78, (N,), 0.5).bfloat16()
+    bias_tile = torch.zeros(32, N, dtype=torch.bfloat16)
+    bias_tile[0] = bias
+    b_dev = ttb.tilize(bias_tile.cuda(), 1, 32, N)
+    y_ref = act_ref(x.float() @ w_ref + bias.float(), act)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y = ttb.untilize(ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, bias=b_dev, act=act), 1, M, N).reshape(M, N)
+    check(y, y_ref)
+    y2 = ttb.matmul(x.cuda().contiguous(), w_dev, cabi.BFLOAT8_B, 1, M, K, N, bias=b_dev, act=act,
+                    flags=cabi.MM_A_ROW_MAJOR | cabi.MM_OUT_ROW_MAJOR).reshape(M, N)
+    check(y2, y_ref)
+    # batch of four 128-row slabs sharing the weight
+    xb = x.reshape(4, 128, K)
+    ab = ttb.tilize(xb.cuda(), 4, 128, K)
+    yb = ttb.untilize(ttb.matmul(ab, w_dev, cabi.BFLOAT8_B, 4, 128, K, N, bias=b_dev, act=act), 4, 128, N).reshape(M, N)
+    check(yb, y_ref)
+
+
+def test_prefill_llama70b_mlp_shape(ttb):
+    """The compute-bound benchmark configuration at full size: [2048, 8192] x bfloat8_b [8192, 28672], seed 3. The weight is
+    packed and unpacked by the GPU kernels (bit-exact with the oracle per the conversion tests); the fp32 golden runs on the GPU."""
+    import torch
+    M, K, N = 2048, 8192, 28672
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(M, K, generator=g, device="cuda").bfloat16()
+    w = torch.randn(K, N, generator=g, device="cuda") * 0.02
+    packed = ttb.pack(w, cabi.BFLOAT8_B, 1, K, N)
+    w_ref = ttb.unpack(packed, cabi.BFLOAT8_B, 1, K, N).reshape(K, N)
+    del w
+    a = ttb.tilize(x, 1, M, K)
+    y = ttb.untilize(ttb.matmul(a, packed, cabi.BFLOAT8_B, 1, M, K, N), 1, M, N).reshape(M, N).float()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    y_ref = x.float() @ w_ref
+    rel = ((y - y_ref).abs().max() / y_ref.abs().max()).item()
+    sample = torch.randint(0, M * N, (2_000_000,), device="cuda")
+    pcc = oracle.comp_pcc(y_ref.reshape(-1)[sample].cpu().numpy(), y.reshape(-1)[sample].cpu().numpy())
+    assert rel <= MAX_REL and pcc >= PCC_MIN, (rel, pcc)
+
+
 def test_batched_activations_share_the_weight(ttb, orc):
     import torch
     B, M, K, N = 2, 32, 128, 256

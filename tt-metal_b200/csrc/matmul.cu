@@ -12,6 +12,12 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
                              int64_t workspace_bytes, bool counters_are_zero, cudaStream_t stream);
 int32_t read_and_clear_status(cudaStream_t stream);
+int32_t status_word_address(int **out);
+bool prefill_supported(int w_dtype, int64_t rows, int64_t K, int64_t N);
+int64_t prefill_workspace_bytes(int64_t rows, int64_t K);
+int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype, int64_t rows,
+                              int64_t K, int64_t N, int act, int flags, void *workspace, int64_t workspace_bytes, int *status,
+                              cudaStream_t stream);
 
 namespace {
 
@@ -53,7 +59,9 @@ extern "C" {
 
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags) {
     const int64_t rows = batch * M;
-    if (!(flags & TTB_MM_FORCE_GENERIC) && decode_supported(w_dtype, rows, K, N)) return decode_workspace_bytes(rows, K, N);
+    if (flags & TTB_MM_FORCE_GENERIC) return 0;
+    if (decode_supported(w_dtype, rows, K, N)) return decode_workspace_bytes(rows, K, N);
+    if (prefill_supported(w_dtype, rows, K, N)) return prefill_workspace_bytes(rows, K);
     return 0;
 }
 
@@ -66,6 +74,11 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
     if (!(flags & TTB_MM_FORCE_GENERIC) && decode_supported(w_dtype, rows, K, N))
         return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes,
                                     (flags & TTB_MM_WORKSPACE_ZEROED) != 0, s);
+    if (!(flags & TTB_MM_FORCE_GENERIC) && prefill_supported(w_dtype, rows, K, N)) {
+        int *status = nullptr;
+        if (int32_t rc = status_word_address(&status)) return rc;
+        return launch_matmul_prefill(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes, status, s);
+    }
     return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
 }
 

@@ -426,7 +426,7 @@ static constexpr int64_t kCounterBytes = 65536;
 int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, cudaStream_t stream);
 
 // Device address of the status word on the current device (looked up once per device).
-static int32_t status_word_address(int **out) {
+int32_t status_word_address(int **out) {
     static int *cached[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));

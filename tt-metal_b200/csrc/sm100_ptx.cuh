@@ -77,6 +77,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src_gmem
         : "memory");
 }
 
+// Same without a cache hint (data that other blocks will read again from L2).
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst_smem, const void *src_gmem, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src_gmem), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // ---- tensor memory -------------------------------------------------------------------------------
 // Whole-warp calls. `ncols` is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
