@@ -139,6 +139,26 @@ int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_
                    void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
                    int32_t activation, int32_t flags, void *workspace_dev, int64_t workspace_bytes, void *stream);
 
+/* Decode matmul for callers that cannot allocate device memory.
+ * This entry point has no counterpart in the reference. It computes exactly what ttb_matmul computes for the decode
+ * shapes (bfloat16 activations of at most 256 rows in total, bfloat8_b / bfloat4_b weights, N a multiple of 128), but
+ * takes no workspace: the scratch the split-K reduction needs is a fixed array inside the library's device image
+ * (16 MiB + 64 KiB, resident on every GPU that loads the library, for the life of the process). It is meant for
+ * code that runs where cudaMalloc is off limits - inside a serving loop that has handed all device memory to its own
+ * pool, in a callback of another runtime, or in any path that must not trigger the implicit synchronisation
+ * of an allocation. The call itself performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - Shapes whose reduction needs more scratch than the array holds are refused with TTB_E_WORKSPACE, other
+ *     shapes than the decode ones with TTB_E_UNSUPPORTED; both point to ttb_matmul.
+ *   - The first call on each device looks up the array's device address (and sets the kernel's shared-memory
+ *     limit); make that first call outside any stream capture.
+ *   - All calls share the one array, which keeps the previous call's contents; the part that must start at zero is
+ *     cleared on `stream` by each call. Two calls that overlap on the GPU (different streams, no dependency) race on
+ *     it: serialise them.
+ * `flags` accepts TTB_MM_A_ROW_MAJOR and TTB_MM_OUT_ROW_MAJOR. */
+int32_t ttb_matmul_decode_static(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
+                                 void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                                 int32_t activation, int32_t flags, void *stream);
+
 /* Reads (and clears) the device-side status word that kernels with bounded waits set when a wait
  * ran out. Synchronises `stream`. Returns TTB_OK or TTB_E_TIMEOUT. */
 int32_t ttb_check_status(void *stream);

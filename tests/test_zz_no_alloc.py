@@ -1,0 +1,70 @@
+"""The allocation-free decode entry point (ttb_matmul_decode_static) against the regular one.
+
+Some callers cannot call cudaMalloc at the point where they need a matmul: an inference server that gave all device
+memory to its own pool at start-up, or code running inside another runtime's callback where an allocation would
+synchronise the device. For them the library carries its split-K scratch as a fixed device array. This file checks, through
+the C ABI, that the variant produces what ttb_matmul produces - on two calls in a row, because the scratch is shared
+between calls and keeps the previous call's contents - and that it refuses what it cannot serve. It is collected last so
+that a run stopping at the first failure has already run every other test; it also passes when run alone."""
+import pytest
+
+import cabi
+import vectors
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(ttb, M, K, N, w_dtype, seed):
+    import torch
+    x = vectors.randn(seed, (M, K), 1.0).bfloat16().cuda()
+    w = (vectors.randn(seed + 1, (K, N), 0.02)).cuda()
+    packed = ttb.pack(w, w_dtype, 1, K, N)
+    return ttb.tilize(x, 1, M, K), packed
+
+
+def _static(ttb, a, w, w_dtype, M, K, N, out_fp32=True):
+    import torch
+    out = torch.empty(M * N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device="cuda")
+    ttb.check(ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), w_dtype, None, out.data_ptr(),
+                                                cabi.FLOAT32 if out_fp32 else cabi.BFLOAT16, 1, M, K, N, 0, 0, None))
+    ttb.check(ttb.check_status(None))
+    return out
+
+
+@pytest.mark.parametrize("M,K,N,w_dtype", [(32, 4096, 1024, cabi.BFLOAT8_B),     # K split over many blocks: uses the scratch
+                                           (32, 4096, 4096, cabi.BFLOAT8_B),
+                                           (64, 2048, 512, cabi.BFLOAT4_B),
+                                           (32, 256, 18176, cabi.BFLOAT8_B)])    # one block per tile: no scratch needed
+def test_static_scratch_variant_matches_regular_entry_point_twice_in_a_row(ttb, M, K, N, w_dtype):
+    import torch
+    assert (ttb.matmul_workspace_bytes(w_dtype, 1, M, K, N, 0) > 0) == (N < 18176)
+    a, w = _operands(ttb, M, K, N, w_dtype, 51)
+    want = ttb.matmul(a, w, w_dtype, 1, M, K, N, out_fp32=True)
+    first = _static(ttb, a, w, w_dtype, M, K, N)
+    # a different problem in between leaves its own partial sums in the shared scratch
+    a2, w2 = _operands(ttb, 32, 2048, 256, cabi.BFLOAT8_B, 61)
+    _static(ttb, a2, w2, cabi.BFLOAT8_B, 32, 2048, 256)
+    second = _static(ttb, a, w, w_dtype, M, K, N)
+    scale = want.abs().max().item()
+    for got in (first, second):
+        # same kernel, same fixed reduction order: the tolerance of the kernel-agreement tests is far from needed
+        assert torch.allclose(got, want, rtol=1e-4, atol=1e-4 * scale)
+    assert torch.equal(first, second)
+
+
+def test_static_scratch_variant_refuses_what_it_cannot_serve(ttb):
+    import torch
+    a, w = _operands(ttb, 32, 256, 128, cabi.BFLOAT8_B, 71)
+    out = torch.empty(32 * 128, dtype=torch.bfloat16, device="cuda")
+    # prefill-sized row count: not a decode shape
+    rc = ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
+                                           1, 512, 256, 128, 0, 0, None)
+    assert rc == -3 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
+    # a reduction that would need more scratch than the built-in array (checked before anything is launched)
+    rc = ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
+                                           1, 256, 28672, 8192, 0, 0, None)
+    assert ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, 256, 28672, 8192, 0) > (16 << 20) + 65536
+    assert rc == -4 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
+    rc = ttb.cdll.ttb_matmul_decode_static(None, cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
+                                           1, 32, 256, 128, 0, 0, None)
+    assert rc == -1

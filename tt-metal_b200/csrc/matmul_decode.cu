@@ -535,3 +535,53 @@ int32_t read_and_clear_status(cudaStream_t stream) {
 }
 
 }  // namespace ttb
+
+// ---- decode matmul for callers that must not allocate ---------------------------------------------------------------
+// Scratch for the split-K reduction lives in this library's own device image instead of a caller-provided buffer.
+// Every GPU that loads the library holds these bytes until the process exits.
+#define TTB_STATIC_SCRATCH_BYTES (65536 + (16 << 20))
+static __device__ __align__(256) unsigned char g_static_scratch[TTB_STATIC_SCRATCH_BYTES];
+
+extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, const void *bias,
+                                            void *out, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                                            int32_t act, int32_t flags, void *stream) {
+    using namespace ttb;
+    if (!a || !w || !out) return fail(TTB_E_INVALID, "ttb_matmul_decode_static: null tensor pointer");
+    if (a_dtype != TTB_BFLOAT16) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_decode_static: activations must be bfloat16");
+    if (out_dtype != TTB_BFLOAT16 && out_dtype != TTB_FLOAT32)
+        return fail(TTB_E_UNSUPPORTED, "ttb_matmul_decode_static: output must be bfloat16 or float32");
+    if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || M % 32 || K % 32 || N % 32)
+        return fail(TTB_E_INVALID, "ttb_matmul_decode_static: batch, M, K, N must be positive and M, K, N multiples of 32");
+    if (act < TTB_ACT_NONE || act > TTB_ACT_SILU) return fail(TTB_E_INVALID, "ttb_matmul_decode_static: unknown activation %d", act);
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(TTB_E_INVALID, "ttb_matmul_decode_static: tensors must be 16-byte aligned");
+    const int64_t rows = batch * M;
+    if (!decode_supported(w_dtype, rows, K, N))
+        return fail(TTB_E_UNSUPPORTED,
+                    "ttb_matmul_decode_static: only the decode shapes are served without allocation (bfloat8_b / bfloat4_b weights, "
+                    "at most 256 rows, N a multiple of 128); use ttb_matmul for [%lld x %lld x %lld]",
+                    (long long)rows, (long long)K, (long long)N);
+    const int64_t need = decode_workspace_bytes(rows, K, N);
+    if (need > (int64_t)TTB_STATIC_SCRATCH_BYTES)
+        return fail(TTB_E_WORKSPACE,
+                    "ttb_matmul_decode_static: this shape needs %lld bytes of scratch, the built-in scratch holds %lld; use ttb_matmul "
+                    "with a caller-provided workspace",
+                    (long long)need, (long long)TTB_STATIC_SCRATCH_BYTES);
+    // Set-up, once per device, with that device current: the array's name is only a host-side handle here, the kernel
+    // needs the device address the runtime maps it to.
+    static void *scratch_addr[64] = {};
+    int dev = 0;
+    TTB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_decode_static: device index %d is out of range", dev);
+    if (!scratch_addr[dev]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(TTB_E_CUDA, "ttb_matmul_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        scratch_addr[dev] = ptr;
+    }
+    // The array keeps whatever the previous call left. Only the arrival counters at its head must start at zero
+    // (launch_matmul_decode clears them on the stream); the partial sums are fully rewritten before they are read.
+    return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR),
+                                need > 0 ? scratch_addr[dev] : nullptr, need, /*counters_are_zero=*/false, (cudaStream_t)stream);
+}
