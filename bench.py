@@ -48,6 +48,7 @@ class Workload:
 
     def __init__(self, key, G):
         self.key = key
+        self.rows = BATCH
         if key == "c5":
             self.metric, self.unit, self.text = METRIC, "tok/s", WORKLOAD
             self.layers = LAYERS
@@ -69,6 +70,14 @@ class Workload:
             self.layers = 4
             self.gemms = [("h_to_4h", 4544, 18176, BFP8, False)]
             self.seed = 1
+        elif key == "c4":
+            self.metric, self.unit = "prefill GEMM bf16 TFLOP/s (Llama-2-70B MLP shape, bfloat8_b weight)", "TFLOP/s"
+            self.text = ("prefill matmul, Llama-2-70B MLP shape: activation bf16 [2048, 8192] x weight bfloat8_b [8192, 28672], fp32 "
+                         "accumulate, bf16 output; 2 distinct weights used in rotation")
+            self.layers = 2
+            self.rows = 2048
+            self.gemms = [("w1", 8192, 28672, BFP8, False)]
+            self.seed = 3
         else:
             raise SystemExit(f"unknown workload {key}")
         if key != "c5" and G != 1:
@@ -76,18 +85,22 @@ class Workload:
 
     def bytes_per_layer(self):
         """Algorithmic bytes: packed weight + bf16 activations read + bf16 outputs written."""
-        return sum(K * N // 1024 * TILE_BYTES[f] + BATCH * K * 2 + BATCH * N * 2 for _, K, N, f, _ in self.gemms)
+        return sum(K * N // 1024 * TILE_BYTES[f] + self.rows * K * 2 + self.rows * N * 2 for _, K, N, f, _ in self.gemms)
+
+    def flops_per_layer(self):
+        return sum(2 * self.rows * K * N for _, K, N, _, _ in self.gemms)
 
     def weight_bytes_per_layer(self):
         return sum(K * N // 1024 * TILE_BYTES[f] for _, K, N, f, _ in self.gemms)
 
 
-def peaks():
+def peaks(key="hbm_gbs"):
+    """Roofline denominators measured on this pool's B200s (driver-written file), else the stated fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            return float(json.load(f)[key]), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}[key], "fallback"
 
 
 class ClockSampler:
@@ -101,7 +114,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -110,7 +123,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def mark(self, name):
+        """Remembers the wall-clock time of `name` ("start" / "end" of the timed region)."""
+        setattr(self, "t_" + name, time.time())
 
     def __exit__(self, *a):
         if self.proc:
@@ -123,7 +140,11 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        t0, t1 = getattr(self, "t_start", 0.0), getattr(self, "t_end", float("inf"))
+        inside = [r for t, r in self.rows if t0 <= t <= t1 + 0.02]
+        # a timed region shorter than a few sampling periods: fall back to the samples of the identical warm-up replays
+        rows = inside if len(inside) >= 3 else [r for t, r in self.rows if t >= getattr(self, "t_load", 0.0)]
+        for r in rows:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except (ValueError, IndexError):
@@ -133,7 +154,8 @@ class ClockSampler:
                     reasons.add(n)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "window": "timed region" if len(inside) >= 3 else "warm-up replays + timed region"}
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -247,6 +269,7 @@ def run_gpu_arm(args):
     gen = torch.Generator(device=dev_t).manual_seed(wl.seed + 1000 * rank)
     gemms = wl.gemms
     NLAYERS = wl.layers
+    ROWS = wl.rows
     weights = []          # [layer][gemm] -> packed uint8 tensor
     t_setup = time.perf_counter()
     for _ in range(NLAYERS):
@@ -263,25 +286,25 @@ def run_gpu_arm(args):
 
     # ---- activations (tiled bf16), outputs, gather buffers, workspace ------------------------------------------
     def tiled_act(K, seed):
-        x = torch.randn(BATCH, K, generator=torch.Generator().manual_seed(seed)).bfloat16()
+        x = torch.randn(ROWS, K, generator=torch.Generator().manual_seed(seed)).bfloat16()
         xd = x.to(dev_t)
-        out = torch.empty(BATCH * K, dtype=torch.bfloat16, device=dev_t)
-        ck(lib.ttb_tilize(xd.data_ptr(), out.data_ptr(), 2, 1, BATCH, K, None))
+        out = torch.empty(ROWS * K, dtype=torch.bfloat16, device=dev_t)
+        ck(lib.ttb_tilize(xd.data_ptr(), out.data_ptr(), 2, 1, ROWS, K, None))
         return x, out
     acts = {}             # K -> (host bf16 [32, K], tiled device copy): a fresh N(0,1) activation per distinct K
     for _, K, _, _, _ in gemms:
         if K not in acts:
             acts[K] = tiled_act(K, 40 + len(acts))
-    outs = [torch.empty(BATCH * N, dtype=torch.bfloat16, device=dev_t) for _, _, N, _, _ in gemms]
-    gathered = [torch.empty(G * BATCH * N, dtype=torch.bfloat16, device=dev_t) if g else None for _, _, N, _, g in gemms]
-    ws_bytes = max(lib.ttb_matmul_workspace_bytes(f, 1, BATCH, K, N, 0) for _, K, N, f, _ in gemms)
+    outs = [torch.empty(ROWS * N, dtype=torch.bfloat16, device=dev_t) for _, _, N, _, _ in gemms]
+    gathered = [torch.empty(G * ROWS * N, dtype=torch.bfloat16, device=dev_t) if g else None for _, _, N, _, g in gemms]
+    ws_bytes = max(lib.ttb_matmul_workspace_bytes(f, 1, ROWS, K, N, 0) for _, K, N, f, _ in gemms)
     ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=dev_t)
 
     def sweep(stream_handle, with_gather=True):
         for layer in range(NLAYERS):
             for i, (_, K, N, fmt, g) in enumerate(gemms):
                 a = acts[K][1]
-                ck(lib.ttb_matmul(a.data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16, 1, BATCH, K, N,
+                ck(lib.ttb_matmul(a.data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16, 1, ROWS, K, N,
                                   0, ZEROED, ws.data_ptr(), ws_bytes, stream_handle))
                 if g and G > 1 and with_gather:
                     # tiled [32, N/G] shards are whole tile runs: the rank-major gather is the tiled [32, N] tensor
@@ -304,16 +327,22 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_replays(graph, steps, warmup):
+    def timed_replays(graph, steps, warmup, sampler=None):
+        if sampler:
+            sampler.mark("load")
         for _ in range(warmup):
             graph.replay()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.mark("start")
         e0.record()
         for _ in range(steps):
             graph.replay()
         e1.record()
         barrier()
+        if sampler:
+            sampler.mark("end")
         ms = e0.elapsed_time(e1)
         if G > 1:
             t = torch.tensor([ms], device=dev_t)
@@ -321,9 +350,9 @@ def run_gpu_arm(args):
             ms = t.item()
         return ms
 
-    graph_full = capture(True)
     with ClockSampler(local_rank) as clocks:
-        ms_total = timed_replays(graph_full, args.steps, args.warmup)
+        graph_full = capture(True)      # also gives nvidia-smi time to start sampling
+        ms_total = timed_replays(graph_full, args.steps, args.warmup, clocks)
     ms_step = ms_total / args.steps
 
     # ---- roofline of the dominant kernel: the matmul-only sweep (no collectives), same weights -------------------
@@ -335,9 +364,20 @@ def run_gpu_arm(args):
     launches_per_step = NLAYERS * len(gemms)
     bytes_per_step = wl.bytes_per_layer() * NLAYERS
     achieved = bytes_per_step / (ms_mm * 1e-3) / 1e9
-    to_value = (lambda sec: BATCH / sec) if wl.unit == "tok/s" else (lambda sec: bytes_per_step / sec / 1e9)
+    flops_per_step = wl.flops_per_layer() * NLAYERS
+    if wl.unit == "tok/s":
+        to_value = lambda sec: BATCH / sec
+    elif wl.unit == "TFLOP/s":
+        to_value = lambda sec: flops_per_step / sec / 1e12
+    else:
+        to_value = lambda sec: bytes_per_step / sec / 1e9
     value = to_value(ms_step * 1e-3)
-    peak, peak_kind = peaks()
+    tensor_bound = wl.unit == "TFLOP/s"
+    if tensor_bound:
+        achieved = flops_per_step / (ms_mm * 1e-3) / 1e12
+        peak, peak_kind = peaks("bf16_tflops")
+    else:
+        peak, peak_kind = peaks("hbm_gbs")
     ck(lib.ttb_check_status(None))
 
     # ---- end to end through the public API: host activations in, result out, every step -------------------------
@@ -348,7 +388,7 @@ def run_gpu_arm(args):
     pinned = {K: v[0].pin_memory() for K, v in acts.items()}
     h2d = sum(p.numel() * 2 for p in pinned.values())
     last_n = gemms[-1][2] * (G if gemms[-1][4] else 1)
-    d2h = BATCH * last_n * 2
+    d2h = ROWS * last_n * 2
 
     def e2e_step():
         a = {K: ttnn.from_torch(p, layout=ttnn.TILE_LAYOUT, device=device) for K, p in pinned.items()}
@@ -374,7 +414,7 @@ def run_gpu_arm(args):
         t = torch.tensor([e2e_s], device=dev_t, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = t.item()
-    assert res.shape == (BATCH, last_n) and bool(torch.isfinite(res.float()).all())
+    assert res.shape == (ROWS, last_n) and bool(torch.isfinite(res.float()).all())
 
     line = {
         "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
@@ -386,9 +426,10 @@ def run_gpu_arm(args):
         "e2e": {"value": to_value(e2e_s), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3,
                 "api": f"ttnn.from_torch -> ttnn.linear x{launches_per_step} (+ ttnn.all_gather) -> ttnn.to_torch"},
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "matmul_decode_kernel",
+        "gpu_launches": launches_per_step * (2 if tensor_bound else 1) * args.steps,
+        "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s" if tensor_bound else "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "matmul_prefill_kernel" if tensor_bound else "matmul_decode_kernel",
                      "launches_per_step": launches_per_step, "algorithmic_bytes_per_step": bytes_per_step,
                      "avg_launch_us": ms_mm * 1e3 / launches_per_step},
     }
@@ -417,8 +458,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="c5", choices=["c5", "c3", "c2"],
-                    help="c5 = Llama-2-70B TP decode sweep (default, the headline), c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")
+    ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
+                    help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "
+                         "c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -153,7 +153,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntile = blockIdx.x, mblock = blockIdx.y;
+    // row blocks vary fastest across the grid: the blocks that share a weight column block run together, so the packed
+    // tiles are read from HBM once and served to the other row blocks from L2
+    const int mblock = blockIdx.x, ntile = blockIdx.y;
     const int nit = p.nkb;
     const int ngroups = (nit + kGroup - 1) / kGroup;
 
@@ -187,7 +189,6 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles and activation blocks -> shared memory ----------------
         if (lane == 0) {
-            const uint64_t policy = l2_policy_evict_first();
             const uint8_t *wsrc = p.w + (int64_t)ntile * 4 * TB;
             const int64_t w_step = (int64_t)p.Nt * TB;
             const uint8_t *xsrc = p.x + (int64_t)mblock * p.nkb * L::kActStageBytes;
@@ -203,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
                 if (!mbar_wait(empty_pk(gs), phs ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
                 mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
                 for (int j = 0; j < r; ++j) {
-                    bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, wsrc, 4 * TB, full_pk(gs), policy);
+                    bulk_g2s_plain(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, wsrc, 4 * TB, full_pk(gs));
                     wsrc += w_step;
                 }
                 if (++gs == kPkGroups) { gs = 0; phs ^= 1; }
@@ -393,7 +394,7 @@ int32_t launch_one(const PrefillArgs &p, dim3 grid, cudaStream_t stream) {
 
 bool prefill_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows >= 512 && rows % BMS == 0 && K % BK == 0 && N % BN == 0 &&
-           rows / BMS <= 65535;
+           N / BN <= 65535;
 }
 
 // Scratch for the re-laid activations.
@@ -421,7 +422,7 @@ int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const v
     p.K = K; p.N = N; p.rows = rows; p.Nt = (int)(N / 32); p.nkb = (int)(K / BK);
     p.act = act; p.out_dtype = out_dtype; p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.status = status;
-    dim3 grid((unsigned)(N / BN), (unsigned)(rows / (BMS * R)));
+    dim3 grid((unsigned)(rows / (BMS * R)), (unsigned)(N / BN));
     if (w_dtype == TTB_BFLOAT8_B) return R == 2 ? launch_one<TTB_BFLOAT8_B, 2>(p, grid, stream) : launch_one<TTB_BFLOAT8_B, 1>(p, grid, stream);
     return R == 2 ? launch_one<TTB_BFLOAT4_B, 2>(p, grid, stream) : launch_one<TTB_BFLOAT4_B, 1>(p, grid, stream);
 }
