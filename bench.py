@@ -447,8 +447,16 @@ def run_gpu_arm(args):
                                               f"host bfloat8_b packing of one 8192x1024 weight: {t_pack:.2f} s = {pack_gbs:.3f} GB/s on 1 thread"}
         print(json.dumps(line), flush=True)
     if G > 1:
+        # Release the captured graphs (they hold NCCL kernels) before the communicator goes away, then leave without the
+        # interpreter's teardown: destroying a communicator that captured graphs still reference can block forever.
+        del graph_full
+        if "graph_mm" in locals():
+            del graph_mm
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -461,7 +469,15 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
                     help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "
                          "c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")
+    ap.add_argument("--max-seconds", type=int, default=1500, help="watchdog: the process exits with status 3 after this long")
     args = ap.parse_args()
+
+    def _watchdog():
+        time.sleep(args.max_seconds)
+        sys.stderr.write(f"bench.py: watchdog fired after {args.max_seconds} s\n")
+        sys.stderr.flush()
+        os._exit(3)
+    threading.Thread(target=_watchdog, daemon=True).start()
     if args.impl == "reference":
         run_reference_arm(args)
     else:
