@@ -27,19 +27,28 @@ __device__ __forceinline__ int64_t act_chunk_offset(const DecodeArgs &p, int64_t
            (int)(k & 15);
 }
 
+// Bias, activation and store of 16 consecutive rows (row0 + col0 .. + 15, col0 a multiple of 16) of output column n.
+// In the tiled layout those 16 elements sit 16 apart inside one face, in the row-major layout N apart.
+template <int ACT>
+__device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
+    const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
+    const int64_t r0 = row0 + col0;
+    const int64_t base = p.out_row_major ? r0 * p.N + n : tiled_offset(r0, n, p.Nt);
+    const int64_t stride = p.out_row_major ? p.N : 16;
+    if (p.out_dtype == TTB_FLOAT32) {
+        float *o = reinterpret_cast<float *>(p.out) + base;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j * stride] = apply_activation_t<ACT>(v[j] + bias);
+    } else {
+        uint16_t *o = reinterpret_cast<uint16_t *>(p.out) + base;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j * stride] = f32_to_bf16_bits(apply_activation_t<ACT>(v[j] + bias));
+    }
+}
+
 template <int NB>
 __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
-    const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const int64_t r = row0 + col0 + j;
-        const float y = apply_activation(v[j] + bias, p.act);
-        const int64_t off = p.out_row_major ? r * p.N + n : tiled_offset(r, n, p.Nt);
-        if (p.out_dtype == TTB_FLOAT32)
-            reinterpret_cast<float *>(p.out)[off] = y;
-        else
-            reinterpret_cast<uint16_t *>(p.out)[off] = f32_to_bf16_bits(y);
-    }
+    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, v, row0, col0, n));
 }
 
 }  // namespace ttb

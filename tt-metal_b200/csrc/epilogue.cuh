@@ -16,6 +16,23 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
     }
 }
 
+// Same with the activation known at compile time. Epilogues branch on the activation once, outside their element
+// loops: a runtime switch inside the loop makes the compiler evaluate erf, exp and the division for every element.
+template <int ACT>
+__device__ __forceinline__ float apply_activation_t(float v) {
+    if (ACT == TTB_ACT_RELU) return fmaxf(v, 0.0f);
+    if (ACT == TTB_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    if (ACT == TTB_ACT_SILU) return v / (1.0f + __expf(-v));
+    return v;
+}
+#define TTB_DISPATCH_ACT(act, CALL)                         \
+    switch (act) {                                          \
+        case TTB_ACT_RELU: { constexpr int ACT = TTB_ACT_RELU; CALL; break; } \
+        case TTB_ACT_GELU: { constexpr int ACT = TTB_ACT_GELU; CALL; break; } \
+        case TTB_ACT_SILU: { constexpr int ACT = TTB_ACT_SILU; CALL; break; } \
+        default: { constexpr int ACT = TTB_ACT_NONE; CALL; break; }           \
+    }
+
 // Element offset of (row r, column c) inside a tiled 2-D slab with Wt tiles per tile row.
 __device__ __forceinline__ int64_t tiled_offset(int64_t r, int64_t c, int64_t Wt) {
     const int64_t tile = (r >> 5) * Wt + (c >> 5);

@@ -31,13 +31,13 @@ using namespace ptx;
 
 constexpr int BN = 128;           // weight columns per block (UMMA M)
 constexpr int BK = 32;            // K per pipeline stage (one row of four tiles)
-// Twelve warps. A warp's scheduler is warp % 4: the two single-thread roles (warp 0 producer, warp 4 MMA issuer)
-// and an idle warp 8 share scheduler 0, so the MMA issuer never competes with expand warps for issue slots.
+// Twelve warps. A warp's scheduler is warp % 4: the single-thread roles (warp 0 producer, warps 4 and 8 MMA issuers)
+// share scheduler 0, so the MMA issuers never compete with expand warps for issue slots.
 // The nine warps with warp % 4 != 0 expand; warps 0..7 run the epilogue (TMEM lane quadrant = warp % 4).
 constexpr int kWarps = 12;
 constexpr int kThreadsDecode = 32 * kWarps;
 constexpr int kExpandWarps = 9;
-constexpr int kProducerWarp = 0, kMmaWarp = 4;
+constexpr int kProducerWarp = 0, kMmaWarp = 4, kMmaWarp2 = 8;
 constexpr int kEpilogueThreads = 256;
 // Stages are handled in groups of three consecutive K-blocks, one per warp of an expand-warp triplet, with one
 // mbarrier per group: the producer and the MMA issuer then pay their per-iteration latencies (barrier wait,
@@ -160,9 +160,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         }
         for (int s = 0; s < kAbGroups; ++s) {
             mbar_init(full_ab(s), kGroup);
-            mbar_init(empty_ab(s), 1);
+            mbar_init(empty_ab(s), 2);   // one commit from each of the two MMA issuers
         }
-        mbar_init(accum_bar, 1);
+        mbar_init(accum_bar, 2);
         *abort_flag = 0;
         *last_flag = 0;
         fence_mbar_init();
@@ -196,8 +196,10 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                 if (++gs == kPkGroups) { gs = 0; ph ^= 1; }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == kMmaWarp || warp == kMmaWarp2) {
+        // ---------------- MMA issuers: warp 4 issues the first K step of every stage (accumulator 0), warp 8 the second
+        // (accumulator 1). The two instruction streams are independent, which doubles the rate at which MMAs are issued.
+        const int k16 = warp == kMmaWarp ? 0 : 1;
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/true, /*b_mn_major=*/false);
             // descriptors differ between stages and K steps only in the 14-bit start-address field (units of 16 B)
@@ -208,24 +210,22 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
             const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
+            const uint32_t d_tmem = tmem_base + (uint32_t)(k16 * NB);
             int gt = 0;
             uint32_t ph = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);
-                for (int j = r; j < kGroup; ++j) mbar_arrive(full_ab(gt));  // stand in for the stages a short last group lacks
+                if (k16 == 0)
+                    for (int j = r; j < kGroup; ++j) mbar_arrive(full_ab(gt));  // stand in for the stages a short last group lacks
                 if (!mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4);
-                const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4);
+                const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4) + (uint32_t)k16 * ((2 * kA_LBO) >> 4);
+                const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4) + (uint32_t)k16 * ((2 * kB_LBO) >> 4);
 #pragma unroll
                 for (int j = 0; j < kGroup; ++j) {
-                    if (j < r) {
-#pragma unroll
-                        for (int k16 = 0; k16 < BK / 16; ++k16)
-                            mma_bf16_ss(tmem_base + (uint32_t)(k16 * NB),
-                                        mk(a_lo + ((j * kAStageBytes + k16 * 2 * kA_LBO) >> 4), a_hi),
-                                        mk(b_lo + ((j * L::kBStageBytes + k16 * 2 * kB_LBO) >> 4), b_hi), idesc, j > 0 || g > 0);
-                    }
+                    if (j < r)
+                        mma_bf16_ss(d_tmem, mk(a_lo + ((j * kAStageBytes) >> 4), a_hi), mk(b_lo + ((j * L::kBStageBytes) >> 4), b_hi), idesc,
+                                    j > 0 || g > 0);
                 }
                 mma_commit(empty_ab(gt));
                 if (++gt == kAbGroups) { gt = 0; ph ^= 1; }
@@ -371,13 +371,25 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float4 *src = reinterpret_cast<const float4 *>(
-                            p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+                    // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
+                    for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                        float4 x[4][4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float4 x = __ldcg(src + j);
-                            v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                        for (int u = 0; u < 4; ++u) {
+                            const int sp = min(sp0 + u, p.splits - 1);
+                            const float4 *src = reinterpret_cast<const float4 *>(
+                                p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (sp0 + u < p.splits) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                                }
+                            }
                         }
                     }
                     finish_and_store<NB>(p, v, row0, col0, n);
@@ -460,12 +472,14 @@ void decode_plan(int64_t rows, int64_t K, int64_t N, int *splits_out, int *kb_pe
         const int kbps = (nkb + s - 1) / s;
         const int real_s = (nkb + kbps - 1) / kbps;
         if (real_s != s) continue;
-        if (s > 1 && kbps < 8) break;
+        if (s > 1 && kbps < 16) break;
         const int blocks = tiles * s;
         const int waves = (blocks + sms - 1) / sms;
         // time model in units of one K-block: each wave costs its blocks' K-blocks plus a fixed fill/drain
         // overhead; split partials add a small reduction cost.
-        const double cost = waves * (kbps + 16.0) + (s > 1 ? 2.0 + 0.5 * s : 0.0);
+        // in units of one K-block's streaming time (~0.16 us): a wave costs ~4 us to fill and drain, the last block of a
+        // tile spends ~0.25 us per partial on the reduction
+        const double cost = waves * (kbps + 25.0) + (s > 1 ? 6.0 + 1.5 * s : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     const int kbps = (nkb + best_s - 1) / best_s;

@@ -17,8 +17,9 @@
 //   * tcgen05.st.16x256b has exactly the fragment layout ldmatrix produced, so the expanded registers go to tensor
 //     memory without any shuffle; tcgen05.mma then takes A from tensor memory and the activations (B) from shared memory.
 // A warp can only write the 32 TMEM lanes of its quadrant (warp % 4), i.e. one tile column of the 128-wide block, so
-// the twelve expand warps form three sets of four: set s expands K-block 3g + s of every group g of three K-blocks.
-// One mbarrier per group keeps the producer thread and the MMA-issuing thread to one wait / commit per three stages.
+// the twelve expand warps form three teams of four (one warp per quadrant): team t expands every third group of three
+// K-blocks, all three stages in one turn. One mbarrier per group keeps the producer thread, the MMA-issuing thread and
+// the expand warps to one wait / commit / arrival per three stages.
 // Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include "decode_common.cuh"
 
@@ -118,10 +119,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPkGroups; ++s) {
             mbar_init(full_pk(s), 1);
-            mbar_init(empty_pk(s), kExpandWarps);
+            mbar_init(empty_pk(s), 4);
         }
         for (int s = 0; s < kAGroups; ++s) {
-            mbar_init(full_a(s), kExpandWarps);
+            mbar_init(full_a(s), 4);
             mbar_init(empty_a(s), 1);
         }
         mbar_init(accum_bar, 1);
@@ -169,8 +170,6 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
             uint32_t ph = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kSets, nit - g * kSets);
-                // a short last group lacks the arrivals of the sets that have no stage in it
-                for (int j = r * 4; j < kExpandWarps; ++j) mbar_arrive(full_a(ga));
                 if (!mbar_wait(full_a(ga), ph, abort_flag, p.status, 12)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t a_col = tmem_base + (uint32_t)(L::kACol0 + ga * kSets * kAColsPerStage);
@@ -191,25 +190,32 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
         }
     } else {
         // ---------------- expand warps: packed codes -> bf16 in tensor memory; activations -> shared memory ----------------
-        const int set = warp >> 2, quad = warp & 3;
+        // Team warp / 4 (four warps, one per TMEM lane quadrant = tile column) takes every third group and expands all
+        // of its stages in one turn, so the per-turn costs (barrier polls, fences, arrivals) are paid once per three stages.
+        const int team = warp >> 2, quad = warp & 3;
         constexpr int kActChunks = NB / 32;  // 16-byte activation chunks per lane per stage (NB rows x 4 chunks over 4 warps)
-        uint4 act_regs[kActChunks];
-        auto load_act = [&](int it) {
+        uint4 act_regs[kSets][kActChunks];
+        auto load_act = [&](int g) {
 #pragma unroll
-            for (int j = 0; j < kActChunks; ++j) {
-                const int c = j * 128 + quad * 32 + lane;
-                const int m = c % NB, kc = c / NB;
-                act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(p.a + act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8)));
+            for (int j = 0; j < kSets; ++j) {
+                const int it = g * kSets + j;
+                if (it < nit) {
+#pragma unroll
+                    for (int q = 0; q < kActChunks; ++q) {
+                        const int c = q * 128 + quad * 32 + lane;
+                        const int m = c % NB, kc = c / NB;
+                        act_regs[j][q] = __ldg(reinterpret_cast<const uint4 *>(p.a + act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8)));
+                    }
+                }
             }
         };
-        if (set < nit) load_act(set);
+        if (team < ngroups) load_act(team);
         // ldmatrix row addresses: lanes 0-15 give the rows of the left face, 16-31 of the right face
         const uint32_t ld_off = 64u + (uint32_t)(lane >> 4) * 256u + (uint32_t)(lane & 15) * 16u;
         const int sh0 = 2 * (lane & 3);  // within a face's 8 scale pairs: this lane's K rows are 4*(lane%4) .. +3
         const uint32_t st_lane = (uint32_t)(quad * 32) << 16;
-        for (int g = 0; g < ngroups; ++g) {
-            const int it = g * kSets + set;
-            if (it >= nit) break;  // short last group: the MMA issuer arrives in this set's place
+        for (int g = team; g < ngroups; g += kSets) {
+            const int r = min(kSets, nit - g * kSets);
             const int gs = g % kPkGroups, ga = g % kAGroups;
             const uint32_t phs = (g / kPkGroups) & 1, pha = (g / kAGroups) & 1;
             int good = 1;
@@ -217,53 +223,56 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
                 good = mbar_wait(empty_a(ga), pha ^ 1, abort_flag, p.status, 13) && mbar_wait(full_pk(gs), phs, abort_flag, p.status, 14);
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) { ok = false; break; }
-            const uint32_t tile = sbase + L::pk + (gs * kSets + set) * kStageBytes + quad * kTile;
-            // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
-            const uint32_t e2 = *reinterpret_cast<const uint16_t *>(smem + (tile - sbase) + 2 * lane);
-            const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
-            const uint32_t my_scale = (__vminu2(eh, 0x007f007fu) + 0x007f007fu) << 7;   // 2^min(E, 127) per half
-            const bool big = __any_sync(0xffffffffu, ((eh | (eh >> 16)) & 0x80u) != 0u);
-            uint32_t top[4], bot[4];
-            ldmatrix_x2_trans_b8(tile + ld_off, top);         // faces 0 (left) and 1 (right): K 0..15
-            ldmatrix_x2_trans_b8(tile + ld_off + 512u, bot);  // faces 2 and 3: K 16..31
-            const uint32_t a_col = tmem_base + st_lane + (uint32_t)(L::kACol0 + (ga * kSets + set) * kAColsPerStage);
 #pragma unroll
-            for (int f = 0; f < 4; ++f) {
-                // face f = 2 * kh + nh; registers {2*nh, 2*nh+1} of the kh-th load: columns lane/4 and lane/4 + 8
-                const uint32_t c0 = (f >> 1) ? bot[2 * (f & 1)] : top[2 * (f & 1)];
-                const uint32_t c1 = (f >> 1) ? bot[2 * (f & 1) + 1] : top[2 * (f & 1) + 1];
-                const uint32_t s01 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0);
-                const uint32_t s23 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0 + 1);
-                uint32_t o[4];
-                expand4(c0, s01, s23, o[0], o[1]);
-                expand4(c1, s01, s23, o[2], o[3]);
-                if (big) {
-                    // exponents above 127 (row maximum of 2 or more): second factor 2^(E - 127)
-                    const uint32_t my_t = __vmaxu2(__vminu2(eh, 0x00fe00feu), 0x007f007fu) << 7;
-                    const uint32_t t01 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0);
-                    const uint32_t t23 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0 + 1);
-                    o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
+            for (int j = 0; j < kSets; ++j) {
+                if (j < r) {
+                    const uint32_t tile = sbase + L::pk + (gs * kSets + j) * kStageBytes + quad * kTile;
+                    // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
+                    const uint32_t e2 = *reinterpret_cast<const uint16_t *>(smem + (tile - sbase) + 2 * lane);
+                    const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
+                    const uint32_t my_scale = (__vminu2(eh, 0x007f007fu) + 0x007f007fu) << 7;   // 2^min(E, 127) per half
+                    const bool big = __any_sync(0xffffffffu, ((eh | (eh >> 16)) & 0x80u) != 0u);
+                    uint32_t top[4], bot[4];
+                    ldmatrix_x2_trans_b8(tile + ld_off, top);         // faces 0 (left) and 1 (right): K 0..15
+                    ldmatrix_x2_trans_b8(tile + ld_off + 512u, bot);  // faces 2 and 3: K 16..31
+                    const uint32_t a_col = tmem_base + st_lane + (uint32_t)(L::kACol0 + (ga * kSets + j) * kAColsPerStage);
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) {
+                        // face f = 2 * kh + nh; registers {2*nh, 2*nh+1} of the kh-th load: columns lane/4 and lane/4 + 8
+                        const uint32_t c0 = (f >> 1) ? bot[2 * (f & 1)] : top[2 * (f & 1)];
+                        const uint32_t c1 = (f >> 1) ? bot[2 * (f & 1) + 1] : top[2 * (f & 1) + 1];
+                        const uint32_t s01 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0);
+                        const uint32_t s23 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0 + 1);
+                        uint32_t o[4];
+                        expand4(c0, s01, s23, o[0], o[1]);
+                        expand4(c1, s01, s23, o[2], o[3]);
+                        if (big) {
+                            // exponents above 127 (row maximum of 2 or more): second factor 2^(E - 127)
+                            const uint32_t my_t = __vmaxu2(__vminu2(eh, 0x00fe00feu), 0x007f007fu) << 7;
+                            const uint32_t t01 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0);
+                            const uint32_t t23 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0 + 1);
+                            o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
+                        }
+                        // TMEM lanes 32*quad + 16*nh + {lane/4, lane/4 + 8}; columns: stage base + 8*kh + 2*(lane%4) + {0, 1}
+                        tmem_st_16x256b(a_col + ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8), o[0], o[1], o[2], o[3]);
+                    }
+                    // activations of this K-block (fetched one turn ahead): this warp stores a quarter of the block
+                    uint8_t *const bst = smem + L::b + (ga * kSets + j) * L::kBStageBytes;
+#pragma unroll
+                    for (int q = 0; q < kActChunks; ++q) {
+                        const int c = q * 128 + quad * 32 + lane;
+                        const int m = c % NB, kc = c / NB;
+                        *reinterpret_cast<uint4 *>(bst + (m >> 3) * kB_SBO + kc * kB_LBO + (m & 7) * 16) = act_regs[j][q];
+                    }
                 }
-                // TMEM lanes 32*quad + 16*nh + {lane/4, lane/4 + 8}; columns: stage base + 8*kh + 2*(lane%4) + {0, 1}
-                tmem_st_16x256b(a_col + ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8), o[0], o[1], o[2], o[3]);
-            }
-            // activations of this K-block (fetched one turn ahead): this warp stores a quarter of the block
-            uint8_t *const bst = smem + L::b + (ga * kSets + set) * L::kBStageBytes;
-#pragma unroll
-            for (int j = 0; j < kActChunks; ++j) {
-                const int c = j * 128 + quad * 32 + lane;
-                const int m = c % NB, kc = c / NB;
-                *reinterpret_cast<uint4 *>(bst + (m >> 3) * kB_SBO + kc * kB_LBO + (m & 7) * 16) = act_regs[j];
             }
             tmem_st_wait();
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(full_a(ga));
-                mbar_arrive(empty_pk(gs));
-            }
-            if (it + kSets < nit) load_act(it + kSets);
+            if (lane == 0) mbar_arrive(full_a(ga));
+            if (lane == 1) mbar_arrive(empty_pk(gs));
+            if (g + kSets < ngroups) load_act(g + kSets);
         }
     }
 
@@ -312,13 +321,25 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float4 *src = reinterpret_cast<const float4 *>(
-                            p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+                    // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
+                    for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                        float4 x[4][4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float4 x = __ldcg(src + j);
-                            v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+                        for (int u = 0; u < 4; ++u) {
+                            const int sp = min(sp0 + u, p.splits - 1);
+                            const float4 *src = reinterpret_cast<const float4 *>(
+                                p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (sp0 + u < p.splits) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                                }
+                            }
                         }
                     }
                     finish_and_store<NB>(p, v, row0, col0, n);

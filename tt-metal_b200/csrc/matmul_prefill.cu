@@ -334,12 +334,14 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
                     tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(rr * BN + col0), r);
                     tmem_ld_wait();
                     float v[16];
+                    TTB_DISPATCH_ACT(p.act, {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float y = __uint_as_float(r[j]);
-                        if (p.bias) y += bias_at(p.bias, n0 + j);
-                        v[j] = apply_activation(y, p.act);
-                    }
+                        for (int j = 0; j < 16; ++j) {
+                            float y = __uint_as_float(r[j]);
+                            if (p.bias) y += bias_at(p.bias, n0 + j);
+                            v[j] = apply_activation_t<ACT>(y);
+                        }
+                    });
                     // 16 consecutive columns of one row: one face row when tiled, contiguous either way
                     const int64_t off = p.out_row_major ? row * p.N + n0 : tiled_offset(row, n0, p.Nt);
                     if (p.out_dtype == TTB_FLOAT32) {
