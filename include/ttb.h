@@ -58,7 +58,9 @@ extern "C" {
 #define TTB_MM_FORCE_GENERIC 4 /* use the shape-generic CUDA-core kernel (cross-check path)      */
 #define TTB_MM_DECODE_TMEM_OPERAND 16 /* bfloat8_b decode shapes: feed the expanded weights to the MMA through
                                          tensor memory (ldmatrix.trans + tcgen05.st) instead of shared memory */
-#define TTB_MM_WORKSPACE_ZEROED 8 /* the first 64 KiB of the workspace are zero: either freshly zeroed or
+#define TTB_MM_DETERMINISTIC 32 /* split-K partial sums are added in a fixed order (bit-reproducible results) instead
+                                   of with floating-point reductions in arrival order */
+#define TTB_MM_WORKSPACE_ZEROED 8 /* the first 16 MiB + 64 KiB of the workspace are zero: freshly zeroed, or
                                     last used by a completed ttb_matmul (which leaves them zero)      */
 
 const char *ttb_last_error(void);

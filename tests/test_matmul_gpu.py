@@ -209,8 +209,11 @@ def test_batched_activations_share_the_weight(ttb, orc):
     check(y, x.float() @ w_ref)
 
 
-def test_repeated_launches_reuse_scratch(ttb, orc):
-    """Split-K scratch counters must return to zero after each launch."""
+@pytest.mark.parametrize("flags", [cabi.MM_DETERMINISTIC, 0, cabi.MM_DECODE_TMEM_OPERAND])
+def test_repeated_launches_reuse_scratch(ttb, orc, flags):
+    """Split-K scratch (arrival counters, accumulation tiles) must be back to zero after each launch. With
+    MM_DETERMINISTIC the partial sums are added in a fixed order and repeated launches agree bit for bit; the default
+    adds them in arrival order, so repeats may differ in the last fp32 bit before rounding to bf16."""
     import torch
     M, K, N = 32, 4096, 1024
     x, w_dev, w_ref = make_case(ttb, orc, 31, M, K, N, cabi.BFLOAT8_B)
@@ -222,10 +225,15 @@ def test_repeated_launches_reuse_scratch(ttb, orc):
     for _ in range(3):
         out = torch.empty(M * N, dtype=torch.bfloat16, device="cuda")
         ttb.check(ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(),
-                                      cabi.BFLOAT16, 1, M, K, N, 0, 0, ws.data_ptr(), nbytes, None))
+                                      cabi.BFLOAT16, 1, M, K, N, 0, flags | cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None))
         outs.append(out)
     ttb.check(ttb.check_status(None))
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    if flags & cabi.MM_DETERMINISTIC:
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    else:
+        assert torch.allclose(outs[0].float(), outs[1].float(), rtol=1e-2, atol=1e-2) and torch.allclose(outs[1].float(), outs[2].float(), rtol=1e-2, atol=1e-2)
+    # everything the kernels must leave zero is zero again
+    assert int(ws[: 65536 + (16 << 20)].count_nonzero().item()) == 0
     check(ttb.untilize(outs[0], 1, M, N).reshape(M, N), x.float() @ w_ref)
     # too small a workspace is refused before anything is launched
     rc = ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, outs[0].data_ptr(),

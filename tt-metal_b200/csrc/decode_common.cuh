@@ -11,14 +11,21 @@ struct DecodeArgs {
     const uint16_t *a;
     const uint16_t *bias;
     void *out;
-    float *partial;
+    float *partial;   // ordered mode: one fp32 partial per split; accumulate mode: unused
+    float *accum;     // accumulate mode: one fp32 tile per output tile, zero between launches
     int *counters;
     int64_t K, N;
     int Kt, Nt;
     int nkb, kb_per_split, splits;
     int act, out_dtype, a_row_major, out_row_major;
+    int ordered;      // 1: add the split-K partials in split order (bit-reproducible); 0: red.add into `accum`
     int *status;  // device status word raised by bounded waits that run out
 };
+
+// Adds four floats to global memory with one vector reduction (no return value, any order).
+__device__ __forceinline__ void red_add_f32x4(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 // Global element offset of the 8-element activation chunk (row r, columns k..k+7).
 __device__ __forceinline__ int64_t act_chunk_offset(const DecodeArgs &p, int64_t r, int64_t k) {

@@ -349,11 +349,15 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                 }
                 if (p.splits == 1) {
                     finish_and_store<NB>(p, v, row0, col0, n);
-                } else {
+                } else if (p.ordered) {
                     float4 *dst = reinterpret_cast<float4 *>(
                         p.partial + (((int64_t)tile_id * p.splits + split) * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    float *dst = p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
         }
@@ -371,25 +375,36 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
-                    for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
-                        float4 x[4][4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int sp = min(sp0 + u, p.splits - 1);
-                            const float4 *src = reinterpret_cast<const float4 *>(
-                                p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (sp0 + u < p.splits) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                    if (p.ordered) {
+                        // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
+                        for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                            float4 x[4][4];
+    #pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int sp = min(sp0 + u, p.splits - 1);
+                                const float4 *src = reinterpret_cast<const float4 *>(
+                                    p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+    #pragma unroll
+                                for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
+                            }
+    #pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (sp0 + u < p.splits) {
+    #pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                                    }
                                 }
                             }
+                        }
+                    } else {
+                        // the tile's sums are complete: read them and leave zeros behind for the next launch
+                        float4 *acc = reinterpret_cast<float4 *>(p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 x = __ldcg(acc + j);
+                            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+                            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
                     finish_and_store<NB>(p, v, row0, col0, n);
@@ -434,6 +449,9 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
 
 // The head of the workspace holds one arrival counter per output tile; the partial sums follow.
 static constexpr int64_t kCounterBytes = 65536;
+// Workspace layout: [arrival counters, 64 KiB][accumulate-mode tiles, 16 MiB, zero between launches][ordered-mode
+// partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
+static constexpr int64_t kAccumBytes = 16 << 20;
 
 int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, cudaStream_t stream);
 
@@ -489,16 +507,29 @@ void decode_plan(int64_t rows, int64_t K, int64_t N, int *splits_out, int *kb_pe
     *nb_out = nb;
 }
 
-int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
+// Bytes of the ordered-mode partials (0 when K is not split).
+static int64_t decode_partial_bytes(int64_t rows, int64_t K, int64_t N) {
     int s, kbps, tiles, nb;
     decode_plan(rows, K, N, &s, &kbps, &tiles, &nb);
-    if (s == 1) return 0;
-    return kCounterBytes + (int64_t)tiles * s * BN * nb * 4;
+    return s == 1 ? 0 : (int64_t)tiles * s * BN * nb * 4;
+}
+
+// Accumulate mode needs rows * N fp32 inside the fixed 16 MiB region; larger outputs use ordered mode.
+static bool decode_accumulate_ok(int64_t rows, int64_t N) { return rows * N * 4 <= kAccumBytes; }
+
+int64_t decode_workspace_bytes_compact(int64_t rows, int64_t K, int64_t N) {
+    const int64_t pb = decode_partial_bytes(rows, K, N);
+    return pb ? kCounterBytes + pb : 0;
+}
+
+int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
+    const int64_t pb = decode_partial_bytes(rows, K, N);
+    return pb ? kCounterBytes + kAccumBytes + pb : 0;
 }
 
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
-                             int64_t workspace_bytes, bool counters_are_zero, cudaStream_t stream) {
+                             int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream) {
     DecodeArgs p;
     int tiles, nb;
     decode_plan(rows, K, N, &p.splits, &p.kb_per_split, &tiles, &nb);
@@ -507,19 +538,24 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     p.act = act; p.out_dtype = out_dtype;
     p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
-    p.partial = nullptr; p.counters = nullptr;
+    p.partial = nullptr; p.accum = nullptr; p.counters = nullptr;
+    p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !decode_accumulate_ok(rows, N);
     if (int32_t rc = status_word_address(&p.status)) return rc;
     if (p.splits > 1) {
-        const int64_t need = decode_workspace_bytes(rows, K, N);
+        const int64_t need = compact ? decode_workspace_bytes_compact(rows, K, N) : decode_workspace_bytes(rows, K, N);
         if (!workspace || workspace_bytes < need)
             return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
                         (long long)workspace_bytes);
         if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
             return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
-        const int64_t counters = kCounterBytes;
         p.counters = (int *)workspace;
-        p.partial = (float *)((uint8_t *)workspace + counters);
-        if (!counters_are_zero) TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)counters, stream));
+        p.accum = (float *)((uint8_t *)workspace + kCounterBytes);
+        p.partial = (float *)((uint8_t *)workspace + kCounterBytes + (compact ? 0 : kAccumBytes));
+        if (!counters_are_zero) {
+            // counters always; in accumulate mode also the tiles this launch adds into
+            const int64_t zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * N * 4);
+            TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
+        }
     }
     dim3 grid((unsigned)(N / BN), (unsigned)p.splits, (unsigned)(rows / nb));
 #define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, stream)
@@ -575,7 +611,7 @@ extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, cons
                     "ttb_matmul_decode_static: only the decode shapes are served without allocation (bfloat8_b / bfloat4_b weights, "
                     "at most 256 rows, N a multiple of 128); use ttb_matmul for [%lld x %lld x %lld]",
                     (long long)rows, (long long)K, (long long)N);
-    const int64_t need = decode_workspace_bytes(rows, K, N);
+    const int64_t need = decode_workspace_bytes_compact(rows, K, N);
     if (need > (int64_t)TTB_STATIC_SCRATCH_BYTES)
         return fail(TTB_E_WORKSPACE,
                     "ttb_matmul_decode_static: this shape needs %lld bytes of scratch, the built-in scratch holds %lld; use ttb_matmul "
@@ -597,5 +633,5 @@ extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, cons
     // The array keeps whatever the previous call left. Only the arrival counters at its head must start at zero
     // (launch_matmul_decode clears them on the stream); the partial sums are fully rewritten before they are read.
     return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR),
-                                need > 0 ? scratch_addr[dev] : nullptr, need, /*counters_are_zero=*/false, (cudaStream_t)stream);
+                                need > 0 ? scratch_addr[dev] : nullptr, need, /*counters_are_zero=*/false, /*compact=*/true, (cudaStream_t)stream);
 }

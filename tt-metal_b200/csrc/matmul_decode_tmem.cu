@@ -300,11 +300,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
                 for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]) + __uint_as_float(r1[j]);
                 if (p.splits == 1) {
                     finish_and_store<NB>(p, v, row0, col0, n);
-                } else {
+                } else if (p.ordered) {
                     float4 *dst = reinterpret_cast<float4 *>(
                         p.partial + (((int64_t)tile_id * p.splits + split) * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    float *dst = p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
         }
@@ -321,25 +325,36 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
-                    for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
-                        float4 x[4][4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int sp = min(sp0 + u, p.splits - 1);
-                            const float4 *src = reinterpret_cast<const float4 *>(
-                                p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (sp0 + u < p.splits) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                    if (p.ordered) {
+                        // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
+                        for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                            float4 x[4][4];
+    #pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int sp = min(sp0 + u, p.splits - 1);
+                                const float4 *src = reinterpret_cast<const float4 *>(
+                                    p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
+    #pragma unroll
+                                for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
+                            }
+    #pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (sp0 + u < p.splits) {
+    #pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
+                                    }
                                 }
                             }
+                        }
+                    } else {
+                        // the tile's sums are complete: read them and leave zeros behind for the next launch
+                        float4 *acc = reinterpret_cast<float4 *>(p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 x = __ldcg(acc + j);
+                            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+                            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
                     finish_and_store<NB>(p, v, row0, col0, n);

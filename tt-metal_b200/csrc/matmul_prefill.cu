@@ -400,8 +400,10 @@ bool prefill_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
 }
 
 // Scratch for the re-laid activations.
-// The first 64 KiB of a matmul workspace belong to the split-K arrival counters of the decode kernels and stay untouched.
-int64_t prefill_workspace_bytes(int64_t rows, int64_t K) { return 65536 + rows * K * 2; }
+// The head of a matmul workspace (64 KiB of arrival counters + 16 MiB of accumulation tiles) belongs to the split-K
+// decode kernels and must stay zero; the re-laid activations go behind it.
+static constexpr int64_t kReservedHead = 65536 + (16 << 20);
+int64_t prefill_workspace_bytes(int64_t rows, int64_t K) { return kReservedHead + rows * K * 2; }
 
 int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype, int64_t rows,
                               int64_t K, int64_t N, int act, int flags, void *workspace, int64_t workspace_bytes, int *status,
@@ -415,12 +417,12 @@ int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const v
     {
         const int64_t nchunks = rows * K / 8;
         const int blocks = (int)((nchunks + 255) / 256 < 148 * 16 ? (nchunks + 255) / 256 : 148 * 16);
-        relayout_activations<<<blocks, 256, 0, stream>>>((const uint16_t *)a, (uint4 *)((uint8_t *)workspace + 65536), rows, K, R,
+        relayout_activations<<<blocks, 256, 0, stream>>>((const uint16_t *)a, (uint4 *)((uint8_t *)workspace + kReservedHead), rows, K, R,
                                                          (flags & TTB_MM_A_ROW_MAJOR) != 0);
         TTB_LAUNCH_CHECK("relayout_activations");
     }
     PrefillArgs p;
-    p.w = (const uint8_t *)w; p.x = (const uint8_t *)workspace + 65536; p.bias = (const uint16_t *)bias; p.out = out;
+    p.w = (const uint8_t *)w; p.x = (const uint8_t *)workspace + kReservedHead; p.bias = (const uint16_t *)bias; p.out = out;
     p.K = K; p.N = N; p.rows = rows; p.Nt = (int)(N / 32); p.nkb = (int)(K / BK);
     p.act = act; p.out_dtype = out_dtype; p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.status = status;
