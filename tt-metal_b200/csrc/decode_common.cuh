@@ -36,6 +36,14 @@ __device__ __forceinline__ int64_t act_chunk_offset(const DecodeArgs &p, int64_t
 
 // Bias, activation and store of 16 consecutive rows (row0 + col0 .. + 15, col0 a multiple of 16) of output column n.
 // In the tiled layout those 16 elements sit 16 apart inside one face, in the row-major layout N apart.
+// Element offset of the chunk (row r, K-block 0, 8-element chunk kc of the block's 32 columns) and the constant step from
+// one K-block to the next: a K-block is one tile column in the tiled layout (1024 elements on), 32 elements in row-major.
+__device__ __forceinline__ int64_t act_chunk_base(const DecodeArgs &p, int64_t r, int kc) {
+    if (p.a_row_major) return r * p.K + kc * 8;
+    return (r >> 5) * p.Kt * 1024 + 256 * (2 * (int)((r & 31) >> 4) + (kc >> 1)) + 16 * (int)(r & 15) + (kc & 1) * 8;
+}
+__device__ __forceinline__ int act_chunk_step(const DecodeArgs &p) { return p.a_row_major ? 32 : 1024; }
+
 template <int ACT>
 __device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
     const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;

@@ -237,14 +237,16 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         const int ew = (warp >> 2) * 3 + (warp & 3) - 1;
         constexpr int kActChunks = NB / 8;  // 16-byte activation chunks per lane per K-block (NB rows x 4 chunks)
         uint4 act_regs[kActChunks];
+        const uint16_t *act_src[kActChunks];
+#pragma unroll
+        for (int j = 0; j < kActChunks; ++j) {
+            const int c = j * 32 + lane;
+            act_src[j] = p.a + act_chunk_base(p, row0 + c % NB, c / NB) + (int64_t)kb0 * act_chunk_step(p);
+        }
+        const int act_step = act_chunk_step(p);
         auto load_act = [&](int it) {
 #pragma unroll
-            for (int j = 0; j < kActChunks; ++j) {
-                const int c = j * 32 + lane;
-                const int m = c % NB, kc = c / NB;
-                const int64_t off = act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8);
-                act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(p.a + off));
-            }
+            for (int j = 0; j < kActChunks; ++j) act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(act_src[j] + (int64_t)it * act_step));
         };
         if (ew < nit) load_act(ew);  // this warp's first stage is K-block ew (group ew / 3, member ew % 3)
         // lane-constant parts of the addressing: lanes 0-15 take the left face of a tile, 16-31 the right one
@@ -560,7 +562,8 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     dim3 grid((unsigned)(N / BN), (unsigned)p.splits, (unsigned)(rows / nb));
 #define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, stream)
     if (w_dtype == TTB_BFLOAT8_B) {
-        if (flags & TTB_MM_DECODE_TMEM_OPERAND) return launch_decode_tmem(p, nb, grid, stream);
+        // 128 rows per block: the tensor-memory path is the faster one (measured); smaller blocks: the shared-memory path
+        if ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128) return launch_decode_tmem(p, nb, grid, stream);
         if (nb == 32) TTB_DECODE(TTB_BFLOAT8_B, 32);
         if (nb == 64) TTB_DECODE(TTB_BFLOAT8_B, 64);
         TTB_DECODE(TTB_BFLOAT8_B, 128);

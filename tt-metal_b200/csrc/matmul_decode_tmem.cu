@@ -195,17 +195,22 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
         const int team = warp >> 2, quad = warp & 3;
         constexpr int kActChunks = NB / 32;  // 16-byte activation chunks per lane per stage (NB rows x 4 chunks over 4 warps)
         uint4 act_regs[kSets][kActChunks];
+        // per-lane source pointers of this lane's chunks at K-block 0 of the block's K range; K-block it is it * step further
+        const uint16_t *act_src[kActChunks];
+#pragma unroll
+        for (int q = 0; q < kActChunks; ++q) {
+            const int c = q * 128 + quad * 32 + lane;
+            act_src[q] = p.a + act_chunk_base(p, row0 + c % NB, c / NB) + (int64_t)kb0 * act_chunk_step(p);
+        }
+        const int act_step = act_chunk_step(p);
         auto load_act = [&](int g) {
 #pragma unroll
             for (int j = 0; j < kSets; ++j) {
                 const int it = g * kSets + j;
                 if (it < nit) {
 #pragma unroll
-                    for (int q = 0; q < kActChunks; ++q) {
-                        const int c = q * 128 + quad * 32 + lane;
-                        const int m = c % NB, kc = c / NB;
-                        act_regs[j][q] = __ldg(reinterpret_cast<const uint4 *>(p.a + act_chunk_offset(p, row0 + m, (int64_t)(kb0 + it) * BK + kc * 8)));
-                    }
+                    for (int q = 0; q < kActChunks; ++q)
+                        act_regs[j][q] = __ldg(reinterpret_cast<const uint4 *>(act_src[q] + (int64_t)it * act_step));
                 }
             }
         };
