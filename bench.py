@@ -259,7 +259,7 @@ def run_gpu_arm(args):
         if rc != 0:
             raise RuntimeError(lib.ttb_last_error().decode())
 
-    ZEROED = 8
+    ZEROED = 8 | (0 if args.no_overlap else 64)   # workspace head is zero; weights are long resident (overlapped launches)
     wl = Workload(args.workload, G)
     import ttnn
     device = ttnn.open_device(local_rank)
@@ -475,6 +475,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="launch every matmul after the previous one has fully completed")
     ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
                     help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "
                          "c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")

@@ -62,6 +62,11 @@ extern "C" {
                                    of with floating-point reductions in arrival order */
 #define TTB_MM_WORKSPACE_ZEROED 8 /* the first 16 MiB + 64 KiB of the workspace are zero: freshly zeroed, or
                                     last used by a completed ttb_matmul (which leaves them zero)      */
+#define TTB_MM_WEIGHTS_RESIDENT 64 /* `w` was complete in device memory before the previous operation on `stream` was
+                                      enqueued (weights loaded once, used many times). Decode kernels then start as a
+                                      programmatic dependent of the previous kernel: they stream packed weights while it
+                                      drains and wait for it before touching activations, bias, workspace or output.
+                                      Takes effect together with TTB_MM_WORKSPACE_ZEROED (no memset between the kernels). */
 
 const char *ttb_last_error(void);
 int32_t ttb_version(void);

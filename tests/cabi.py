@@ -13,6 +13,7 @@ HEADER = os.path.join(ROOT, "include", "ttb.h")
 BFLOAT16, FLOAT32, UINT32, BFLOAT8_B, BFLOAT4_B, UINT16 = 0, 1, 2, 3, 4, 6
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 MM_A_ROW_MAJOR, MM_OUT_ROW_MAJOR, MM_FORCE_GENERIC, MM_WORKSPACE_ZEROED, MM_DECODE_TMEM_OPERAND, MM_DETERMINISTIC = 1, 2, 4, 8, 16, 32
+MM_WEIGHTS_RESIDENT = 64
 TILE_BYTES = {BFLOAT8_B: 1088, BFLOAT4_B: 576}
 
 _vp, _i32, _i64, _sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t

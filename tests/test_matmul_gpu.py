@@ -239,3 +239,43 @@ def test_repeated_launches_reuse_scratch(ttb, orc, flags):
     rc = ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, outs[0].data_ptr(),
                              cabi.BFLOAT16, 1, M, K, N, 0, 0, ws.data_ptr(), 16, None)
     assert rc == -4
+
+
+@pytest.mark.parametrize("tmem", [0, cabi.MM_DECODE_TMEM_OPERAND])
+@pytest.mark.parametrize("M", [32, 128])
+def test_overlapped_launches_keep_their_dependencies(ttb, orc, tmem, M):
+    """MM_WEIGHTS_RESIDENT lets a decode kernel start while the previous one drains. A chain in which every launch consumes
+    the previous launch's output (and all share one workspace) must give exactly the results of the same chain launched
+    without overlap; MM_DETERMINISTIC makes both chains bit-reproducible."""
+    import torch
+    K = N = 2048
+    depth = 6
+    x = vectors.randn(77, (M, K), 1.0).bfloat16()
+    ws_list = []
+    for i in range(depth):
+        _, w_dev, _ = make_case(ttb, orc, 80 + i, M, K, N, cabi.BFLOAT8_B, w_std=0.02)
+        ws_list.append(w_dev)
+    torch.cuda.synchronize()
+    nbytes = ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N, cabi.MM_DETERMINISTIC)
+    assert nbytes > 0
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+
+    def chain(extra):
+        cur = ttb.tilize(x.cuda(), 1, M, K)
+        outs = []
+        for i in range(depth):
+            out = torch.empty(M * N, dtype=torch.bfloat16, device="cuda")
+            ttb.check(ttb.cdll.ttb_matmul(cur.data_ptr(), cabi.BFLOAT16, ws_list[i].data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(),
+                                          cabi.BFLOAT16, 1, M, K, N, 0, cabi.MM_DETERMINISTIC | cabi.MM_WORKSPACE_ZEROED | tmem | extra,
+                                          ws.data_ptr(), nbytes, None))
+            outs.append(out)
+            cur = out
+        ttb.check(ttb.check_status(None))
+        return outs
+
+    plain = chain(0)
+    for _ in range(3):
+        fast = chain(cabi.MM_WEIGHTS_RESIDENT)
+        for a, b in zip(plain, fast):
+            assert torch.equal(a, b)
+    assert int(ws[:65536].count_nonzero().item()) == 0

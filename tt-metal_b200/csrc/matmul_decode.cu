@@ -176,6 +176,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    // The next kernel on the stream may start its own set-up and weight streaming while this grid drains. Only the packed
+    // weights are read before grid_dep_wait(): activations, bias, scratch and the output wait for the previous grid.
+    grid_dep_launch();
 
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles -> shared-memory ring ----------------
@@ -244,6 +247,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
             act_src[j] = p.a + act_chunk_base(p, row0 + c % NB, c / NB) + (int64_t)kb0 * act_chunk_step(p);
         }
         const int act_step = act_chunk_step(p);
+        grid_dep_wait();
         auto load_act = [&](int it) {
 #pragma unroll
             for (int j = 0; j < kActChunks; ++j) act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(act_src[j] + (int64_t)it * act_step));
@@ -322,6 +326,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
     if (warp < 8) {
         // ---------------- epilogue: warps 0..7, TMEM lane quadrant warp % 4, column half warp / 4 ----------------
         const int tid = threadIdx.x;
+        grid_dep_wait();
         {
             int good = ok ? 1 : 0;
             good = __shfl_sync(0xffffffffu, good, 0);   // lane 0 ran the single-thread roles
@@ -433,7 +438,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
 }
 
 template <int FMT, int NB>
-int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
+int32_t launch_one(const DecodeArgs &p, dim3 grid, bool overlap, cudaStream_t stream) {
     constexpr int smem_bytes = SmemLayout<FMT, NB>::total + 128;
     static bool configured[64] = {};
     int dev = 0;
@@ -442,7 +447,17 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
         TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_kernel<FMT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
-    matmul_decode_kernel<FMT, NB><<<grid, kThreadsDecode, smem_bytes, stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreadsDecode);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_kernel<FMT, NB>, p));
     TTB_LAUNCH_CHECK("matmul_decode");
     return TTB_OK;
 }
@@ -455,7 +470,7 @@ static constexpr int64_t kCounterBytes = 65536;
 // partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
 static constexpr int64_t kAccumBytes = 16 << 20;
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, cudaStream_t stream);
+int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, bool overlap, cudaStream_t stream);
 
 // Device address of the status word on the current device (looked up once per device).
 int32_t status_word_address(int **out) {
@@ -541,6 +556,8 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.partial = nullptr; p.accum = nullptr; p.counters = nullptr;
+    // Overlap with the previous kernel only when nothing but kernels separates the two launches (no memset below).
+    bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
     p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !decode_accumulate_ok(rows, N);
     if (int32_t rc = status_word_address(&p.status)) return rc;
     if (p.splits > 1) {
@@ -557,13 +574,14 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
             // counters always; in accumulate mode also the tiles this launch adds into
             const int64_t zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * N * 4);
             TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
+            overlap = false;
         }
     }
     dim3 grid((unsigned)(N / BN), (unsigned)p.splits, (unsigned)(rows / nb));
-#define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, stream)
+#define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, overlap, stream)
     if (w_dtype == TTB_BFLOAT8_B) {
         // 128 rows per block: the tensor-memory path is the faster one (measured); smaller blocks: the shared-memory path
-        if ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128) return launch_decode_tmem(p, nb, grid, stream);
+        if ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128) return launch_decode_tmem(p, nb, grid, overlap, stream);
         if (nb == 32) TTB_DECODE(TTB_BFLOAT8_B, 32);
         if (nb == 64) TTB_DECODE(TTB_BFLOAT8_B, 64);
         TTB_DECODE(TTB_BFLOAT8_B, 128);

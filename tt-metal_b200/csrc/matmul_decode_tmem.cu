@@ -139,6 +139,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    // As in the shared-memory kernel: the next kernel may start while this grid drains, and only the packed weights are
+    // read before grid_dep_wait().
+    grid_dep_launch();
 
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles -> shared-memory ring, three stages per barrier ----------------
@@ -203,6 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
             act_src[q] = p.a + act_chunk_base(p, row0 + c % NB, c / NB) + (int64_t)kb0 * act_chunk_step(p);
         }
         const int act_step = act_chunk_step(p);
+        grid_dep_wait();
         auto load_act = [&](int g) {
 #pragma unroll
             for (int j = 0; j < kSets; ++j) {
@@ -285,6 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
         // ---------------- epilogue: TMEM lane quadrant warp % 4; the three warps of a quadrant share the columns ----------------
         const int tid = threadIdx.x;
         const int set = warp >> 2, quad = warp & 3;
+        grid_dep_wait();
         {
             int good = ok ? 1 : 0;
             if (lane == 0 && good && nit > 0) good = mbar_wait(accum_bar, 0, abort_flag, p.status, 15);
@@ -386,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
 }
 
 template <int NB>
-int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
+int32_t launch_one(const DecodeArgs &p, dim3 grid, bool overlap, cudaStream_t stream) {
     constexpr int smem_bytes = Layout<NB>::total + 128;
     static bool configured[64] = {};
     int dev = 0;
@@ -395,17 +400,27 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, cudaStream_t stream) {
         TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
-    matmul_decode_tmem_kernel<NB><<<grid, kThreads, smem_bytes, stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<NB>, p));
     TTB_LAUNCH_CHECK("matmul_decode_tmem");
     return TTB_OK;
 }
 
 }  // namespace
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, cudaStream_t stream) {
-    if (nb == 32) return launch_one<32>(p, grid, stream);
-    if (nb == 64) return launch_one<64>(p, grid, stream);
-    return launch_one<128>(p, grid, stream);
+int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, bool overlap, cudaStream_t stream) {
+    if (nb == 32) return launch_one<32>(p, grid, overlap, stream);
+    if (nb == 64) return launch_one<64>(p, grid, overlap, stream);
+    return launch_one<128>(p, grid, overlap, stream);
 }
 
 }  // namespace ttb

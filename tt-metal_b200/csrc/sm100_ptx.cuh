@@ -62,6 +62,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// grid_dep_launch: lets a kernel that was launched as a programmatic dependent of this one be scheduled once every
+// block of this grid has executed it (or exited). grid_dep_wait: returns when the grids this one depends on have
+// completed and their writes are visible. Both do nothing in a launch without a programmatic dependency.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- bulk copy global -> shared, completion counted on an mbarrier ------------------------------
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;

@@ -255,8 +255,12 @@ Tensor run_matmul(const char *op, const Tensor &a, const Tensor &b, const std::o
     auto outb = allocate_device_buffer(dev, physical_bytes(out_shape, out_dtype, Layout::TILE));
     const int64_t ws_bytes = ttb_matmul_workspace_bytes(ttb_dtype(b.dtype()), batch, Mp, Kp, Np, 0);
     void *ws = ws_bytes > 0 ? dev->workspace(ws_bytes) : nullptr;
+    // Every producer of a block-float tensor on this API (from_torch, to_layout, load_tensor, to_device) has finished on the
+    // device before it returns, so a block-float weight is complete long before this launch is enqueued and the kernel may
+    // stream it while the previous kernel drains.
+    const int flags = TTB_MM_WORKSPACE_ZEROED | (is_block_float(b.dtype()) ? TTB_MM_WEIGHTS_RESIDENT : 0);
     check(ttb_matmul(a.data(), ttb_dtype(a.dtype()), b.data(), ttb_dtype(b.dtype()), bias_ptr, outb->ptr, ttb_dtype(out_dtype), batch, Mp,
-                     Kp, Np, activation_code(activation), TTB_MM_WORKSPACE_ZEROED, ws, ws_bytes, nullptr),
+                     Kp, Np, activation_code(activation), flags, ws, ws_bytes, nullptr),
           op);
     return Tensor(outb, out_shape, out_dtype, Layout::TILE);
 }
