@@ -179,6 +179,54 @@ int32_t ttb_check_status(void *stream);
 int32_t ttb_gather_interleave(const void *src_dev, void *dst_dev, int32_t elem_size, int32_t ranks, int64_t rows,
                               int64_t cols_per_rank, void *stream);
 
+/* ---- matmul with the all-gather in its epilogue (tensor-parallel decode) -------------------------
+ * One process per GPU. Every rank computes its column slice out[:, rank*N : (rank+1)*N] of a gathered
+ * [batch*M, ranks*N] bfloat16 tiled tensor and stores each finished tile into its own copy and, over NVLink with plain
+ * peer stores, into every other rank's copy; no separate collective runs. Replaces ttnn.all_gather(ttnn.linear(x, w),
+ * dim=-1) (ttnn/ttnn/operations/ccl.py:26-39, tt_eager/tt_dnn/op_library/all_gather/all_gather_op.cpp:18-104,
+ * column-sharded weights as models/demos/llama2_70b/tt/llama_mlp_optimized.py:100-103).
+ *
+ * A gather point is a pair of 32-bit counters on every rank, both starting at zero: `arrived` (peers add one per
+ * finished launch, over NVLink) and `uses` (only the owning rank's launches count in it). The gathered copy on a rank
+ * is complete for the u-th use when arrived >= u * ranks. A later ttb_matmul_peer on the same stream that passes the
+ * gather point as `wait` holds its activation loads until then (its weight streaming is not held); any other consumer
+ * first runs ttb_peer_wait on the stream. Waits are bounded (about two seconds) and end in TTB_E_TIMEOUT through
+ * ttb_check_status instead of hanging.
+ * Rules the caller keeps: all ranks issue the same sequence of gathering launches; consecutive gathering launches on a
+ * stream use different gather points and different output buffers (two of each, alternating, suffice), and every gathered
+ * result is waited for (by a consuming launch or ttb_peer_wait) before the next gathering launch is enqueued;
+ * peer pointers come from ttb_ipc_open on handles made by ttb_ipc_export in the owning process. Decode shapes only
+ * (as ttb_matmul_decode_static), bfloat16 tiled output; a workspace is always required (ttb_matmul_peer_workspace_bytes),
+ * zero at first use. */
+#define TTB_MAX_RANKS 8
+typedef struct ttb_peer_gather {
+    int32_t ranks;                     /* 2..TTB_MAX_RANKS */
+    int32_t rank;                      /* this process's position */
+    void *out[TTB_MAX_RANKS];          /* the gathered tensor on every rank as mapped into this process; out[rank] is local */
+    uint32_t *arrived[TTB_MAX_RANKS];  /* the gather point's arrival counter on every rank; arrived[rank] is local */
+    uint32_t *uses;                    /* the gather point's local use counter */
+} ttb_peer_gather;
+typedef struct ttb_peer_wait_t {
+    const uint32_t *arrived;           /* local arrival counter of the gather point that produced the activations */
+    const uint32_t *uses;              /* its local use counter */
+    uint32_t ranks;
+} ttb_peer_wait_t;
+int64_t ttb_matmul_peer_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N);
+/* `gather` and `wait` may each be NULL: without `gather` the result is an ordinary local matmul into out_dev (then
+ * `out_dev` is used, otherwise gather->out[rank]); without `wait` the activations are assumed complete. */
+int32_t ttb_matmul_peer(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
+                        void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
+                        int32_t activation, int32_t flags, void *workspace_dev, int64_t workspace_bytes,
+                        const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream);
+/* Holds `stream` until the gather point's current use is complete on this rank (bounded). */
+int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream);
+/* CUDA IPC plumbing for the peer pointers: `handle` is a 64-byte buffer. `ptr_dev` must be the start of an allocation
+ * made by ttb_malloc. ttb_ipc_open maps a peer's allocation into this process (enabling peer access). */
+#define TTB_IPC_HANDLE_BYTES 64
+int32_t ttb_ipc_export(void *ptr_dev, void *handle);
+int32_t ttb_ipc_open(const void *handle, void **ptr_dev);
+int32_t ttb_ipc_close(void *ptr_dev);
+
 #ifdef __cplusplus
 }
 #endif

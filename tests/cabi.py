@@ -44,7 +44,40 @@ _SIGS = {
     "ttb_matmul_decode_static": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_check_status": (_i32, [_vp]),
     "ttb_gather_interleave": (_i32, [_vp, _vp, _i32, _i32, _i64, _i64, _vp]),
+    "ttb_matmul_peer_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
+    "ttb_matmul_peer": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    "ttb_peer_wait": (_i32, [_vp, _vp]),
+    "ttb_ipc_export": (_i32, [_vp, _vp]),
+    "ttb_ipc_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "ttb_ipc_close": (_i32, [_vp]),
 }
+
+MAX_RANKS = 8
+
+
+class PeerGather(ctypes.Structure):
+    """ttb_peer_gather of include/ttb.h."""
+    _fields_ = [("ranks", _i32), ("rank", _i32), ("out", _vp * MAX_RANKS), ("arrived", _vp * MAX_RANKS), ("uses", _vp)]
+
+
+class PeerWait(ctypes.Structure):
+    """ttb_peer_wait_t of include/ttb.h."""
+    _fields_ = [("arrived", _vp), ("uses", _vp), ("ranks", ctypes.c_uint32)]
+
+
+def peer_gather(rank, outs, arrived, uses):
+    g = PeerGather()
+    g.ranks, g.rank = len(outs), rank
+    for r, (o, a) in enumerate(zip(outs, arrived)):
+        g.out[r], g.arrived[r] = o, a
+    g.uses = uses
+    return g
+
+
+def peer_wait(arrived, uses, ranks):
+    w = PeerWait()
+    w.arrived, w.uses, w.ranks = arrived, uses, ranks
+    return w
 
 
 def declared_symbols():

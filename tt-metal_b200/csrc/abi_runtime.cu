@@ -51,6 +51,28 @@ int32_t ttb_free(void *dev_ptr) {
     if (dev_ptr) TTB_CUDA_TRY(cudaFree(dev_ptr));
     return TTB_OK;
 }
+// ---- CUDA IPC: peer pointers for the gather epilogue ------------------------------------------------------------------
+static_assert(sizeof(cudaIpcMemHandle_t) == TTB_IPC_HANDLE_BYTES, "IPC handle size");
+int32_t ttb_ipc_export(void *ptr_dev, void *handle) {
+    if (!ptr_dev || !handle) return fail(TTB_E_INVALID, "ttb_ipc_export: null pointer");
+    cudaIpcMemHandle_t h;
+    TTB_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr_dev));
+    memcpy(handle, &h, sizeof(h));
+    return TTB_OK;
+}
+int32_t ttb_ipc_open(const void *handle, void **ptr_dev) {
+    if (!ptr_dev || !handle) return fail(TTB_E_INVALID, "ttb_ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    *ptr_dev = nullptr;
+    TTB_CUDA_TRY(cudaIpcOpenMemHandle(ptr_dev, h, cudaIpcMemLazyEnablePeerAccess));
+    return TTB_OK;
+}
+int32_t ttb_ipc_close(void *ptr_dev) {
+    if (ptr_dev) TTB_CUDA_TRY(cudaIpcCloseMemHandle(ptr_dev));
+    return TTB_OK;
+}
+
 int32_t ttb_host_alloc(void **host_ptr, size_t bytes) {
     if (!host_ptr) return fail(TTB_E_INVALID, "ttb_host_alloc: null output pointer");
     *host_ptr = nullptr;

@@ -20,7 +20,54 @@ struct DecodeArgs {
     int act, out_dtype, a_row_major, out_row_major;
     int ordered;      // 1: add the split-K partials in split order (bit-reproducible); 0: red.add into `accum`
     int *status;  // device status word raised by bounded waits that run out
+    // ---- output placement: the result is columns [out_n0, out_n0 + N) of a tensor with out_Nt tiles (or out_N columns
+    // in row-major) per row; a plain matmul has out_n0 = 0, out_Nt = Nt, out_N = N ----
+    int64_t out_n0, out_N;
+    int out_Nt;
+    // ---- gather epilogue (ranks > 1): every finished tile is also stored into the same columns of the other ranks'
+    // copies of the output; the block that finishes last tells every rank that this rank's slice is complete ----
+    int ranks, rank;
+    uint16_t *peer_out[TTB_MAX_RANKS];
+    unsigned *peer_arrived[TTB_MAX_RANKS];
+    unsigned *uses;       // this rank's count of launches that used the gather point
+    int *grid_ticket;     // counts this launch's finished tiles
+    int tiles_total;
+    // ---- wait before the first activation load: `wait_arrived` must reach *wait_uses * wait_per_use ----
+    const unsigned *wait_arrived;
+    const unsigned *wait_uses;
+    unsigned wait_per_use;
 };
+
+// System-scope release / acquire on counters that other GPUs write or read over NVLink.
+__device__ __forceinline__ void red_release_sys_add(unsigned *addr, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *addr) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// Bounded wait for the peers' slices of a gathered activation (one lane calls it). Returns false and raises the
+// status word after `limit_cycles`, or as soon as another thread of the block gave up.
+__device__ __forceinline__ bool peer_wait(const DecodeArgs &p, volatile int *abort_flag, int code,
+                                          long long limit_cycles = 4000000000LL) {
+    if (!p.wait_arrived) return true;
+    const unsigned expected = *reinterpret_cast<const volatile unsigned *>(p.wait_uses) * p.wait_per_use;
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+        if ((int)(ld_acquire_sys(p.wait_arrived) - expected) >= 0) return true;
+        if ((spin & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > limit_cycles) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, code);
+                return false;
+            }
+        }
+        __nanosleep(64);
+    }
+}
 
 // Adds four floats to global memory with one vector reduction (no return value, any order).
 __device__ __forceinline__ void red_add_f32x4(float *addr, float a, float b, float c, float d) {
@@ -44,26 +91,69 @@ __device__ __forceinline__ int64_t act_chunk_base(const DecodeArgs &p, int64_t r
 }
 __device__ __forceinline__ int act_chunk_step(const DecodeArgs &p) { return p.a_row_major ? 32 : 1024; }
 
+// `stage` (gather epilogue only, bf16 tiled output) receives a copy at the element's position inside the block's own
+// [rows of the block, 128 columns] tiled slab, from where whole tiles are sent to the other ranks.
 template <int ACT>
-__device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
+__device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n,
+                                                   uint16_t *stage) {
     const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
     const int64_t r0 = row0 + col0;
-    const int64_t base = p.out_row_major ? r0 * p.N + n : tiled_offset(r0, n, p.Nt);
-    const int64_t stride = p.out_row_major ? p.N : 16;
+    const int64_t base = p.out_row_major ? r0 * p.out_N + p.out_n0 + n : tiled_offset(r0, p.out_n0 + n, p.out_Nt);
+    const int64_t stride = p.out_row_major ? p.out_N : 16;
     if (p.out_dtype == TTB_FLOAT32) {
         float *o = reinterpret_cast<float *>(p.out) + base;
 #pragma unroll
         for (int j = 0; j < 16; ++j) o[j * stride] = apply_activation_t<ACT>(v[j] + bias);
     } else {
         uint16_t *o = reinterpret_cast<uint16_t *>(p.out) + base;
+        if (stage) {
+            const int c = (int)(n & 127);
+            uint16_t *s = stage + ((col0 >> 5) * 4 + (c >> 5)) * 1024 + 256 * (2 * ((col0 & 31) >> 4) + ((c & 31) >> 4)) + (c & 15);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j * stride] = f32_to_bf16_bits(apply_activation_t<ACT>(v[j] + bias));
+            for (int j = 0; j < 16; ++j) {
+                const uint16_t b = f32_to_bf16_bits(apply_activation_t<ACT>(v[j] + bias));
+                o[j * stride] = b;
+                s[j * 16] = b;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j * stride] = f32_to_bf16_bits(apply_activation_t<ACT>(v[j] + bias));
+        }
     }
 }
 
 template <int NB>
-__device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n) {
-    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, v, row0, col0, n));
+__device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n,
+                                                 uint16_t *stage = nullptr) {
+    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, v, row0, col0, n, stage));
+}
+
+// Gather epilogue, called by all `nthreads` epilogue threads of a block (named barrier `bar_id`) after the block has
+// stored its finished [NB x 128] slab locally and into `stage`: sends the slab to every other rank with 16-byte stores
+// (each 32-row tile row of the slab is 8 KiB contiguous in the tiled output), then counts the tile as finished; the
+// block that finishes the launch's last tile signals every rank's arrival counter.
+template <int NB>
+__device__ __forceinline__ void gather_send(const DecodeArgs &p, const uint16_t *stage, int64_t row0, int ntile, int tid, int nthreads) {
+    asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");   // the slab is complete in shared memory
+    constexpr int kVecPerRow = 4 * 1024 * 2 / 16;                  // 512 16-byte vectors per tile row of the slab
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage);
+    for (int step = 1; step < p.ranks; ++step) {
+        const int r = (p.rank + step) % p.ranks;
+        for (int rt = 0; rt < NB / 32; ++rt) {
+            uint4 *dst = reinterpret_cast<uint4 *>(p.peer_out[r] + (((row0 >> 5) + rt) * p.out_Nt + ((p.out_n0 >> 5) + ntile * 4)) * 1024);
+            for (int i = tid; i < kVecPerRow; i += nthreads) dst[i] = src[rt * kVecPerRow + i];
+        }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+    if (tid == 0) {
+        const int done = atomicAdd(p.grid_ticket, 1);
+        if (done == p.tiles_total - 1) {
+            *p.grid_ticket = 0;                                     // ready for the next launch
+            __threadfence_system();
+            for (int r = 0; r < p.ranks; ++r) red_release_sys_add(p.peer_arrived[r], 1u);
+        }
+    }
 }
 
 }  // namespace ttb

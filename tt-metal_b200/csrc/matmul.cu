@@ -10,7 +10,8 @@ bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N);
 int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N);
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
-                             int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream);
+                             int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream,
+                             const ttb_peer_gather *gather, const ttb_peer_wait_t *wait);
 int32_t read_and_clear_status(cudaStream_t stream);
 int32_t status_word_address(int **out);
 bool prefill_supported(int w_dtype, int64_t rows, int64_t K, int64_t N);
@@ -73,7 +74,7 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
     auto s = (cudaStream_t)stream;
     if (!(flags & TTB_MM_FORCE_GENERIC) && decode_supported(w_dtype, rows, K, N))
         return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes,
-                                    (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false, s);
+                                    (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false, s, nullptr, nullptr);
     if (!(flags & TTB_MM_FORCE_GENERIC) && prefill_supported(w_dtype, rows, K, N)) {
         int *status = nullptr;
         if (int32_t rc = status_word_address(&status)) return rc;

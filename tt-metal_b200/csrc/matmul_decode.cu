@@ -248,16 +248,22 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         }
         const int act_step = act_chunk_step(p);
         grid_dep_wait();
+        if (p.wait_arrived) {
+            // activations gathered from other GPUs: hold until every rank's slice has landed in this rank's copy
+            int good = 1;
+            if (lane == 0) good = peer_wait(p, abort_flag, 6) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, good, 0)) ok = false;
+        }
         auto load_act = [&](int it) {
 #pragma unroll
-            for (int j = 0; j < kActChunks; ++j) act_regs[j] = __ldg(reinterpret_cast<const uint4 *>(act_src[j] + (int64_t)it * act_step));
+            for (int j = 0; j < kActChunks; ++j) act_regs[j] = __ldcg(reinterpret_cast<const uint4 *>(act_src[j] + (int64_t)it * act_step));
         };
-        if (ew < nit) load_act(ew);  // this warp's first stage is K-block ew (group ew / 3, member ew % 3)
+        if (ok && ew < nit) load_act(ew);  // this warp's first stage is K-block ew (group ew / 3, member ew % 3)
         // lane-constant parts of the addressing: lanes 0-15 take the left face of a tile, 16-31 the right one
         const int lane_pk = lane * (FMT == TTB_BFLOAT8_B ? 16 : 8);
         const int lane_a = ((lane & 15) >> 3) * kA_LBO + (lane >> 4) * 2 * kA_SBO + (lane & 7) * 16;
         // triplet ew / 3 takes every third group; within a group this warp expands stage ew % 3
-        for (int g = ew / kGroup; g < ngroups; g += kExpandWarps / kGroup) {
+        for (int g = ew / kGroup; ok && g < ngroups; g += kExpandWarps / kGroup) {
             const int it = g * kGroup + ew % kGroup;
             if (it >= nit) break;  // short last group: the MMA issuer arrives in this warp's place
             const int gs = g % kPkGroups, gt = g % kAbGroups;
@@ -327,6 +333,8 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         // ---------------- epilogue: warps 0..7, TMEM lane quadrant warp % 4, column half warp / 4 ----------------
         const int tid = threadIdx.x;
         grid_dep_wait();
+        uint16_t *const stage = p.ranks > 1 ? reinterpret_cast<uint16_t *>(smem + L::pk) : nullptr;   // the packed ring is idle by now
+        if (p.ranks > 1 && tid == 0 && blockIdx.x + blockIdx.y + blockIdx.z == 0) *p.uses = *p.uses + 1;
         {
             int good = ok ? 1 : 0;
             good = __shfl_sync(0xffffffffu, good, 0);   // lane 0 ran the single-thread roles
@@ -355,7 +363,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                     for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
                 }
                 if (p.splits == 1) {
-                    finish_and_store<NB>(p, v, row0, col0, n);
+                    finish_and_store<NB>(p, v, row0, col0, n, stage);
                 } else if (p.ordered) {
                     float4 *dst = reinterpret_cast<float4 *>(
                         p.partial + (((int64_t)tile_id * p.splits + split) * BN + quad * 32 + lane) * NB + col0);
@@ -414,10 +422,16 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
                             acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
-                    finish_and_store<NB>(p, v, row0, col0, n);
+                    finish_and_store<NB>(p, v, row0, col0, n, stage);
                 }
                 if (tid == 0) p.counters[tile_id] = 0;  // leave the scratch ready for the next launch
+                if (p.ranks > 1) gather_send<NB>(p, stage, row0, ntile, tid, kEpilogueThreads);
             }
+        } else if (p.ranks > 1) {
+            // one decision for the whole block, so that every epilogue thread takes part in gather_send's barriers
+            if (tid == 0) *last_flag = (*abort_flag == 0 && nit > 0) ? 1 : 0;
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+            if (*last_flag) gather_send<NB>(p, stage, row0, ntile, tid, kEpilogueThreads);
         }
     }
 
@@ -492,7 +506,7 @@ static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : 
 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes;
+           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes - 64;   // the last counter is the launch-wide ticket
 }
 
 // Chooses how many blocks share one output tile along K so that the grid fills the 148 SMs in whole waves.
@@ -544,10 +558,16 @@ int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
     return pb ? kCounterBytes + kAccumBytes + pb : 0;
 }
 
+// The gather epilogue always needs the counters (launch-wide ticket), also when K is not split.
+int64_t decode_workspace_bytes_peer(int64_t rows, int64_t K, int64_t N) {
+    return kCounterBytes + kAccumBytes + decode_partial_bytes(rows, K, N);
+}
+
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
-                             int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream) {
-    DecodeArgs p;
+                             int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream,
+                             const ttb_peer_gather *gather, const ttb_peer_wait_t *wait) {
+    DecodeArgs p = {};
     int tiles, nb;
     decode_plan(rows, K, N, &p.splits, &p.kb_per_split, &tiles, &nb);
     p.w = (const uint8_t *)w; p.a = (const uint16_t *)a; p.bias = (const uint16_t *)bias; p.out = out;
@@ -559,15 +579,33 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     // Overlap with the previous kernel only when nothing but kernels separates the two launches (no memset below).
     bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
     p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !decode_accumulate_ok(rows, N);
+    p.out_n0 = 0; p.out_N = N; p.out_Nt = p.Nt;
+    if (wait) {
+        p.wait_arrived = wait->arrived; p.wait_uses = wait->uses; p.wait_per_use = wait->ranks;
+    }
+    if (gather) {
+        p.ranks = gather->ranks; p.rank = gather->rank;
+        p.out = gather->out[gather->rank];
+        p.out_n0 = (int64_t)gather->rank * N; p.out_N = (int64_t)gather->ranks * N; p.out_Nt = gather->ranks * p.Nt;
+        for (int r = 0; r < gather->ranks; ++r) {
+            p.peer_out[r] = (uint16_t *)gather->out[r];
+            p.peer_arrived[r] = gather->arrived[r];
+        }
+        p.uses = gather->uses;
+        p.tiles_total = tiles;
+    }
     if (int32_t rc = status_word_address(&p.status)) return rc;
-    if (p.splits > 1) {
-        const int64_t need = compact ? decode_workspace_bytes_compact(rows, K, N) : decode_workspace_bytes(rows, K, N);
+    if (p.splits > 1 || gather) {
+        const int64_t need = compact   ? decode_workspace_bytes_compact(rows, K, N)
+                             : gather ? decode_workspace_bytes_peer(rows, K, N)
+                                      : decode_workspace_bytes(rows, K, N);
         if (!workspace || workspace_bytes < need)
             return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
                         (long long)workspace_bytes);
         if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
             return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
         p.counters = (int *)workspace;
+        p.grid_ticket = (int *)workspace + (kCounterBytes / 4 - 1);
         p.accum = (float *)((uint8_t *)workspace + kCounterBytes);
         p.partial = (float *)((uint8_t *)workspace + kCounterBytes + (compact ? 0 : kAccumBytes));
         if (!counters_are_zero) {
@@ -581,7 +619,8 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
 #define TTB_DECODE(F, B) return launch_one<F, B>(p, grid, overlap, stream)
     if (w_dtype == TTB_BFLOAT8_B) {
         // 128 rows per block: the tensor-memory path is the faster one (measured); smaller blocks: the shared-memory path
-        if ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128) return launch_decode_tmem(p, nb, grid, overlap, stream);
+        // (the gather epilogue and the peer wait exist in the shared-memory kernel only)
+        if (!gather && !wait && ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128)) return launch_decode_tmem(p, nb, grid, overlap, stream);
         if (nb == 32) TTB_DECODE(TTB_BFLOAT8_B, 32);
         if (nb == 64) TTB_DECODE(TTB_BFLOAT8_B, 64);
         TTB_DECODE(TTB_BFLOAT8_B, 128);
@@ -654,5 +693,73 @@ extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, cons
     // The array keeps whatever the previous call left. Only the arrival counters at its head must start at zero
     // (launch_matmul_decode clears them on the stream); the partial sums are fully rewritten before they are read.
     return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR),
-                                need > 0 ? scratch_addr[dev] : nullptr, need, /*counters_are_zero=*/false, /*compact=*/true, (cudaStream_t)stream);
+                                need > 0 ? scratch_addr[dev] : nullptr, need, /*counters_are_zero=*/false, /*compact=*/true, (cudaStream_t)stream,
+                                nullptr, nullptr);
+}
+
+// ---- matmul with the all-gather in its epilogue ------------------------------------------------------------------------
+extern "C" int64_t ttb_matmul_peer_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N) {
+    using namespace ttb;
+    if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || !decode_supported(w_dtype, batch * M, K, N)) return 0;
+    return decode_workspace_bytes_peer(batch * M, K, N);
+}
+
+extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, const void *bias, void *out,
+                                   int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t act, int32_t flags,
+                                   void *workspace, int64_t workspace_bytes, const ttb_peer_gather *gather,
+                                   const ttb_peer_wait_t *wait, void *stream) {
+    using namespace ttb;
+    if (!a || !w || (!out && !gather)) return fail(TTB_E_INVALID, "ttb_matmul_peer: null tensor pointer");
+    if (a_dtype != TTB_BFLOAT16) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_peer: activations must be bfloat16");
+    if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || M % 32 || K % 32 || N % 32)
+        return fail(TTB_E_INVALID, "ttb_matmul_peer: batch, M, K, N must be positive and M, K, N multiples of 32");
+    if (act < TTB_ACT_NONE || act > TTB_ACT_SILU) return fail(TTB_E_INVALID, "ttb_matmul_peer: unknown activation %d", act);
+    const int64_t rows = batch * M;
+    if (!decode_supported(w_dtype, rows, K, N))
+        return fail(TTB_E_UNSUPPORTED,
+                    "ttb_matmul_peer: decode shapes only (bfloat8_b / bfloat4_b weights, at most 256 rows, N a multiple of 128), got "
+                    "[%lld x %lld x %lld]", (long long)rows, (long long)K, (long long)N);
+    if (gather) {
+        if (gather->ranks < 2 || gather->ranks > TTB_MAX_RANKS || gather->rank < 0 || gather->rank >= gather->ranks)
+            return fail(TTB_E_INVALID, "ttb_matmul_peer: ranks must be 2..%d and rank inside it", TTB_MAX_RANKS);
+        if (out_dtype != TTB_BFLOAT16 || (flags & TTB_MM_OUT_ROW_MAJOR))
+            return fail(TTB_E_UNSUPPORTED, "ttb_matmul_peer: the gathered output is bfloat16 in tile layout");
+        if (!gather->uses) return fail(TTB_E_INVALID, "ttb_matmul_peer: null use counter");
+        for (int r = 0; r < gather->ranks; ++r)
+            if (!gather->out[r] || !gather->arrived[r] || (reinterpret_cast<uintptr_t>(gather->out[r]) & 15))
+                return fail(TTB_E_INVALID, "ttb_matmul_peer: null or misaligned peer pointer for rank %d", r);
+    } else if (out_dtype != TTB_BFLOAT16 && out_dtype != TTB_FLOAT32) {
+        return fail(TTB_E_UNSUPPORTED, "ttb_matmul_peer: output must be bfloat16 or float32");
+    }
+    if (wait && (!wait->arrived || !wait->uses || wait->ranks < 1 || wait->ranks > TTB_MAX_RANKS))
+        return fail(TTB_E_INVALID, "ttb_matmul_peer: incomplete wait description");
+    return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
+                                flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT),
+                                workspace, workspace_bytes, (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false,
+                                (cudaStream_t)stream, gather, wait);
+}
+
+namespace {
+__global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *uses, uint32_t ranks, int *status) {
+    const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(uses) * ranks;
+    const long long t0 = clock64();
+    while ((int)(ttb::ld_acquire_sys(arrived) - expected) < 0) {
+        if (clock64() - t0 > 4000000000LL) {
+            atomicCAS(status, 0, 7);
+            return;
+        }
+        __nanosleep(100);
+    }
+}
+}  // namespace
+
+extern "C" int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream) {
+    using namespace ttb;
+    if (!wait || !wait->arrived || !wait->uses || wait->ranks < 1 || wait->ranks > TTB_MAX_RANKS)
+        return fail(TTB_E_INVALID, "ttb_peer_wait: incomplete wait description");
+    int *status = nullptr;
+    if (int32_t rc = status_word_address(&status)) return rc;
+    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(wait->arrived, wait->uses, wait->ranks, status);
+    TTB_LAUNCH_CHECK("peer_wait");
+    return TTB_OK;
 }
