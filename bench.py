@@ -234,6 +234,9 @@ def load_lib():
     lib.ttb_matmul_workspace_bytes.restype = i64
     lib.ttb_matmul.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, i64, i32, i32, vp, i64, vp]
     lib.ttb_check_status.argtypes = [vp]
+    lib.ttb_matmul_peer_workspace_bytes.argtypes = [i32, i64, i64, i64, i64]
+    lib.ttb_matmul_peer_workspace_bytes.restype = i64
+    lib.ttb_matmul_peer.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, i64, i32, i32, vp, i64, vp, vp, vp]
     return lib
 
 
@@ -298,9 +301,32 @@ def run_gpu_arm(args):
     outs = [torch.empty(ROWS * N, dtype=torch.bfloat16, device=dev_t) for _, _, N, _, _ in gemms]
     gathered = [torch.empty(G * ROWS * N, dtype=torch.bfloat16, device=dev_t) if g else None for _, _, N, _, g in gemms]
     ws_bytes = max(lib.ttb_matmul_workspace_bytes(f, 1, ROWS, K, N, 0) for _, K, N, f, _ in gemms)
+    # Tensor parallel: the all-gather is the matmul's epilogue (peer stores over NVLink into every rank's copy) unless
+    # --gather nccl asks for a separate NCCL all-gather after the matmul.
+    ring = None
+    if G > 1 and args.gather == "fused":
+        from ttnn.peer import GatherRing
+        ring = GatherRing(rank, G, max(G * ROWS * N * 2 for _, _, N, _, g in gemms if g), slots=4)
+        ws_bytes = max(ws_bytes, max(lib.ttb_matmul_peer_workspace_bytes(f, 1, ROWS, K, N) for _, K, N, f, _ in gemms))
+        assert (NLAYERS * sum(1 for x in gemms if x[4])) % ring.slots == 0
     ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=dev_t)
 
+    def sweep_fused(stream_handle):
+        pending = None          # gather point whose result the next launch has to wait for
+        for layer in range(NLAYERS):
+            for i, (_, K, N, fmt, g) in enumerate(gemms):
+                slot = ring.take(G * ROWS * N * 2) if g else None
+                ck(lib.ttb_matmul_peer(acts[K][1].data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16,
+                                       1, ROWS, K, N, 0, ZEROED, ws.data_ptr(), ws_bytes,
+                                       ctypes.byref(ring.gather(slot)) if g else None,
+                                       ctypes.byref(ring.wait(pending)) if pending is not None else None, stream_handle))
+                pending = slot
+        if pending is not None:
+            ring.stream_wait(pending, stream_handle)     # the step ends when this rank holds every gathered result
+
     def sweep(stream_handle, with_gather=True):
+        if ring is not None and with_gather:
+            return sweep_fused(stream_handle)
         for layer in range(NLAYERS):
             for i, (_, K, N, fmt, g) in enumerate(gemms):
                 a = acts[K][1]
@@ -429,7 +455,7 @@ def run_gpu_arm(args):
         "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": wl.text, "parallelism": f"tp{G}", "l2": "per-step working set (%.1f GB per GPU) far exceeds the 126 MB L2" % (bytes_per_step / 1e9),
+        "config": {"workload": wl.text, "parallelism": f"tp{G}", "gather": ("none" if G == 1 else args.gather), "l2": "per-step working set (%.1f GB per GPU) far exceeds the 126 MB L2" % (bytes_per_step / 1e9),
                    "timed": "CUDA-graph replay of the whole step", "setup_s": round(t_setup, 2)},
         "clocks": clocks.summary(),
         "e2e": {"value": to_value(e2e_s), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -475,6 +501,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: all-gather in the matmul epilogue over peer memory (default) or a separate NCCL all-gather")
     ap.add_argument("--no-overlap", action="store_true", help="launch every matmul after the previous one has fully completed")
     ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
                     help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "

@@ -186,30 +186,29 @@ int32_t ttb_gather_interleave(const void *src_dev, void *dst_dev, int32_t elem_s
  * dim=-1) (ttnn/ttnn/operations/ccl.py:26-39, tt_eager/tt_dnn/op_library/all_gather/all_gather_op.cpp:18-104,
  * column-sharded weights as models/demos/llama2_70b/tt/llama_mlp_optimized.py:100-103).
  *
- * A gather point is a pair of 32-bit counters on every rank, both starting at zero: `arrived` (peers add one per
- * finished launch, over NVLink) and `uses` (only the owning rank's launches count in it). The gathered copy on a rank
- * is complete for the u-th use when arrived >= u * ranks. A later ttb_matmul_peer on the same stream that passes the
- * gather point as `wait` holds its activation loads until then (its weight streaming is not held); any other consumer
- * first runs ttb_peer_wait on the stream. Waits are bounded (about two seconds) and end in TTB_E_TIMEOUT through
- * ttb_check_status instead of hanging.
+ * A gather point is a pair of 32-bit counters on every rank, both starting at zero: `arrived`, to which every rank adds
+ * one per finished output tile (over NVLink), and `expected`, the running total of arrivals that the owning rank's own
+ * gathering launches announce (ranks x tiles per launch; all ranks launch the same shapes). The gathered copy on a rank is
+ * complete when arrived >= expected. A later ttb_matmul_peer on the same stream that passes the gather point as `wait`
+ * holds its activation loads until then (its weight streaming is not held); any other consumer first runs ttb_peer_wait on
+ * the stream. Waits are bounded (about ten seconds) and end in TTB_E_TIMEOUT through ttb_check_status instead of hanging.
  * Rules the caller keeps: all ranks issue the same sequence of gathering launches; consecutive gathering launches on a
- * stream use different gather points and different output buffers (two of each, alternating, suffice), and every gathered
- * result is waited for (by a consuming launch or ttb_peer_wait) before the next gathering launch is enqueued;
+ * stream use different gather points and different output buffers (two of each, alternating, suffice), and every gathering
+ * launch is waited for (by a consuming ttb_matmul_peer or by ttb_peer_wait) no later than in the next gathering launch on
+ * that stream, which keeps any rank from running more than one gather ahead of another;
  * peer pointers come from ttb_ipc_open on handles made by ttb_ipc_export in the owning process. Decode shapes only
- * (as ttb_matmul_decode_static), bfloat16 tiled output; a workspace is always required (ttb_matmul_peer_workspace_bytes),
- * zero at first use. */
+ * (as ttb_matmul_decode_static), bfloat16 tiled output; workspace as ttb_matmul (ttb_matmul_peer_workspace_bytes). */
 #define TTB_MAX_RANKS 8
 typedef struct ttb_peer_gather {
     int32_t ranks;                     /* 2..TTB_MAX_RANKS */
     int32_t rank;                      /* this process's position */
     void *out[TTB_MAX_RANKS];          /* the gathered tensor on every rank as mapped into this process; out[rank] is local */
     uint32_t *arrived[TTB_MAX_RANKS];  /* the gather point's arrival counter on every rank; arrived[rank] is local */
-    uint32_t *uses;                    /* the gather point's local use counter */
+    uint32_t *expected;                /* the gather point's local expected-arrivals counter */
 } ttb_peer_gather;
 typedef struct ttb_peer_wait_t {
     const uint32_t *arrived;           /* local arrival counter of the gather point that produced the activations */
-    const uint32_t *uses;              /* its local use counter */
-    uint32_t ranks;
+    const uint32_t *expected;          /* its local expected-arrivals counter */
 } ttb_peer_wait_t;
 int64_t ttb_matmul_peer_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N);
 /* `gather` and `wait` may each be NULL: without `gather` the result is an ordinary local matmul into out_dev (then

@@ -57,12 +57,12 @@ MAX_RANKS = 8
 
 class PeerGather(ctypes.Structure):
     """ttb_peer_gather of include/ttb.h."""
-    _fields_ = [("ranks", _i32), ("rank", _i32), ("out", _vp * MAX_RANKS), ("arrived", _vp * MAX_RANKS), ("uses", _vp)]
+    _fields_ = [("ranks", _i32), ("rank", _i32), ("out", _vp * MAX_RANKS), ("arrived", _vp * MAX_RANKS), ("expected", _vp)]
 
 
 class PeerWait(ctypes.Structure):
     """ttb_peer_wait_t of include/ttb.h."""
-    _fields_ = [("arrived", _vp), ("uses", _vp), ("ranks", ctypes.c_uint32)]
+    _fields_ = [("arrived", _vp), ("expected", _vp)]
 
 
 def peer_gather(rank, outs, arrived, uses):
@@ -70,13 +70,13 @@ def peer_gather(rank, outs, arrived, uses):
     g.ranks, g.rank = len(outs), rank
     for r, (o, a) in enumerate(zip(outs, arrived)):
         g.out[r], g.arrived[r] = o, a
-    g.uses = uses
+    g.expected = uses
     return g
 
 
-def peer_wait(arrived, uses, ranks):
+def peer_wait(arrived, expected):
     w = PeerWait()
-    w.arrived, w.uses, w.ranks = arrived, uses, ranks
+    w.arrived, w.expected = arrived, expected
     return w
 
 

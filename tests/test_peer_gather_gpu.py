@@ -26,9 +26,8 @@ def test_gather_epilogue_fills_every_rank(ttb, orc, G, M, K, N):
         w_ref.append(wr)
     y_ref = torch.cat([x.float() @ wr for wr in w_ref], dim=1)                      # [M, G*N]
     outs = [torch.zeros(M * G * N, dtype=torch.bfloat16, device="cuda") for _ in range(G)]
-    counters = torch.zeros(G, 64, dtype=torch.int32, device="cuda")                  # [rank]: arrived at [0], uses at [32]
+    counters = torch.zeros(G, 64, dtype=torch.int32, device="cuda")                  # [rank]: arrived at [0], expected at [32]
     nbytes = ttb.matmul_peer_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N)
-    assert nbytes >= 65536
     ws = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(G)]
     arrived = [counters[r, 0:].data_ptr() for r in range(G)]
     uses = [counters[r, 32:].data_ptr() for r in range(G)]
@@ -43,18 +42,19 @@ def test_gather_epilogue_fills_every_rank(ttb, orc, G, M, K, N):
                                                1, M, K, N, 0, cabi.MM_WORKSPACE_ZEROED | cabi.MM_WEIGHTS_RESIDENT, ws[r].data_ptr(), nbytes,
                                                ctypes.byref(g), None, None))
         # a consumer on "rank" 0 that waits for the gather point, then a plain stream wait on rank 1
-        wt = cabi.peer_wait(arrived[0], uses[0], G)
+        wt = cabi.peer_wait(arrived[0], uses[0])
         y2 = torch.empty(M * N2, dtype=torch.bfloat16, device="cuda")
         nb2 = ttb.matmul_peer_workspace_bytes(cabi.BFLOAT8_B, 1, M, K2, N2)
         ws2 = torch.zeros(nb2, dtype=torch.uint8, device="cuda")
         ttb.check(ttb.cdll.ttb_matmul_peer(outs[0].data_ptr(), cabi.BFLOAT16, w2_dev.data_ptr(), cabi.BFLOAT8_B, None, y2.data_ptr(),
                                            cabi.BFLOAT16, 1, M, K2, N2, 0, cabi.MM_WORKSPACE_ZEROED, ws2.data_ptr(), nb2, None,
                                            ctypes.byref(wt), None))
-        wt1 = cabi.peer_wait(arrived[1], uses[1], G)
+        wt1 = cabi.peer_wait(arrived[1], uses[1])
         ttb.check(ttb.cdll.ttb_peer_wait(ctypes.byref(wt1), None))
         ttb.check(ttb.check_status(None))
         c = counters.cpu()
-        assert c[:, 0].tolist() == [use * G] * G and c[:, 32].tolist() == [use] * G
+        tiles = (N // 128) * (M // (128 if M % 128 == 0 else 64 if M % 64 == 0 else 32))
+        assert c[:, 0].tolist() == [use * G * tiles] * G and c[:, 32].tolist() == [use * G * tiles] * G
         for r in range(G):
             y = ttb.untilize(outs[r], 1, M, G * N).reshape(M, G * N)
             check(y, y_ref)
@@ -62,23 +62,26 @@ def test_gather_epilogue_fills_every_rank(ttb, orc, G, M, K, N):
         y_gathered = ttb.untilize(outs[0], 1, M, G * N).reshape(M, G * N).float().cpu()
         check(ttb.untilize(y2, 1, M, N2).reshape(M, N2), y_gathered @ w2_ref)
         for r in range(G):
-            assert int(ws[r][:65536].count_nonzero().item()) == 0           # tickets and counters are back to zero
+            assert int(ws[r][:65536].count_nonzero().item()) == 0           # arrival counters of the split-K tiles are back to zero
 
 
 def test_peer_arguments_are_validated(ttb):
+    """Refusals happen before any launch. The buffers are nevertheless large enough for every shape used here, so that a
+    call that was not refused would still stay inside them."""
     import torch
-    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
-    g = cabi.peer_gather(0, [buf.data_ptr()], [buf.data_ptr()], buf.data_ptr())      # one rank only: refused
-    rc = ttb.cdll.ttb_matmul_peer(buf.data_ptr(), cabi.BFLOAT16, buf.data_ptr(), cabi.BFLOAT8_B, None, None, cabi.BFLOAT16, 1, 32, 64, 128,
-                                  0, 0, buf.data_ptr(), 1 << 16, ctypes.byref(g), None, None)
+    buf = torch.zeros(4 << 20, dtype=torch.uint8, device="cuda")
+    M, K, N = 32, 4096, 128
+    args = (buf.data_ptr(), cabi.BFLOAT16, buf.data_ptr(), cabi.BFLOAT8_B, None, None)
+    g1 = cabi.peer_gather(0, [buf.data_ptr()], [buf.data_ptr()], buf.data_ptr())      # one rank only
+    rc = ttb.cdll.ttb_matmul_peer(*args, cabi.BFLOAT16, 1, M, K, N, 0, 0, buf.data_ptr(), 4 << 20, ctypes.byref(g1), None, None)
     assert rc == -1 and b"ranks" in ttb.cdll.ttb_last_error()
     g = cabi.peer_gather(0, [buf.data_ptr(), buf.data_ptr()], [buf.data_ptr(), buf.data_ptr()], buf.data_ptr())
-    rc = ttb.cdll.ttb_matmul_peer(buf.data_ptr(), cabi.BFLOAT16, buf.data_ptr(), cabi.BFLOAT8_B, None, None, cabi.FLOAT32, 1, 32, 64, 128,
-                                  0, 0, buf.data_ptr(), 1 << 16, ctypes.byref(g), None, None)
+    rc = ttb.cdll.ttb_matmul_peer(*args, cabi.FLOAT32, 1, M, K, N, 0, 0, buf.data_ptr(), 4 << 20, ctypes.byref(g), None, None)
     assert rc == -3 and b"bfloat16" in ttb.cdll.ttb_last_error()
-    rc = ttb.cdll.ttb_matmul_peer(buf.data_ptr(), cabi.BFLOAT16, buf.data_ptr(), cabi.BFLOAT8_B, None, None, cabi.BFLOAT16, 1, 32, 64, 128,
-                                  0, 0, buf.data_ptr(), 16, ctypes.byref(g), None, None)
-    assert rc == -4                                                                       # workspace too small: nothing launched
-    rc = ttb.cdll.ttb_matmul_peer(buf.data_ptr(), cabi.BFLOAT16, buf.data_ptr(), cabi.BFLOAT8_B, None, None, cabi.BFLOAT16, 1, 512, 64, 128,
-                                  0, 0, buf.data_ptr(), 1 << 16, ctypes.byref(g), None, None)
+    assert ttb.matmul_peer_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N) > 16              # this shape splits K
+    rc = ttb.cdll.ttb_matmul_peer(*args, cabi.BFLOAT16, 1, M, K, N, 0, 0, buf.data_ptr(), 16, ctypes.byref(g), None, None)
+    assert rc == -4                                                                       # workspace too small
+    rc = ttb.cdll.ttb_matmul_peer(*args, cabi.BFLOAT16, 1, 512, 64, 128, 0, 0, buf.data_ptr(), 4 << 20, ctypes.byref(g), None, None)
     assert rc == -3                                                                       # not a decode shape
+    torch.cuda.synchronize()
+    assert int(buf.count_nonzero().item()) == 0                                          # nothing ran

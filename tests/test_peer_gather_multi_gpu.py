@@ -1,0 +1,21 @@
+"""ttb_matmul_peer across real GPUs (skipped on a single-GPU machine; the single-GPU emulation in
+test_peer_gather_gpu.py covers the address arithmetic there). Ranks run as child processes under torchrun."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_gather_epilogue_between_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29731", os.path.join(HERE, "peer_gather_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "PEER-OK 0" in r.stdout and "PEER-OK 1" in r.stdout

@@ -25,22 +25,20 @@ struct DecodeArgs {
     int64_t out_n0, out_N;
     int out_Nt;
     // ---- gather epilogue (ranks > 1): every finished tile is also stored into the same columns of the other ranks'
-    // copies of the output; the block that finishes last tells every rank that this rank's slice is complete ----
+    // copies of the output, then counted on every rank's arrival counter ----
     int ranks, rank;
     uint16_t *peer_out[TTB_MAX_RANKS];
     unsigned *peer_arrived[TTB_MAX_RANKS];
-    unsigned *uses;       // this rank's count of launches that used the gather point
-    int *grid_ticket;     // counts this launch's finished tiles
-    int tiles_total;
-    // ---- wait before the first activation load: `wait_arrived` must reach *wait_uses * wait_per_use ----
+    unsigned *expected;        // this rank's running total of arrivals its gather point will have seen after this launch
+    unsigned launch_arrivals;  // ranks x output tiles per rank
+    // ---- wait before the first activation load: *wait_arrived must reach *wait_expected ----
     const unsigned *wait_arrived;
-    const unsigned *wait_uses;
-    unsigned wait_per_use;
+    const unsigned *wait_expected;
 };
 
 // System-scope release / acquire on counters that other GPUs write or read over NVLink.
-__device__ __forceinline__ void red_release_sys_add(unsigned *addr, unsigned v) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+__device__ __forceinline__ void red_relaxed_sys_add(unsigned *addr, unsigned v) {
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *addr) {
     unsigned v;
@@ -51,9 +49,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *addr) {
 // Bounded wait for the peers' slices of a gathered activation (one lane calls it). Returns false and raises the
 // status word after `limit_cycles`, or as soon as another thread of the block gave up.
 __device__ __forceinline__ bool peer_wait(const DecodeArgs &p, volatile int *abort_flag, int code,
-                                          long long limit_cycles = 4000000000LL) {
+                                          long long limit_cycles = 20000000000LL) {
     if (!p.wait_arrived) return true;
-    const unsigned expected = *reinterpret_cast<const volatile unsigned *>(p.wait_uses) * p.wait_per_use;
+    const unsigned expected = *reinterpret_cast<const volatile unsigned *>(p.wait_expected);
     const long long t0 = clock64();
     for (unsigned spin = 1;; ++spin) {
         if ((int)(ld_acquire_sys(p.wait_arrived) - expected) >= 0) return true;
@@ -128,10 +126,13 @@ __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const floa
     TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, v, row0, col0, n, stage));
 }
 
-// Gather epilogue, called by all `nthreads` epilogue threads of a block (named barrier `bar_id`) after the block has
-// stored its finished [NB x 128] slab locally and into `stage`: sends the slab to every other rank with 16-byte stores
-// (each 32-row tile row of the slab is 8 KiB contiguous in the tiled output), then counts the tile as finished; the
-// block that finishes the launch's last tile signals every rank's arrival counter.
+// Gather epilogue, called by all `nthreads` epilogue threads of a block after the block has stored its finished
+// [NB x 128] slab locally and into `stage`: sends the slab to every other rank with 16-byte stores (each 32-row tile row
+// of the slab is 8 KiB contiguous in the tiled output) and counts the tile on every rank's arrival counter.
+// Cost of the pieces, measured between two B200s over NVLink: a system-scope fence is ~1.7 us with nothing outstanding and
+// ~3.6 us behind remote stores, a release-flavoured remote reduction costs as much as a fence, a relaxed one ~40 ns, and
+// a flag needs ~1.25 us to be seen by the peer. Hence exactly one fence per tile: all threads store, a barrier orders
+// them before thread 0, whose single fence (cumulative) precedes relaxed reductions on the counters.
 template <int NB>
 __device__ __forceinline__ void gather_send(const DecodeArgs &p, const uint16_t *stage, int64_t row0, int ntile, int tid, int nthreads) {
     asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");   // the slab is complete in shared memory
@@ -144,15 +145,10 @@ __device__ __forceinline__ void gather_send(const DecodeArgs &p, const uint16_t 
             for (int i = tid; i < kVecPerRow; i += nthreads) dst[i] = src[rt * kVecPerRow + i];
         }
     }
-    __threadfence_system();
     asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
     if (tid == 0) {
-        const int done = atomicAdd(p.grid_ticket, 1);
-        if (done == p.tiles_total - 1) {
-            *p.grid_ticket = 0;                                     // ready for the next launch
-            __threadfence_system();
-            for (int r = 0; r < p.ranks; ++r) red_release_sys_add(p.peer_arrived[r], 1u);
-        }
+        __threadfence_system();
+        for (int step = 1; step <= p.ranks; ++step) red_relaxed_sys_add(p.peer_arrived[(p.rank + step) % p.ranks], 1u);
     }
 }
 

@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_kernel(const 
         const int tid = threadIdx.x;
         grid_dep_wait();
         uint16_t *const stage = p.ranks > 1 ? reinterpret_cast<uint16_t *>(smem + L::pk) : nullptr;   // the packed ring is idle by now
-        if (p.ranks > 1 && tid == 0 && blockIdx.x + blockIdx.y + blockIdx.z == 0) *p.uses = *p.uses + 1;
+        if (p.ranks > 1 && tid == 0 && blockIdx.x + blockIdx.y + blockIdx.z == 0) *p.expected = *p.expected + p.launch_arrivals;
         {
             int good = ok ? 1 : 0;
             good = __shfl_sync(0xffffffffu, good, 0);   // lane 0 ran the single-thread roles
@@ -506,7 +506,7 @@ static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : 
 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes - 64;   // the last counter is the launch-wide ticket
+           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes;
 }
 
 // Chooses how many blocks share one output tile along K so that the grid fills the 148 SMs in whole waves.
@@ -558,10 +558,7 @@ int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
     return pb ? kCounterBytes + kAccumBytes + pb : 0;
 }
 
-// The gather epilogue always needs the counters (launch-wide ticket), also when K is not split.
-int64_t decode_workspace_bytes_peer(int64_t rows, int64_t K, int64_t N) {
-    return kCounterBytes + kAccumBytes + decode_partial_bytes(rows, K, N);
-}
+int64_t decode_workspace_bytes_peer(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes(rows, K, N); }
 
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
@@ -581,7 +578,7 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
     p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !decode_accumulate_ok(rows, N);
     p.out_n0 = 0; p.out_N = N; p.out_Nt = p.Nt;
     if (wait) {
-        p.wait_arrived = wait->arrived; p.wait_uses = wait->uses; p.wait_per_use = wait->ranks;
+        p.wait_arrived = wait->arrived; p.wait_expected = wait->expected;
     }
     if (gather) {
         p.ranks = gather->ranks; p.rank = gather->rank;
@@ -591,11 +588,11 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
             p.peer_out[r] = (uint16_t *)gather->out[r];
             p.peer_arrived[r] = gather->arrived[r];
         }
-        p.uses = gather->uses;
-        p.tiles_total = tiles;
+        p.expected = gather->expected;
+        p.launch_arrivals = (unsigned)(gather->ranks * tiles);
     }
     if (int32_t rc = status_word_address(&p.status)) return rc;
-    if (p.splits > 1 || gather) {
+    if (p.splits > 1) {
         const int64_t need = compact   ? decode_workspace_bytes_compact(rows, K, N)
                              : gather ? decode_workspace_bytes_peer(rows, K, N)
                                       : decode_workspace_bytes(rows, K, N);
@@ -605,7 +602,6 @@ int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const vo
         if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
             return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
         p.counters = (int *)workspace;
-        p.grid_ticket = (int *)workspace + (kCounterBytes / 4 - 1);
         p.accum = (float *)((uint8_t *)workspace + kCounterBytes);
         p.partial = (float *)((uint8_t *)workspace + kCounterBytes + (compact ? 0 : kAccumBytes));
         if (!counters_are_zero) {
@@ -724,14 +720,14 @@ extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w
             return fail(TTB_E_INVALID, "ttb_matmul_peer: ranks must be 2..%d and rank inside it", TTB_MAX_RANKS);
         if (out_dtype != TTB_BFLOAT16 || (flags & TTB_MM_OUT_ROW_MAJOR))
             return fail(TTB_E_UNSUPPORTED, "ttb_matmul_peer: the gathered output is bfloat16 in tile layout");
-        if (!gather->uses) return fail(TTB_E_INVALID, "ttb_matmul_peer: null use counter");
+        if (!gather->expected) return fail(TTB_E_INVALID, "ttb_matmul_peer: null expected-arrivals counter");
         for (int r = 0; r < gather->ranks; ++r)
             if (!gather->out[r] || !gather->arrived[r] || (reinterpret_cast<uintptr_t>(gather->out[r]) & 15))
                 return fail(TTB_E_INVALID, "ttb_matmul_peer: null or misaligned peer pointer for rank %d", r);
     } else if (out_dtype != TTB_BFLOAT16 && out_dtype != TTB_FLOAT32) {
         return fail(TTB_E_UNSUPPORTED, "ttb_matmul_peer: output must be bfloat16 or float32");
     }
-    if (wait && (!wait->arrived || !wait->uses || wait->ranks < 1 || wait->ranks > TTB_MAX_RANKS))
+    if (wait && (!wait->arrived || !wait->expected))
         return fail(TTB_E_INVALID, "ttb_matmul_peer: incomplete wait description");
     return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
                                 flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT),
@@ -740,11 +736,11 @@ extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w
 }
 
 namespace {
-__global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *uses, uint32_t ranks, int *status) {
-    const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(uses) * ranks;
+__global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *expected_ptr, int *status) {
+    const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(expected_ptr);
     const long long t0 = clock64();
     while ((int)(ttb::ld_acquire_sys(arrived) - expected) < 0) {
-        if (clock64() - t0 > 4000000000LL) {
+        if (clock64() - t0 > 20000000000LL) {
             atomicCAS(status, 0, 7);
             return;
         }
@@ -755,11 +751,10 @@ __global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *uses, 
 
 extern "C" int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream) {
     using namespace ttb;
-    if (!wait || !wait->arrived || !wait->uses || wait->ranks < 1 || wait->ranks > TTB_MAX_RANKS)
-        return fail(TTB_E_INVALID, "ttb_peer_wait: incomplete wait description");
+    if (!wait || !wait->arrived || !wait->expected) return fail(TTB_E_INVALID, "ttb_peer_wait: incomplete wait description");
     int *status = nullptr;
     if (int32_t rc = status_word_address(&status)) return rc;
-    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(wait->arrived, wait->uses, wait->ranks, status);
+    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(wait->arrived, wait->expected, status);
     TTB_LAUNCH_CHECK("peer_wait");
     return TTB_OK;
 }
