@@ -237,6 +237,9 @@ def load_lib():
     lib.ttb_matmul_peer_workspace_bytes.argtypes = [i32, i64, i64, i64, i64]
     lib.ttb_matmul_peer_workspace_bytes.restype = i64
     lib.ttb_matmul_peer.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, i64, i32, i32, vp, i64, vp, vp, vp]
+    lib.ttb_matmul_multi_workspace_bytes.argtypes = [i32, i64, i64, i64, i32, vp]
+    lib.ttb_matmul_multi_workspace_bytes.restype = i64
+    lib.ttb_matmul_multi.argtypes = [vp, i32, i32, vp, i32, vp, vp, i32, i64, i64, i64, vp, i32, i32, vp, i64, vp, vp, vp]
     return lib
 
 
@@ -307,34 +310,55 @@ def run_gpu_arm(args):
     if G > 1 and args.gather == "fused":
         from ttnn.peer import GatherRing
         ring = GatherRing(rank, G, max(G * ROWS * N * 2 for _, _, N, _, g in gemms if g), slots=4)
-        ws_bytes = max(ws_bytes, max(lib.ttb_matmul_peer_workspace_bytes(f, 1, ROWS, K, N) for _, K, N, f, _ in gemms))
         assert (NLAYERS * sum(1 for x in gemms if x[4])) % ring.slots == 0
+    # Launch groups: matmuls of a layer that multiply the same activation go out as one launch (q/k/v; w1/w3), unless
+    # --no-group asks for one launch per weight. Only the first weight of a group is ever gathered.
+    SHARE = {"wq": "qkv", "wk": "qkv", "wv": "qkv", "w1": "w13", "w3": "w13"}
+    groups = []
+    for i, (name, K, N, fmt, g) in enumerate(gemms):
+        key = None if args.no_group else SHARE.get(name)
+        if key is not None and groups and groups[-1][0] == key and len(groups[-1][1]) < 4 and not g:
+            groups[-1][1].append(i)
+        else:
+            groups.append((key, [i]))
+    groups = [idxs for _, idxs in groups]
+    arrays = {}
+    for idxs in groups:
+        arr_n = (ctypes.c_int64 * len(idxs))(*[gemms[i][2] for i in idxs])
+        ws_bytes = max(ws_bytes, lib.ttb_matmul_multi_workspace_bytes(gemms[idxs[0]][3], 1, ROWS, gemms[idxs[0]][1], len(idxs), arr_n))
     ws = torch.zeros(max(ws_bytes, 16), dtype=torch.uint8, device=dev_t)
 
-    def sweep_fused(stream_handle):
-        pending = None          # gather point whose result the next launch has to wait for
-        for layer in range(NLAYERS):
-            for i, (_, K, N, fmt, g) in enumerate(gemms):
-                slot = ring.take(G * ROWS * N * 2) if g else None
-                ck(lib.ttb_matmul_peer(acts[K][1].data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16,
-                                       1, ROWS, K, N, 0, ZEROED, ws.data_ptr(), ws_bytes,
-                                       ctypes.byref(ring.gather(slot)) if g else None,
-                                       ctypes.byref(ring.wait(pending)) if pending is not None else None, stream_handle))
-                pending = slot
-        if pending is not None:
-            ring.stream_wait(pending, stream_handle)     # the step ends when this rank holds every gathered result
+    def group_arrays(layer, idxs):
+        key = (layer, idxs[0])
+        if key not in arrays:
+            n = len(idxs)
+            arrays[key] = ((ctypes.c_void_p * n)(*[weights[layer][i].data_ptr() for i in idxs]),
+                           (ctypes.c_void_p * n)(*[outs[i].data_ptr() for i in idxs]),
+                           (ctypes.c_int64 * n)(*[gemms[i][2] for i in idxs]))
+        return arrays[key]
 
     def sweep(stream_handle, with_gather=True):
-        if ring is not None and with_gather:
-            return sweep_fused(stream_handle)
+        fused = ring is not None and with_gather
+        pending = None          # gather point whose result the next launch has to wait for
         for layer in range(NLAYERS):
-            for i, (_, K, N, fmt, g) in enumerate(gemms):
-                a = acts[K][1]
-                ck(lib.ttb_matmul(a.data_ptr(), BF16, weights[layer][i].data_ptr(), fmt, None, outs[i].data_ptr(), BF16, 1, ROWS, K, N,
-                                  0, ZEROED, ws.data_ptr(), ws_bytes, stream_handle))
-                if g and G > 1 and with_gather:
+            for idxs in groups:
+                _, K, N, fmt, g = gemms[idxs[0]]
+                arr_w, arr_o, arr_n = group_arrays(layer, idxs)
+                if ROWS > 256:      # prefill shape: the single-weight entry point (tensor-bound kernel)
+                    ck(lib.ttb_matmul(acts[K][1].data_ptr(), BF16, weights[layer][idxs[0]].data_ptr(), fmt, None, outs[idxs[0]].data_ptr(),
+                                      BF16, 1, ROWS, K, N, 0, ZEROED, ws.data_ptr(), ws_bytes, stream_handle))
+                    continue
+                slot = ring.take(G * ROWS * N * 2) if (fused and g) else None
+                ck(lib.ttb_matmul_multi(acts[K][1].data_ptr(), BF16, len(idxs), arr_w, fmt, None, arr_o, BF16, 1, ROWS, K, arr_n,
+                                        0, ZEROED, ws.data_ptr(), ws_bytes,
+                                        ctypes.byref(ring.gather(slot)) if slot is not None else None,
+                                        ctypes.byref(ring.wait(pending)) if pending is not None else None, stream_handle))
+                pending = slot
+                if g and G > 1 and with_gather and not fused:
                     # tiled [32, N/G] shards are whole tile runs: the rank-major gather is the tiled [32, N] tensor
-                    dist.all_gather_into_tensor(gathered[i], outs[i])
+                    dist.all_gather_into_tensor(gathered[idxs[0]], outs[idxs[0]])
+        if pending is not None:
+            ring.stream_wait(pending, stream_handle)     # the step ends when this rank holds every gathered result
 
     def capture(with_gather):
         side = torch.cuda.Stream()
@@ -343,6 +367,7 @@ def run_gpu_arm(args):
             sweep(side.cuda_stream, with_gather)      # warm-up outside capture (lazy module loading, NCCL channels)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        ck(lib.ttb_check_status(None))                 # a kernel whose bounded wait ran out ends the run here, not after K steps
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             sweep(torch.cuda.current_stream().cuda_stream, with_gather)
@@ -387,7 +412,7 @@ def run_gpu_arm(args):
         ms_mm = timed_replays(graph_mm, args.steps, 1) / args.steps
     else:
         ms_mm = ms_step
-    launches_per_step = NLAYERS * len(gemms)
+    launches_per_step = NLAYERS * len(groups)
     bytes_per_step = wl.bytes_per_layer() * NLAYERS
     achieved = bytes_per_step / (ms_mm * 1e-3) / 1e9
     flops_per_step = wl.flops_per_layer() * NLAYERS
@@ -455,16 +480,17 @@ def run_gpu_arm(args):
         "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": wl.text, "parallelism": f"tp{G}", "gather": ("none" if G == 1 else args.gather), "l2": "per-step working set (%.1f GB per GPU) far exceeds the 126 MB L2" % (bytes_per_step / 1e9),
+        "config": {"workload": wl.text, "parallelism": f"tp{G}", "gather": ("none" if G == 1 else args.gather),
+                   "launch_groups": [[gemms[i][0] for i in idxs] for idxs in groups], "l2": "per-step working set (%.1f GB per GPU) far exceeds the 126 MB L2" % (bytes_per_step / 1e9),
                    "timed": "CUDA-graph replay of the whole step", "setup_s": round(t_setup, 2)},
         "clocks": clocks.summary(),
         "e2e": {"value": to_value(e2e_s), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3,
-                "api": f"ttnn.from_torch -> ttnn.linear x{launches_per_step} (+ ttnn.all_gather) -> ttnn.to_torch"},
+                "api": f"ttnn.from_torch -> ttnn.linear x{NLAYERS * len(gemms)} (+ ttnn.all_gather) -> ttnn.to_torch"},
         "gpu_launches": launches_per_step * (2 if tensor_bound else 1) * args.steps,
         "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s" if tensor_bound else "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_src, "peak_kind": peak_kind, "kernel": "matmul_prefill_kernel" if tensor_bound else "matmul_decode_kernel",
+                     "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_src, "peak_kind": peak_kind, "kernel": "matmul_prefill_kernel" if tensor_bound else "matmul_decode_stream_kernel",
                      "launches_per_step": launches_per_step, "algorithmic_bytes_per_step": bytes_per_step,
                      "avg_launch_us": ms_mm * 1e3 / launches_per_step},
     }
@@ -503,6 +529,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather in the matmul epilogue over peer memory (default) or a separate NCCL all-gather")
+    ap.add_argument("--no-group", action="store_true", help="one launch per weight instead of one per group of weights that share an activation")
     ap.add_argument("--no-overlap", action="store_true", help="launch every matmul after the previous one has fully completed")
     ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
                     help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "

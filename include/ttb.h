@@ -162,6 +162,8 @@ int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_
  *     cleared on `stream` by each call. Two calls that overlap on the GPU (different streams, no dependency) race on
  *     it: serialise them.
  * `flags` accepts TTB_MM_A_ROW_MAJOR and TTB_MM_OUT_ROW_MAJOR. */
+/* Scratch a shape would need from the built-in array (it holds 16 MiB + 64 KiB); -1 for shapes that are not decode shapes. */
+int64_t ttb_matmul_decode_static_scratch_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N);
 int32_t ttb_matmul_decode_static(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
                                  void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
                                  int32_t activation, int32_t flags, void *stream);
@@ -199,6 +201,7 @@ int32_t ttb_gather_interleave(const void *src_dev, void *dst_dev, int32_t elem_s
  * peer pointers come from ttb_ipc_open on handles made by ttb_ipc_export in the owning process. Decode shapes only
  * (as ttb_matmul_decode_static), bfloat16 tiled output; workspace as ttb_matmul (ttb_matmul_peer_workspace_bytes). */
 #define TTB_MAX_RANKS 8
+#define TTB_MAX_GROUP 4 /* weights per ttb_matmul_multi launch */
 typedef struct ttb_peer_gather {
     int32_t ranks;                     /* 2..TTB_MAX_RANKS */
     int32_t rank;                      /* this process's position */
@@ -217,6 +220,19 @@ int32_t ttb_matmul_peer(const void *a_dev, int32_t a_dtype, const void *w_dev, i
                         void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
                         int32_t activation, int32_t flags, void *workspace_dev, int64_t workspace_bytes,
                         const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream);
+/* Several weights that multiply the same activation, in one launch: out[j] = act(a x w[j] + bias[j]), j < count <=
+ * TTB_MAX_GROUP, every weight [K, N[j]] in the same block-float format. What the reference's models issue as separate
+ * matmuls on one input - the q / k / v projections (models/demos/mistral7b/tt/mistral_attention.py:72-99, which fuses them
+ * by concatenating the weights) and the w1 / w3 projections of the gated MLP (mistral_mlp.py:51-73,
+ * llama2_70b/tt/llama_mlp_optimized.py:165-193) - becomes one pass of one persistent kernel over all their tiles; the
+ * weights stay separate tensors. Decode shapes only. `bias` may be NULL or hold NULL entries. `gather` (may be NULL)
+ * applies to weight 0 only: its result goes to gather->out[...] on every rank and out[0] is ignored; `wait` as in
+ * ttb_matmul_peer. Results are identical to `count` calls of ttb_matmul. */
+int64_t ttb_matmul_multi_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N);
+int32_t ttb_matmul_multi(const void *a_dev, int32_t a_dtype, int32_t count, const void *const *w_dev, int32_t w_dtype,
+                         const void *const *bias_dev, void *const *out_dev, int32_t out_dtype, int64_t batch, int64_t M,
+                         int64_t K, const int64_t *N, int32_t activation, int32_t flags, void *workspace_dev,
+                         int64_t workspace_bytes, const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream);
 /* Holds `stream` until the gather point's current use is complete on this rank (bounded). */
 int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream);
 /* CUDA IPC plumbing for the peer pointers: `handle` is a 64-byte buffer. `ptr_dev` must be the start of an allocation

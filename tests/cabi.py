@@ -42,11 +42,14 @@ _SIGS = {
     "ttb_matmul_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64, _i32]),
     "ttb_matmul": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp]),
     "ttb_matmul_decode_static": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "ttb_matmul_decode_static_scratch_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_check_status": (_i32, [_vp]),
     "ttb_gather_interleave": (_i32, [_vp, _vp, _i32, _i32, _i64, _i64, _vp]),
     "ttb_matmul_peer_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_matmul_peer": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_peer_wait": (_i32, [_vp, _vp]),
+    "ttb_matmul_multi_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i32, _vp]),
+    "ttb_matmul_multi": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_ipc_export": (_i32, [_vp, _vp]),
     "ttb_ipc_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "ttb_ipc_close": (_i32, [_vp]),

@@ -279,3 +279,58 @@ def test_overlapped_launches_keep_their_dependencies(ttb, orc, tmem, M):
         for a, b in zip(plain, fast):
             assert torch.equal(a, b)
     assert int(ws[:65536].count_nonzero().item()) == 0
+
+
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
+@pytest.mark.parametrize("M,K,Ns", [(32, 2048, [512, 128, 256]), (64, 1024, [128, 384]), (32, 8192, [1024, 128, 128]), (128, 512, [256, 128]),
+                                     (96, 4096, [256, 256, 128, 128])])
+def test_several_weights_in_one_launch(ttb, orc, w_dtype, M, K, Ns):
+    """ttb_matmul_multi: every output equals the single-weight result (same tolerances against the fp32 reference), with
+    per-weight bias, a fused activation, and the scratch left clean for the next launch."""
+    import ctypes
+    import torch
+    x = vectors.randn(41, (M, K), 1.0).bfloat16()
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    w_devs, w_refs, biases, bias_devs, outs = [], [], [], [], []
+    for j, N in enumerate(Ns):
+        _, wd, wr = make_case(ttb, orc, 50 + j, M, K, N, w_dtype)
+        w_devs.append(wd)
+        w_refs.append(wr)
+        b = vectors.randn(60 + j, (1, N), 0.5).bfloat16()
+        biases.append(b)
+        bias_devs.append(ttb.tilize(torch.cat([b, torch.zeros(31, N, dtype=torch.bfloat16)]).cuda(), 1, 32, N) if j != 1 else None)
+        outs.append(torch.empty(M * N, dtype=torch.bfloat16, device="cuda"))
+    n = len(Ns)
+    arr_w = (ctypes.c_void_p * n)(*[t.data_ptr() for t in w_devs])
+    arr_b = (ctypes.c_void_p * n)(*[t.data_ptr() if t is not None else None for t in bias_devs])
+    arr_o = (ctypes.c_void_p * n)(*[t.data_ptr() for t in outs])
+    arr_n = (ctypes.c_int64 * n)(*Ns)
+    nbytes = ttb.matmul_multi_workspace_bytes(w_dtype, 1, M, K, n, arr_n)
+    ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    for rep in range(2):
+        ttb.check(ttb.cdll.ttb_matmul_multi(a.data_ptr(), cabi.BFLOAT16, n, arr_w, w_dtype, arr_b, arr_o, cabi.BFLOAT16, 1, M, K, arr_n,
+                                            cabi.ACT_SILU, cabi.MM_WORKSPACE_ZEROED | cabi.MM_WEIGHTS_RESIDENT, ws.data_ptr(), nbytes, None, None, None))
+        ttb.check(ttb.check_status(None))
+        for j, N in enumerate(Ns):
+            y_ref = x.float() @ w_refs[j]
+            if j != 1:
+                y_ref = y_ref + biases[j].float()
+            check(ttb.untilize(outs[j], 1, M, N).reshape(M, N), act_ref(y_ref, cabi.ACT_SILU))
+        if nbytes:
+            assert int(ws[: min(nbytes, 65536 + (16 << 20))].count_nonzero().item()) == 0
+
+
+def test_multi_arguments_are_validated(ttb):
+    import ctypes
+    import torch
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
+    ns = (ctypes.c_int64 * 2)(128, 96)                    # 96 is not a multiple of 128: not a decode shape
+    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 2, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 32, 64, ns, 0, 0,
+                                   buf.data_ptr(), 1 << 20, None, None, None)
+    assert rc == -3
+    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 5, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 32, 64, ns, 0, 0,
+                                   buf.data_ptr(), 1 << 20, None, None, None)
+    assert rc == -1 and b"count" in ttb.cdll.ttb_last_error()
+    torch.cuda.synchronize()
+    assert int(buf.count_nonzero().item()) == 0

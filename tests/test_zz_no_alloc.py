@@ -60,12 +60,15 @@ def test_static_scratch_variant_refuses_what_it_cannot_serve(ttb):
     rc = ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
                                            1, 512, 256, 128, 0, 0, None)
     assert rc == -3 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
-    # a reduction that would need more scratch than the built-in array: refused before anything is launched. The size
-    # check comes first so that a planner change can never turn this into a launch on the small buffers above.
-    # (The regular entry point's figure includes its 16 MiB accumulation region, which the built-in scratch does without.)
-    assert ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, 256, 65536, 4096, 0) - (16 << 20) > (16 << 20) + 65536
-    rc = ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
-                                           1, 256, 65536, 4096, 0, 0, None)
+    # A reduction that needs more scratch than the built-in array is refused before anything is launched. The library's own
+    # figure is checked first, and the operands are full-sized for the shape, so that a planner change can neither turn
+    # this into a launch that the test did not expect nor into one that leaves its buffers.
+    M2, K2, N2 = 256, 1024, 7680
+    assert ttb.matmul_decode_static_scratch_bytes(cabi.BFLOAT8_B, 1, M2, K2, N2) > (16 << 20) + 65536
+    a2, w2 = _operands(ttb, M2, K2, N2, cabi.BFLOAT8_B, 72)
+    out2 = torch.empty(M2 * N2, dtype=torch.bfloat16, device="cuda")
+    rc = ttb.cdll.ttb_matmul_decode_static(a2.data_ptr(), cabi.BFLOAT16, w2.data_ptr(), cabi.BFLOAT8_B, None, out2.data_ptr(), cabi.BFLOAT16,
+                                           1, M2, K2, N2, 0, 0, None)
     assert rc == -4 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
     rc = ttb.cdll.ttb_matmul_decode_static(None, cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
                                            1, 32, 256, 128, 0, 0, None)

@@ -34,7 +34,28 @@ struct DecodeArgs {
     // ---- wait before the first activation load: *wait_arrived must reach *wait_expected ----
     const unsigned *wait_arrived;
     const unsigned *wait_expected;
+    // ---- streamed decomposition (matmul_decode_stream.cu): up to four weights share the activation; their 128-column
+    // tiles form one list (per row chunk). sk_grid persistent blocks first take whole tiles, round by round, then share
+    // the remaining tiles, whose K-blocks are cut into units of sk_gran K-blocks and dealt out evenly, in order ----
+    int nprob;
+    const uint8_t *wv[TTB_MAX_GROUP];
+    const uint16_t *biasv[TTB_MAX_GROUP];
+    void *outv[TTB_MAX_GROUP];
+    int64_t Nv[TTB_MAX_GROUP];
+    int tstart[TTB_MAX_GROUP + 1];   // first 128-column tile of each weight in the list; tstart[nprob] = tiles per row chunk
+    int sk_grid, sk_gran, sk_upt;    // blocks, K-blocks per unit, units per tile
+    int sk_waves, sk_rem_tile0;      // rounds of whole tiles (tile = round * sk_grid + block), first tile of the split remainder
+    long long sk_units;              // units of the remainder
 };
+
+// Where a finished tile goes: one weight's output tensor (or its slice of a gathered tensor).
+struct OutView {
+    void *out;
+    const uint16_t *bias;
+    int64_t n0, N;   // first column of the slice inside the output tensor, and the output tensor's columns
+    int Nt;          // 32-column tiles per row of the output tensor
+};
+__device__ __forceinline__ OutView out_view_of(const DecodeArgs &p) { return OutView{p.out, p.bias, p.out_n0, p.out_N, p.out_Nt}; }
 
 // System-scope release / acquire on counters that other GPUs write or read over NVLink.
 __device__ __forceinline__ void red_relaxed_sys_add(unsigned *addr, unsigned v) {
@@ -92,18 +113,18 @@ __device__ __forceinline__ int act_chunk_step(const DecodeArgs &p) { return p.a_
 // `stage` (gather epilogue only, bf16 tiled output) receives a copy at the element's position inside the block's own
 // [rows of the block, 128 columns] tiled slab, from where whole tiles are sent to the other ranks.
 template <int ACT>
-__device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n,
-                                                   uint16_t *stage) {
-    const float bias = p.bias ? bias_at(p.bias, n) : 0.0f;
+__device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const OutView &ov, const float (&v)[16], int64_t row0, int col0,
+                                                   int64_t n, uint16_t *stage) {
+    const float bias = ov.bias ? bias_at(ov.bias, n) : 0.0f;
     const int64_t r0 = row0 + col0;
-    const int64_t base = p.out_row_major ? r0 * p.out_N + p.out_n0 + n : tiled_offset(r0, p.out_n0 + n, p.out_Nt);
-    const int64_t stride = p.out_row_major ? p.out_N : 16;
+    const int64_t base = p.out_row_major ? r0 * ov.N + ov.n0 + n : tiled_offset(r0, ov.n0 + n, ov.Nt);
+    const int64_t stride = p.out_row_major ? ov.N : 16;
     if (p.out_dtype == TTB_FLOAT32) {
-        float *o = reinterpret_cast<float *>(p.out) + base;
+        float *o = reinterpret_cast<float *>(ov.out) + base;
 #pragma unroll
         for (int j = 0; j < 16; ++j) o[j * stride] = apply_activation_t<ACT>(v[j] + bias);
     } else {
-        uint16_t *o = reinterpret_cast<uint16_t *>(p.out) + base;
+        uint16_t *o = reinterpret_cast<uint16_t *>(ov.out) + base;
         if (stage) {
             const int c = (int)(n & 127);
             uint16_t *s = stage + ((col0 >> 5) * 4 + (c >> 5)) * 1024 + 256 * (2 * ((col0 & 31) >> 4) + ((c & 31) >> 4)) + (c & 15);
@@ -121,9 +142,14 @@ __device__ __forceinline__ void finish_and_store_t(const DecodeArgs &p, const fl
 }
 
 template <int NB>
+__device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const OutView &ov, const float (&v)[16], int64_t row0, int col0,
+                                                 int64_t n, uint16_t *stage = nullptr) {
+    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, ov, v, row0, col0, n, stage));
+}
+template <int NB>
 __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n,
                                                  uint16_t *stage = nullptr) {
-    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, v, row0, col0, n, stage));
+    finish_and_store<NB>(p, out_view_of(p), v, row0, col0, n, stage);
 }
 
 // Gather epilogue, called by all `nthreads` epilogue threads of a block after the block has stored its finished
@@ -135,6 +161,7 @@ __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const floa
 // them before thread 0, whose single fence (cumulative) precedes relaxed reductions on the counters.
 template <int NB>
 __device__ __forceinline__ void gather_send(const DecodeArgs &p, const uint16_t *stage, int64_t row0, int ntile, int tid, int nthreads) {
+    // (the gathered tensor is the output of the first weight of the launch: p.out_n0 / p.out_Nt describe it)
     asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");   // the slab is complete in shared memory
     constexpr int kVecPerRow = 4 * 1024 * 2 / 16;                  // 512 16-byte vectors per tile row of the slab
     const uint4 *src = reinterpret_cast<const uint4 *>(stage);
