@@ -441,17 +441,24 @@ def run_gpu_arm(args):
     last_n = gemms[-1][2] * (G if gemms[-1][4] else 1)
     d2h = ROWS * last_n * 2
 
+    fused_api = mesh is not None and args.gather == "fused"
+
     def e2e_step():
         a = {K: ttnn.from_torch(p, layout=ttnn.TILE_LAYOUT, device=device) for K, p in pinned.items()}
         if mesh is not None:
             a = {K: ttnn.MultiDeviceTensor(t, mesh) for K, t in a.items()}
         y = None
         for layer in range(NLAYERS):
-            for i, (_, K, N, _, g) in enumerate(gemms):
-                y = ttnn.linear(a[K], tt_weights[layer][i])
-                if g and mesh is not None:
+            for idxs in groups:
+                _, K, N, _, g = gemms[idxs[0]]
+                if ROWS <= 256 and (len(idxs) > 1 or (fused_api and g)):
+                    # one launch for the weights that share this activation; the first result gathered by the kernel itself
+                    y = ttnn.linear_multi(a[K], [tt_weights[layer][i] for i in idxs], all_gather_first=bool(fused_api and g))[0]
+                else:
+                    y = ttnn.linear(a[K], tt_weights[layer][idxs[0]])
+                if g and mesh is not None and not fused_api:
                     y = ttnn.all_gather(y, dim=-1, num_links=1)
-        return ttnn.to_torch(y.local if mesh is not None else y)
+        return ttnn.to_torch(y)
 
     for _ in range(min(args.warmup, 3)):
         res = e2e_step()
@@ -486,7 +493,8 @@ def run_gpu_arm(args):
         "clocks": clocks.summary(),
         "e2e": {"value": to_value(e2e_s), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3,
-                "api": f"ttnn.from_torch -> ttnn.linear x{NLAYERS * len(gemms)} (+ ttnn.all_gather) -> ttnn.to_torch"},
+                "api": ("ttnn.from_torch -> ttnn.linear_multi / ttnn.linear x%d%s -> ttnn.to_torch" %
+                        (NLAYERS * len(groups), "" if mesh is None else (", gather in the matmul epilogue" if fused_api else " + ttnn.all_gather")))},
         "gpu_launches": launches_per_step * (2 if tensor_bound else 1) * args.steps,
         "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s" if tensor_bound else "GB/s", "frac": achieved / peak,

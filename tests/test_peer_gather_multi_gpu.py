@@ -19,3 +19,14 @@ def test_gather_epilogue_between_two_gpus():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "PEER-OK 0" in r.stdout and "PEER-OK 1" in r.stdout
+
+
+def test_ttnn_tensor_parallel_layers_between_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29741", os.path.join(HERE, "ttnn_tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP-OK 0" in r.stdout and "TP-OK 1" in r.stdout

@@ -139,3 +139,29 @@ def test_single_device_mesh_and_cache_on_device(device, tmp_path):
     s = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device, mesh_mapper=ttnn.ShardTensorToMesh(mesh, dim=-1))
     g = ttnn.all_gather(s, dim=-1, num_links=1)
     assert torch.equal(ttnn.to_torch(g, mesh_composer=ttnn.ConcatMeshToTensor(mesh, dim=-1)), ttnn.to_torch(t))
+
+
+def test_linear_multi_equals_separate_linears(device):
+    """ttnn.linear_multi: q / k / v style projections of one activation in one launch, then a further linear on a result."""
+    x = vectors.randn(31, (1, 1, 32, 2048), 1.0).bfloat16()
+    a = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    ws = [ttnn.from_torch(vectors.randn(32 + j, (2048, n), 0.02), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+          for j, n in enumerate((1024, 128, 256))]
+    bias = ttnn.from_torch(vectors.randn(40, (1, 1024), 0.5).bfloat16(), layout=ttnn.TILE_LAYOUT, device=device)
+    outs = ttnn.linear_multi(a, ws, biases=[bias, None, None], activation="silu")
+    assert len(outs) == 3
+    for j, (w, y) in enumerate(zip(ws, outs)):
+        want = ttnn.to_torch(ttnn.linear(a, w, bias=bias if j == 0 else None, activation="silu")).float()
+        got = ttnn.to_torch(y).float()
+        assert list(y.shape) == [1, 1, 32, [1024, 128, 256][j]]
+        assert oracle.comp_pcc(want.numpy(), got.numpy()) >= 0.9999
+        assert (got - want).abs().max() / want.abs().max() <= 1e-2
+    # a result feeds the next op like any other tensor
+    w2 = ttnn.from_torch(vectors.randn(45, (1024, 256), 0.02), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    z = ttnn.to_torch(ttnn.linear(outs[0], w2)).float()
+    z_ref = ttnn.to_torch(outs[0]).float() @ ttnn.to_torch(w2)
+    assert oracle.comp_pcc(z_ref.numpy(), z.numpy()) >= 0.9999
+    with pytest.raises(RuntimeError):
+        ttnn.linear_multi(a, ws + ws)                     # more than four weights
+    with pytest.raises(RuntimeError):
+        ttnn.linear_all_gather(a, ws[0])                  # needs multi-device tensors

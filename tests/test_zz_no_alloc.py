@@ -63,7 +63,7 @@ def test_static_scratch_variant_refuses_what_it_cannot_serve(ttb):
     # A reduction that needs more scratch than the built-in array is refused before anything is launched. The library's own
     # figure is checked first, and the operands are full-sized for the shape, so that a planner change can neither turn
     # this into a launch that the test did not expect nor into one that leaves its buffers.
-    M2, K2, N2 = 256, 1024, 7680
+    M2, K2, N2 = 256, 16384, 7680
     assert ttb.matmul_decode_static_scratch_bytes(cabi.BFLOAT8_B, 1, M2, K2, N2) > (16 << 20) + 65536
     a2, w2 = _operands(ttb, M2, K2, N2, cabi.BFLOAT8_B, 72)
     out2 = torch.empty(M2 * N2, dtype=torch.bfloat16, device="cuda")

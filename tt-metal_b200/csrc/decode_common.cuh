@@ -45,7 +45,8 @@ struct DecodeArgs {
     int tstart[TTB_MAX_GROUP + 1];   // first 128-column tile of each weight in the list; tstart[nprob] = tiles per row chunk
     int sk_grid, sk_gran, sk_upt;    // blocks, K-blocks per unit, units per tile
     int sk_waves, sk_rem_tile0;      // rounds of whole tiles (tile = round * sk_grid + block), first tile of the split remainder
-    long long sk_units;              // units of the remainder
+    int sk_tiles;                    // tiles in the list (all row chunks)
+    int sk_units, sk_q, sk_r;        // units of the streamed remainder; units / blocks and units % blocks
 };
 
 // Where a finished tile goes: one weight's output tensor (or its slice of a gathered tensor).

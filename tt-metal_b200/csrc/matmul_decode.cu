@@ -76,17 +76,22 @@ int32_t launch_decode_stream(const DecodeArgs &p, int fmt, int nb, bool overlap,
 
 struct StreamPlan {
     int nb, rchunks, tiles_row, tiles_total, grid, gran, upt;
-    int waves, rem_tile0;   // rounds of whole tiles; first tile of the remainder that is split along K
-    long long units;        // units of the remainder
+    int pieces, kbps;       // pieces decomposition: parts per tile (1 = not used) and K-blocks per part
+    int waves, rem_tile0;   // rounds of whole tiles (or pieces); first tile of the remainder that is streamed (or the piece count)
+    long long units;        // units of the streamed remainder
+    int slots;              // partial-sum slots
     bool shared_tiles;      // some tile's K range is shared by several blocks: scratch needed
 };
 // One persistent block per SM of a B200. The sizes derived from it (scratch) do not depend on the device at hand.
 static constexpr int kStreamBlocks = 148;
 static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a piece of a tile shorter than this
 
-// Whole tiles go out round by round, one per block. What is left after the last full round is split along K over all
-// blocks when that pays: not when the leftover tiles nearly fill a round anyway (each split tile costs its blocks a
-// partial-sum exchange), and not when they are too short to give every block a unit.
+// Picks the cheaper of two decompositions by a small cost model in units of one K-block's streaming time (~0.155 us):
+//  * pieces: every tile cut into s equal parts along K, taken round by round - cost rounds * (K-blocks per part + 6,
+//    + 20 for the partial-sum exchange when s > 1);
+//  * whole tiles round by round, the tiles left after the last full round streamed evenly over all blocks - each block
+//    then has up to two shared segments, ~35 each for the exchange and the pipeline bubble around it.
+// Both pay ~25 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama / Mistral / Falcon shapes.
 static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N) {
     StreamPlan sp;
     sp.nb = decode_rows_per_block(rows);
@@ -97,22 +102,46 @@ static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t 
     const int nkb = (int)(K / BK);
     sp.gran = kStreamGran;
     sp.upt = (nkb + sp.gran - 1) / sp.gran;
-    const int full = sp.tiles_total / kStreamBlocks, rem = sp.tiles_total % kStreamBlocks;
-    const bool split = rem > 0 && rem * 8 < kStreamBlocks * 7 && (long long)rem * sp.upt >= 2;
-    if (split) {
+    const int T = sp.tiles_total;
+    // pieces
+    int best_s = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 32 && s <= nkb; ++s) {
+        const int kbps = (nkb + s - 1) / s;
+        if ((nkb + kbps - 1) / kbps != s) continue;
+        if (s > 1 && kbps < 8) break;
+        const int rounds = (T * s + kStreamBlocks - 1) / kStreamBlocks;
+        const double cost = rounds * (kbps + 6.0 + (s > 1 ? 20.0 + 0.5 * s : 0.0));
+        if (cost < best_cost) { best_cost = cost; best_s = s; }
+    }
+    // whole tiles + streamed remainder
+    const int full = T / kStreamBlocks, rem = T % kStreamBlocks;
+    double stream_cost = 1e30;
+    if (rem > 0 && (long long)rem * sp.upt >= 2) {
+        const double share = (double)rem * nkb / kStreamBlocks;
+        stream_cost = full * (nkb + 6.0) + share + (full > 0 ? 35.0 : 70.0);   // after whole tiles a block has one shared segment, else two
+    }
+    if (stream_cost < best_cost) {
+        sp.pieces = 1; sp.kbps = nkb;
         sp.waves = full;
         sp.rem_tile0 = full * kStreamBlocks;
         sp.units = (long long)rem * sp.upt;
         sp.grid = full > 0 ? kStreamBlocks : (int)(sp.units < kStreamBlocks ? sp.units : kStreamBlocks);
+        sp.slots = rem + sp.grid;
+        sp.shared_tiles = false;
+        const long long q = sp.units / sp.grid, r = sp.units % sp.grid;
+        for (int b = 1; b < sp.grid; ++b)
+            if ((b * q + (b < r ? b : r)) % sp.upt != 0) sp.shared_tiles = true;
     } else {
-        sp.waves = full + (rem > 0 ? 1 : 0);
-        sp.rem_tile0 = sp.tiles_total;
+        sp.pieces = best_s; sp.kbps = (nkb + best_s - 1) / best_s;
+        const int npieces = T * best_s;
+        sp.waves = (npieces + kStreamBlocks - 1) / kStreamBlocks;
+        sp.rem_tile0 = npieces;
         sp.units = 0;
-        sp.grid = full > 0 ? kStreamBlocks : rem;
+        sp.grid = npieces < kStreamBlocks ? npieces : kStreamBlocks;
+        sp.slots = best_s > 1 ? npieces : 0;
+        sp.shared_tiles = best_s > 1;
     }
-    sp.shared_tiles = false;
-    for (int b = 1; b < sp.grid && sp.units > 0; ++b)
-        if (((long long)b * sp.units / sp.grid) % sp.upt != 0) sp.shared_tiles = true;
     return sp;
 }
 
@@ -133,9 +162,7 @@ static bool stream_accumulate_ok(int64_t rows, int nprob, const int64_t *N) {
     for (int j = 0; j < nprob; ++j) n += N[j];
     return rows * n * 4 <= kAccumBytes;
 }
-static int64_t stream_partial_bytes(const StreamPlan &sp) {
-    return (int64_t)(sp.tiles_total - sp.rem_tile0 + sp.grid) * BN * sp.nb * 4;   // one slot per (split tile, block) pair
-}
+static int64_t stream_partial_bytes(const StreamPlan &sp) { return (int64_t)sp.slots * BN * sp.nb * 4; }
 
 int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const int64_t *N, bool compact) {
     const StreamPlan sp = stream_plan(rows, K, nprob, N);
@@ -221,8 +248,10 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
         nsum += N[j];
     }
     p.tstart[nprob] = t0;
-    p.sk_grid = sp.grid; p.sk_gran = sp.gran; p.sk_upt = sp.upt; p.sk_units = sp.units;
-    p.sk_waves = sp.waves; p.sk_rem_tile0 = sp.rem_tile0;
+    p.sk_grid = sp.grid; p.sk_gran = sp.gran; p.sk_upt = sp.upt;
+    p.sk_units = (int)sp.units; p.sk_q = (int)(sp.units / sp.grid); p.sk_r = (int)(sp.units % sp.grid);
+    p.sk_waves = sp.waves; p.sk_rem_tile0 = sp.rem_tile0; p.sk_tiles = sp.tiles_total;
+    p.splits = sp.pieces; p.kb_per_split = sp.kbps;
     p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !stream_accumulate_ok(rows, nprob, N);
     if (gather) {
         p.ranks = gather->ranks; p.rank = gather->rank;

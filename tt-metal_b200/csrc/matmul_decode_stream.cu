@@ -20,6 +20,14 @@
 
 namespace ttb {
 
+#ifdef TTB_DEBUG_TIMING
+__device__ long long g_dbg[32];
+__device__ __forceinline__ long long dbg_clk() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory"); return t; }
+#define DBG(i) do { if (blockIdx.x == 0 && lane == 0) g_dbg[i] = dbg_clk(); } while (0)
+#else
+#define DBG(i) do { } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
@@ -48,44 +56,71 @@ struct StreamLayout {
 };
 
 struct Seg {
-    int tile;   // index into the tile list: row chunk * tiles per chunk + tile within the chunk
-    int kb0;    // first K-block
-    int nit;    // K-blocks
+    int tile;            // index into the tile list: row chunk * tiles per chunk + tile within the chunk
+    int kb0;             // first K-block
+    int nit;             // K-blocks
+    int contributors;    // blocks (or pieces) that share the tile; 1 = this segment is the whole tile
+    int slot0, slot;     // partial-sum slots of the tile's first contributor and of this segment
 };
 
-// A block's work, in order: `sk_waves` whole tiles (tile w * grid + block, the full K range: all blocks then read the same
-// K rows of neighbouring tiles at the same time, which DRAM likes), then its share of the remainder - the tiles from
-// sk_rem_tile0 on, cut into units of sk_gran K-blocks and dealt out evenly, in order.
+// The streamed remainder holds sk_units units; block b takes [b * q + min(b, r), ...) with q = units / grid, r = units % grid
+// (the first r blocks take one unit more). All of it in 32-bit arithmetic: these run on single threads' critical paths.
+__device__ __forceinline__ int unit_begin(const DecodeArgs &p, int b) { return b * p.sk_q + min(b, p.sk_r); }
+__device__ __forceinline__ int block_of_unit(const DecodeArgs &p, int u) {
+    const int big = p.sk_r * (p.sk_q + 1);
+    return u < big ? u / (p.sk_q + 1) : p.sk_r + (u - big) / p.sk_q;
+}
+
+// A block's work, in order. Two decompositions:
+//  * pieces (p.splits > 1): every tile is cut along K into p.splits equal pieces; piece q = part (q / tiles) of tile
+//    (q % tiles); the blocks take pieces round by round (q = round * grid + block). Neighbouring blocks read the same K
+//    rows of neighbouring tiles at the same time, which DRAM likes, and every block has one segment per round.
+//  * whole tiles + streamed remainder (p.splits == 1): `sk_waves` rounds of whole tiles (tile = round * grid + block), then
+//    the block's share of the remainder - the tiles from sk_rem_tile0 on, cut into units of sk_gran K-blocks and dealt
+//    out evenly, in order, so that all blocks finish together.
 struct SegIter {
     int w;
-    long long u, u_end;
+    int u, u_end;
     __device__ __forceinline__ void start(const DecodeArgs &p, int block) {
         w = 0;
-        u = (long long)block * p.sk_units / p.sk_grid;
-        u_end = (long long)(block + 1) * p.sk_units / p.sk_grid;
+        u = unit_begin(p, block);
+        u_end = unit_begin(p, block + 1);
     }
     __device__ __forceinline__ bool next(const DecodeArgs &p, int block, Seg &s) {
         while (w < p.sk_waves) {
-            const int tile = w * p.sk_grid + block;
+            const int q = w * p.sk_grid + block;
             ++w;
-            if (tile < p.sk_rem_tile0) {
-                s.tile = tile; s.kb0 = 0; s.nit = p.nkb;
+            if (q < p.sk_rem_tile0) {   // (in the pieces decomposition sk_rem_tile0 is the number of pieces)
+                if (p.splits > 1) {
+                    const int part = q / p.sk_tiles;
+                    s.tile = q - part * p.sk_tiles;
+                    s.kb0 = part * p.kb_per_split;
+                    s.nit = min(p.nkb, s.kb0 + p.kb_per_split) - s.kb0;
+                    s.contributors = p.splits;
+                    s.slot0 = s.tile * p.splits;
+                    s.slot = s.slot0 + part;
+                } else {
+                    s.tile = q; s.kb0 = 0; s.nit = p.nkb;
+                    s.contributors = 1; s.slot0 = 0; s.slot = 0;
+                }
                 return true;
             }
         }
         if (u >= u_end) return false;
-        const int rt = (int)(u / p.sk_upt);
-        const long long t0 = (long long)rt * p.sk_upt;
-        const long long e = min(u_end, t0 + p.sk_upt);
+        const int rt = u / p.sk_upt;
+        const int t0 = rt * p.sk_upt;
+        const int e = min(u_end, t0 + p.sk_upt);
         s.tile = p.sk_rem_tile0 + rt;
-        s.kb0 = (int)(u - t0) * p.sk_gran;
-        s.nit = min(p.nkb, (int)(e - t0) * p.sk_gran) - s.kb0;
+        s.kb0 = (u - t0) * p.sk_gran;
+        s.nit = min(p.nkb, (e - t0) * p.sk_gran) - s.kb0;
+        const int fb = block_of_unit(p, t0);
+        s.contributors = block_of_unit(p, t0 + p.sk_upt - 1) - fb + 1;
+        s.slot0 = rt + fb;
+        s.slot = rt + block;
         u = e;
         return true;
     }
 };
-// The block whose range [b * U / grid, (b + 1) * U / grid) holds unit u.
-__device__ __forceinline__ int block_of_unit(long long u, int grid, long long U) { return (int)(((u + 1) * grid + U - 1) / U) - 1; }
 
 // Which weight a tile of the list belongs to, its 128-column index inside that weight, and its row chunk.
 struct TileRef {
@@ -121,7 +156,7 @@ constexpr int kPartialsUpTo = 4;
 // ---------------- epilogue of one segment, run by warps 4..11 together; returns false after a wait that ran out ----------------
 // Kept out of line: inlined into the expand loop it costs that loop registers and instruction-cache room.
 template <int FMT, int NB>
-__device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx &c, const Seg s, const int seg_idx, bool ok) {
+__device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, bool ok) {
     using L = StreamLayout<FMT, NB>;
     constexpr int kAcc = BK / 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,6 +166,7 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx &
     int good = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0);
     if (lane == 0 && good) good = mbar_wait(c.accum_bar, (uint32_t)(seg_idx & 1), c.abort_flag, p.status, 5, c.lim) ? 1 : 0;
     const bool eok = __shfl_sync(0xffffffffu, good, 0) != 0;
+    if (warp == kMmaWarp) DBG(8);
     tc_fence_after_sync();
     const TileRef tr = tile_ref(p, s.tile);
     const int64_t row0 = (int64_t)tr.rchunk * NB;
@@ -143,14 +179,7 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx &
     ov.N = gathered ? p.out_N : p.Nv[tr.prob];
     ov.Nt = (int)(ov.N >> 5);
     uint16_t *const stage = gathered ? reinterpret_cast<uint16_t *>(c.smem + L::stage) : nullptr;
-    // blocks that share this tile (whole tiles of the first rounds belong to one block)
-    int fb = 0, contributors = 1;
-    const int rt = s.tile - p.sk_rem_tile0;
-    if (rt >= 0) {
-        const long long tu0 = (long long)rt * p.sk_upt;
-        fb = block_of_unit(tu0, p.sk_grid, p.sk_units);
-        contributors = block_of_unit(tu0 + p.sk_upt - 1, p.sk_grid, p.sk_units) - fb + 1;
-    }
+    const int contributors = s.contributors;
     const bool partials = p.ordered || contributors <= kPartialsUpTo;
     float *const acc_tile = p.accum + (int64_t)s.tile * BN * NB;
     if (eok) {
@@ -171,7 +200,7 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx &
             if (contributors == 1) {
                 finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
             } else if (partials) {
-                float4 *dst = reinterpret_cast<float4 *>(p.partial + ((int64_t)(rt + (int)blockIdx.x) * BN + quad * 32 + lane) * NB + col0);
+                float4 *dst = reinterpret_cast<float4 *>(p.partial + ((int64_t)s.slot * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
             } else {
@@ -206,7 +235,7 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx &
                         for (int u = 0; u < 4; ++u) {
                             const int cb = min(c0 + u, contributors - 1);
                             const float4 *src = reinterpret_cast<const float4 *>(
-                                p.partial + ((int64_t)(rt + fb + cb) * BN + quad * 32 + lane) * NB + col0);
+                                p.partial + ((int64_t)(s.slot0 + cb) * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
                         }
@@ -267,13 +296,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = (int)blockIdx.x;
-    int nseg = 0;
-    {
-        SegIter it;
-        it.start(p, block);
-        Seg s;
-        while (it.next(p, block, s)) ++nseg;
-    }
+    if (warp == 0) DBG(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPkG; ++s) {
@@ -298,6 +321,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    if (warp == 0) DBG(1);
     // Limit of every barrier wait, in clocks: about a second, but longer than the peer wait when the activations come from
     // other GPUs (the roles downstream of the expand warps sit in barrier waits while those wait for the peers).
     const long long lim = p.wait_arrived ? 25000000000LL : 2000000000LL;
@@ -333,6 +357,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                         src += src_step;
                     }
                     if (++gs == kPkG) { gs = 0; ph ^= 1; }
+#ifdef TTB_DEBUG_TIMING
+                    if (blockIdx.x == 0 && g_dbg[2] == 0) g_dbg[2] = dbg_clk();
+#endif
                 }
             }
         }
@@ -358,6 +385,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
                     const int r = min(kGroup, s.nit - i0);
                     if (!mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2, lim)) { ok = false; break; }
+#ifdef TTB_DEBUG_TIMING
+                    if (blockIdx.x == 0 && warp == kMmaWarp && g_dbg[6] == 0) g_dbg[6] = dbg_clk();
+#endif
                     tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4);
                     const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4);
@@ -371,9 +401,11 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                     if (++gt == kAbGroups) { gt = 0; ph ^= 1; }
                 }
                 if (ok) mma_commit(accum_bar);
+                if (warp == kMmaWarp) DBG(7);
             }
             __syncwarp();
             ok = stream_epilogue<FMT, NB>(p, ectx, s, seg_idx, ok);
+            if (warp == kMmaWarp) DBG(9);
             tc_fence_after_sync();
         }
     } else {
@@ -392,6 +424,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         const int act_step = act_chunk_step(p);
         const int64_t chunk_step = p.a_row_major ? (int64_t)NB * p.K : (int64_t)(NB / 32) * p.Kt * 1024;   // one row chunk further
         grid_dep_wait();
+        if (warp == 1) DBG(3);
         if (p.wait_arrived) {
             int good = 1;
             if (lane == 0) good = peer_wait(p, abort_flag, 6) ? 1 : 0;
@@ -403,7 +436,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         SegIter cur_it;
         cur_it.start(p, block);
         int cur_g0 = 0, cur_ng = 0, cur_si = -1;
-        Seg cur = {0, 0, 0};
+        Seg cur = {0, 0, 0, 1, 0, 0};
         const uint16_t *cur_act = p.a;   // activations of K-block 0 of the current segment's row chunk
         bool more = true;
         // advances `cur` to the segment that holds group G; false once the block's work ends (rare path, kept out of the loop body)
@@ -439,7 +472,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         auto epilogues_up_to = [&](int upto) {
             while (epi_done < upto) {
                 Seg s;
-                epi_it.next(p, block, s);
+                if (!epi_it.next(p, block, s)) break;
                 ok = stream_epilogue<FMT, NB>(p, ectx, s, epi_done, ok);
                 ++epi_done;
             }
@@ -462,6 +495,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 good = mbar_wait(empty_ab(gt), pht ^ 1, abort_flag, p.status, 3, lim) && mbar_wait(full_pk(gs), phs, abort_flag, p.status, 4, lim);
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) { ok = false; break; }
+#ifdef TTB_DEBUG_TIMING
+            if (blockIdx.x == 0 && warp == 1 && lane == 0 && g_dbg[4] == 0) g_dbg[4] = dbg_clk();
+#endif
             if (present) {
                 const uint8_t *pst = smem + L::pk + sl * Pk<FMT>::kStageBytes;
                 uint8_t *const ast = smem + L::a + t * kAStageBytes + lane_a;
@@ -510,6 +546,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 mbar_arrive(full_ab(gt));
                 mbar_arrive(empty_pk(gs));
             }
+#ifdef TTB_DEBUG_TIMING
+            if (blockIdx.x == 0 && warp == 1 && lane == 0) { if (g_dbg[5] == 0) g_dbg[5] = dbg_clk(); g_dbg[11] = dbg_clk(); }
+#endif
             G += kExpandWarps / kGroup;
             gs += kExpandWarps / kGroup;
             if (gs >= kPkG) { gs -= kPkG; phs ^= 1u; }
@@ -518,7 +557,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
             more = G < cur_g0 + cur_ng || locate_slow(G);
             if (more) load_act(G);
         }
-        if (in_epi) epilogues_up_to(nseg);
+        if (in_epi) epilogues_up_to(1 << 30);   // whatever is left
     }
 
     // ---------------- teardown ----------------
@@ -532,6 +571,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
+        DBG(10);
     }
 }
 
@@ -562,6 +602,19 @@ int32_t launch_one(const DecodeArgs &p, bool overlap, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef TTB_DEBUG_TIMING
+extern "C" int32_t ttb_debug_timing(long long *out32, int clear) {
+    if (clear) {
+        long long z[32] = {};
+        cudaMemcpyToSymbol(g_dbg, z, sizeof(z));
+        return 0;
+    }
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out32, g_dbg, 32 * sizeof(long long));
+    return 0;
+}
+#endif
 
 int32_t launch_decode_stream(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream) {
 #define TTB_STREAM(F, B) return launch_one<F, B>(p, overlap, stream)

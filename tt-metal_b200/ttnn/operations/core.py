@@ -26,7 +26,14 @@ def _is_block_float(dtype):
 
 
 def _unwrap(tensor):
-    return tensor.local if isinstance(tensor, MultiDeviceTensor) else tensor
+    if isinstance(tensor, MultiDeviceTensor):
+        if getattr(tensor, "_gather_slot", None) is not None:
+            from .ccl import wait_for_gather     # result of a fused linear + all-gather: hold the stream until it is complete
+            wait_for_gather(tensor)
+        return tensor.local
+    if type(tensor).__name__ == "FusedOutput":     # single-device result of ttnn.linear_multi
+        return tensor.local
+    return tensor
 
 
 def _rewrap(like, tensor):

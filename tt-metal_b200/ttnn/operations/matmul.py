@@ -50,6 +50,11 @@ def _split(a, b, bias=None):
     for t in (a, b, bias):
         if isinstance(t, MultiDeviceTensor):
             mesh = t.mesh
+            if getattr(t, "_gather_slot", None) is not None:
+                from .ccl import wait_for_gather     # gathered by a fused linear: complete it before a plain matmul reads it
+                wait_for_gather(t)
+            t = t.local
+        elif type(t).__name__ == "FusedOutput":
             t = t.local
         out.append(t)
     return mesh, out

@@ -38,6 +38,9 @@ def _declare(cdll):
     cdll.ttb_matmul_peer_workspace_bytes.argtypes = [_i32, _i64, _i64, _i64, _i64]
     cdll.ttb_matmul_peer_workspace_bytes.restype = _i64
     cdll.ttb_matmul_peer.argtypes = [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]
+    cdll.ttb_matmul_multi_workspace_bytes.argtypes = [_i32, _i64, _i64, _i64, _i32, _vp]
+    cdll.ttb_matmul_multi_workspace_bytes.restype = _i64
+    cdll.ttb_matmul_multi.argtypes = [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]
 
 
 _declare(_rt.cdll)
