@@ -147,6 +147,14 @@ __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const OutV
                                                  int64_t n, uint16_t *stage = nullptr) {
     TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, ov, v, row0, col0, n, stage));
 }
+// The same as one out-of-line copy: a kernel that finishes tiles in several places would otherwise carry the activation x
+// output-type x staging variants of the store loop at each of them, and its instruction footprint decides how long a
+// short launch takes (instruction-fetch stalls dominated the profile of the inlined form).
+template <int NB>
+__device__ __noinline__ void finish_and_store_shared(const DecodeArgs &p, const OutView &ov, const float (&v)[16], int64_t row0, int col0,
+                                                     int64_t n, uint16_t *stage) {
+    TTB_DISPATCH_ACT(p.act, finish_and_store_t<ACT>(p, ov, v, row0, col0, n, stage));
+}
 template <int NB>
 __device__ __forceinline__ void finish_and_store(const DecodeArgs &p, const float (&v)[16], int64_t row0, int col0, int64_t n,
                                                  uint16_t *stage = nullptr) {

@@ -88,7 +88,8 @@ static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a pi
 
 // Picks the cheaper of two decompositions by a small cost model in units of one K-block's streaming time (~0.155 us):
 //  * pieces: every tile cut into s equal parts along K, taken round by round - cost rounds * (K-blocks per part + 6,
-//    + 20 for the partial-sum exchange when s > 1);
+//    + 13 + 4.5 s for the partial-sum exchange when s > 1: ~2 us until a block knows its ticket, ~0.7 us per partial
+//    the last arriver reads);
 //  * whole tiles round by round, the tiles left after the last full round streamed evenly over all blocks - each block
 //    then has up to two shared segments, ~35 each for the exchange and the pipeline bubble around it.
 // Both pay ~25 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama / Mistral / Falcon shapes.
@@ -109,9 +110,12 @@ static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t 
     for (int s = 1; s <= 32 && s <= nkb; ++s) {
         const int kbps = (nkb + s - 1) / s;
         if ((nkb + kbps - 1) / kbps != s) continue;
-        if (s > 1 && kbps < 8) break;
+#ifndef TTB_MIN_KBPS
+#define TTB_MIN_KBPS 8
+#endif
+        if (s > 1 && kbps < TTB_MIN_KBPS) break;
         const int rounds = (T * s + kStreamBlocks - 1) / kStreamBlocks;
-        const double cost = rounds * (kbps + 6.0 + (s > 1 ? 20.0 + 0.5 * s : 0.0));
+        const double cost = rounds * (kbps + 6.0 + (s > 1 ? 13.0 + 4.5 * s : 0.0));
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     // whole tiles + streamed remainder

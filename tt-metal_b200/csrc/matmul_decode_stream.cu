@@ -20,13 +20,6 @@
 
 namespace ttb {
 
-#ifdef TTB_DEBUG_TIMING
-__device__ long long g_dbg[32];
-__device__ __forceinline__ long long dbg_clk() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory"); return t; }
-#define DBG(i) do { if (blockIdx.x == 0 && lane == 0) g_dbg[i] = dbg_clk(); } while (0)
-#else
-#define DBG(i) do { } while (0)
-#endif
 
 namespace {
 
@@ -151,12 +144,14 @@ struct EpiCtx {
 // Tiles shared by at most this many blocks are summed from per-block partials (plain stores, fixed order); tiles shared
 // by more use fp32 reductions in L2 (when every block of a launch flushes a partial tile at once, 16 KiB of reductions
 // per block cost several microseconds, plain stores a fraction of that).
-constexpr int kPartialsUpTo = 4;
+#ifndef TTB_PARTIALS_UP_TO
+#define TTB_PARTIALS_UP_TO 4
+#endif
+constexpr int kPartialsUpTo = TTB_PARTIALS_UP_TO;
 
 // ---------------- epilogue of one segment, run by warps 4..11 together; returns false after a wait that ran out ----------------
-// Kept out of line: inlined into the expand loop it costs that loop registers and instruction-cache room.
 template <int FMT, int NB>
-__device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, bool ok) {
+__device__ __forceinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, bool ok) {
     using L = StreamLayout<FMT, NB>;
     constexpr int kAcc = BK / 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,7 +161,6 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx c
     int good = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0);
     if (lane == 0 && good) good = mbar_wait(c.accum_bar, (uint32_t)(seg_idx & 1), c.abort_flag, p.status, 5, c.lim) ? 1 : 0;
     const bool eok = __shfl_sync(0xffffffffu, good, 0) != 0;
-    if (warp == kMmaWarp) DBG(8);
     tc_fence_after_sync();
     const TileRef tr = tile_ref(p, s.tile);
     const int64_t row0 = (int64_t)tr.rchunk * NB;
@@ -182,86 +176,104 @@ __device__ __noinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCtx c
     const int contributors = s.contributors;
     const bool partials = p.ordered || contributors <= kPartialsUpTo;
     float *const acc_tile = p.accum + (int64_t)s.tile * BN * NB;
-    if (eok) {
+    // sum of the two accumulators, 16 consecutive columns of this lane's row
+    auto read_accumulators = [&](int col0, float (&v)[16]) {
 #pragma unroll
-        for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
-            const int col0 = half * kColsPerWarp + cc * 16;
-            float v[16];
+        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+        for (int ac = 0; ac < kAcc; ++ac) {
+            uint32_t r[16];
+            tmem_ld16(c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ac * NB + col0), r);
+            tmem_ld_wait();
 #pragma unroll
-            for (int ac = 0; ac < kAcc; ++ac) {
-                uint32_t r[16];
-                tmem_ld16(c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ac * NB + col0), r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
-            }
-            if (contributors == 1) {
-                finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
-            } else if (partials) {
-                float4 *dst = reinterpret_cast<float4 *>(p.partial + ((int64_t)s.slot * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-            } else {
-                float *dst = acc_tile + (quad * 32 + lane) * NB + col0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            }
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
         }
-    }
-    // From here on the accumulators are free: the MMA issuers are among the threads of this barrier.
-    tc_fence_before_sync();
-    if (contributors > 1) __threadfence();
-    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+    };
     bool finished = contributors == 1;
     if (contributors > 1) {
-        if (tid == 0) *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        finished = *c.last_flag != 0;
-        if (finished) {
-            __threadfence();
+        // phase 1: hand this block's share over (partial tile or reductions), then learn whether it arrived last
+        if (eok) {
 #pragma unroll
             for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
                 const int col0 = half * kColsPerWarp + cc * 16;
                 float v[16];
+                read_accumulators(col0, v);
+                if (partials) {
+                    float4 *dst = reinterpret_cast<float4 *>(p.partial + ((int64_t)s.slot * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                } else {
+                    float *dst = acc_tile + (quad * 32 + lane) * NB + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+        }
+        // From this barrier on the accumulators are free: the MMA issuers are among its threads.
+        tc_fence_before_sync();
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0) *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        finished = *c.last_flag != 0;
+        // No fence on this side: the other blocks' partial sums were performed in L2 before their tickets (their fences),
+        // thread 0 has its ticket's value, the barrier orders this thread after it, and the loads below bypass L1 (.cg).
+    }
+    // phase 2: whoever holds the complete sum - the only block of an unshared tile, or the last arriver - finishes the tile
+    if (finished && (eok || contributors > 1)) {
+#pragma unroll
+        for (int cc = 0; cc < kColsPerWarp / 16; ++cc) {
+            const int col0 = half * kColsPerWarp + cc * 16;
+            float v[16];
+            if (contributors == 1) {
+                read_accumulators(col0, v);
+            } else if (partials) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                if (partials) {
-                    // four blocks' partials per round: the loads are issued together, the adds stay in block order
-                    for (int c0 = 0; c0 < contributors; c0 += 4) {
-                        float4 x[4][4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int cb = min(c0 + u, contributors - 1);
-                            const float4 *src = reinterpret_cast<const float4 *>(
-                                p.partial + ((int64_t)(s.slot0 + cb) * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (c0 + u < contributors) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
-                                }
-                            }
-                        }
-                    }
-                } else {
-                    float4 *acc = reinterpret_cast<float4 *>(acc_tile + (quad * 32 + lane) * NB + col0);
+                // Up to four blocks' partials per round: all loads of a round are issued before the first add (under the
+                // weight stream a trip to L2 takes ~1.5 us, so rounds are what this costs); the adds stay in block order.
+#pragma unroll 1
+                for (int c0 = 0; c0 < contributors; c0 += 4) {
+                    const float4 *src = reinterpret_cast<const float4 *>(
+                        p.partial + ((int64_t)(s.slot0 + c0) * BN + quad * 32 + lane) * NB + col0);
+                    constexpr int64_t kSlot = (int64_t)BN * NB / 4;   // float4 per slot
+                    const int cnt = min(4, contributors - c0);
+                    float4 x0[4], x1[4], x2[4], x3[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float4 x = __ldcg(acc + j);
-                        v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
-                        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);   // leave zeros for the next launch
+                        x0[j] = __ldcg(src + j);
+                        x1[j] = cnt > 1 ? __ldcg(src + kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        x2[j] = cnt > 2 ? __ldcg(src + 2 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        x3[j] = cnt > 3 ? __ldcg(src + 3 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
+                    auto add = [&](const float4 (&x)[4]) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            v[4 * j] += x[j].x; v[4 * j + 1] += x[j].y; v[4 * j + 2] += x[j].z; v[4 * j + 3] += x[j].w;
+                        }
+                    };
+                    add(x0);
+                    if (cnt > 1) add(x1);
+                    if (cnt > 2) add(x2);
+                    if (cnt > 3) add(x3);
                 }
-                finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+            } else {
+                float4 *acc = reinterpret_cast<float4 *>(acc_tile + (quad * 32 + lane) * NB + col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 x = __ldcg(acc + j);
+                    v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+                    acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);   // leave zeros for the next launch
+                }
             }
-            if (tid == 0) p.counters[s.tile] = 0;
+            finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
         }
+        if (contributors > 1 && tid == 0) p.counters[s.tile] = 0;
+    }
+    if (contributors == 1) {
+        // the accumulators are free from here on: the MMA issuers are among the threads of this barrier
+        tc_fence_before_sync();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     }
     if (gathered) {
         // one decision for the whole group of threads, so that all of them take part in gather_send's barriers
@@ -296,7 +308,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = (int)blockIdx.x;
-    if (warp == 0) DBG(0);
+    // Limit of every barrier wait, in clocks: about a second, but longer than the peer wait when the activations come from
+    // other GPUs (the roles downstream of the expand warps sit in barrier waits while those wait for the peers).
+    const long long lim = p.wait_arrived ? 25000000000LL : 2000000000LL;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPkG; ++s) {
@@ -321,10 +335,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
-    if (warp == 0) DBG(1);
-    // Limit of every barrier wait, in clocks: about a second, but longer than the peer wait when the activations come from
-    // other GPUs (the roles downstream of the expand warps sit in barrier waits while those wait for the peers).
-    const long long lim = p.wait_arrived ? 25000000000LL : 2000000000LL;
     // The next kernel on the stream may start streaming its weights while this grid drains; before grid_dep_wait() this
     // kernel reads nothing but packed weights.
     grid_dep_launch();
@@ -335,32 +345,33 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     // group like the others and arrives on both barriers without expanding anything - so every barrier sees the same
     // arrivals in the same order for every group.
     if (warp == kProducerWarp) {
-        // ---------------- producer: packed weight tiles -> shared-memory ring, across segment borders ----------------
-        if (lane == 0) {
-            const uint64_t policy = l2_policy_evict_first();
-            int gs = 0;
-            uint32_t ph = 0;
-            SegIter it;
-            it.start(p, block);
-            Seg s;
-            while (ok && it.next(p, block, s)) {
-                const TileRef tr = tile_ref(p, s.tile);
-                const int Ntj = (int)(p.Nv[tr.prob] >> 5);
-                const uint8_t *src = p.wv[tr.prob] + ((int64_t)s.kb0 * Ntj + (int64_t)tr.nt * 4) * TB;
-                const int64_t src_step = (int64_t)Ntj * TB;
-                for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    const int r = min(kGroup, s.nit - i0);
-                    if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
-                    for (int j = 0; j < r; ++j) {
-                        bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
-                        src += src_step;
-                    }
-                    if (++gs == kPkG) { gs = 0; ph ^= 1; }
-#ifdef TTB_DEBUG_TIMING
-                    if (blockIdx.x == 0 && g_dbg[2] == 0) g_dbg[2] = dbg_clk();
-#endif
+        // ---------------- producer (warp 0): packed weight tiles -> shared-memory ring, across segment borders ----------------
+        // Lane 0 waits for the group's ring slot and announces the bytes; lanes 0..2 then each send one stage's copy, so the
+        // copies of a group are issued side by side (one thread alone needs ~120 ns per copy, close to the whole budget of
+        // a stage).
+        const uint64_t policy = l2_policy_evict_first();
+        int gs = 0;
+        uint32_t ph = 0;
+        SegIter it;
+        it.start(p, block);
+        Seg s;
+        while (ok && it.next(p, block, s)) {
+            const TileRef tr = tile_ref(p, s.tile);
+            const int Ntj = (int)(p.Nv[tr.prob] >> 5);
+            const int64_t src_step = (int64_t)Ntj * TB;
+            const uint8_t *src = p.wv[tr.prob] + ((int64_t)s.kb0 * Ntj + (int64_t)tr.nt * 4) * TB + (int64_t)lane * src_step;
+            for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
+                const int r = min(kGroup, s.nit - i0);
+                int good = 1;
+                if (lane == 0) {
+                    good = mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim) ? 1 : 0;
+                    if (good) mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
                 }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+                if (lane < r) bulk_g2s(sbase + L::pk + (gs * kGroup + lane) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
+                src += kGroup * src_step;
+                if (++gs == kPkG) { gs = 0; ph ^= 1; }
             }
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp2) {
@@ -385,9 +396,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
                     const int r = min(kGroup, s.nit - i0);
                     if (!mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2, lim)) { ok = false; break; }
-#ifdef TTB_DEBUG_TIMING
-                    if (blockIdx.x == 0 && warp == kMmaWarp && g_dbg[6] == 0) g_dbg[6] = dbg_clk();
-#endif
                     tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4);
                     const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4);
@@ -401,11 +409,9 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                     if (++gt == kAbGroups) { gt = 0; ph ^= 1; }
                 }
                 if (ok) mma_commit(accum_bar);
-                if (warp == kMmaWarp) DBG(7);
             }
             __syncwarp();
             ok = stream_epilogue<FMT, NB>(p, ectx, s, seg_idx, ok);
-            if (warp == kMmaWarp) DBG(9);
             tc_fence_after_sync();
         }
     } else {
@@ -424,7 +430,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         const int act_step = act_chunk_step(p);
         const int64_t chunk_step = p.a_row_major ? (int64_t)NB * p.K : (int64_t)(NB / 32) * p.Kt * 1024;   // one row chunk further
         grid_dep_wait();
-        if (warp == 1) DBG(3);
         if (p.wait_arrived) {
             int good = 1;
             if (lane == 0) good = peer_wait(p, abort_flag, 6) ? 1 : 0;
@@ -485,19 +490,17 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         uint32_t phs = (uint32_t)(G / kPkG) & 1u, pht = (uint32_t)(G / kAbGroups) & 1u;
         more = ok && locate_slow(G);
         if (more) load_act(G);
-        while (more) {
-            if (in_epi) epilogues_up_to(cur_si);   // every earlier segment is finished before any stage of this one is touched
-            if (!ok) break;
+        while (true) {
+            // every earlier segment is finished before any stage of this one is touched; at the end, whatever is left
+            if (in_epi) epilogues_up_to(more && ok ? cur_si : (1 << 30));
+            if (!more || !ok) break;
             const bool present = (G - cur_g0) * kGroup + member < cur.nit;
             const int sl = gs * kGroup + member, t = gt * kGroup + member;
             int good = 1;
             if (lane == 0)
                 good = mbar_wait(empty_ab(gt), pht ^ 1, abort_flag, p.status, 3, lim) && mbar_wait(full_pk(gs), phs, abort_flag, p.status, 4, lim);
             good = __shfl_sync(0xffffffffu, good, 0);
-            if (!good) { ok = false; break; }
-#ifdef TTB_DEBUG_TIMING
-            if (blockIdx.x == 0 && warp == 1 && lane == 0 && g_dbg[4] == 0) g_dbg[4] = dbg_clk();
-#endif
+            if (!good) { ok = false; continue; }   // (the top of the loop still runs this warp's share of the epilogues)
             if (present) {
                 const uint8_t *pst = smem + L::pk + sl * Pk<FMT>::kStageBytes;
                 uint8_t *const ast = smem + L::a + t * kAStageBytes + lane_a;
@@ -546,9 +549,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 mbar_arrive(full_ab(gt));
                 mbar_arrive(empty_pk(gs));
             }
-#ifdef TTB_DEBUG_TIMING
-            if (blockIdx.x == 0 && warp == 1 && lane == 0) { if (g_dbg[5] == 0) g_dbg[5] = dbg_clk(); g_dbg[11] = dbg_clk(); }
-#endif
             G += kExpandWarps / kGroup;
             gs += kExpandWarps / kGroup;
             if (gs >= kPkG) { gs -= kPkG; phs ^= 1u; }
@@ -557,7 +557,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
             more = G < cur_g0 + cur_ng || locate_slow(G);
             if (more) load_act(G);
         }
-        if (in_epi) epilogues_up_to(1 << 30);   // whatever is left
     }
 
     // ---------------- teardown ----------------
@@ -571,7 +570,6 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
-        DBG(10);
     }
 }
 
@@ -603,18 +601,6 @@ int32_t launch_one(const DecodeArgs &p, bool overlap, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef TTB_DEBUG_TIMING
-extern "C" int32_t ttb_debug_timing(long long *out32, int clear) {
-    if (clear) {
-        long long z[32] = {};
-        cudaMemcpyToSymbol(g_dbg, z, sizeof(z));
-        return 0;
-    }
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out32, g_dbg, 32 * sizeof(long long));
-    return 0;
-}
-#endif
 
 int32_t launch_decode_stream(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream) {
 #define TTB_STREAM(F, B) return launch_one<F, B>(p, overlap, stream)
