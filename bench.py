@@ -108,10 +108,12 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, enabled=True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
 
     def __enter__(self):
+        if not self.enabled:      # only the rank that prints the line samples (several nvidia-smi at once slow each other down)
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
                                           "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -142,8 +144,10 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         t0, t1 = getattr(self, "t_start", 0.0), getattr(self, "t_end", float("inf"))
         inside = [r for t, r in self.rows if t0 <= t <= t1 + 0.02]
-        # a timed region shorter than a few sampling periods: fall back to the samples of the identical warm-up replays
-        rows = inside if len(inside) >= 3 else [r for t, r in self.rows if t >= getattr(self, "t_load", 0.0)]
+        # a timed region shorter than a few sampling periods: add the samples of the identical replays that ran right
+        # before and after it (same graph, same load)
+        t2 = getattr(self, "t_end_load", t1)
+        rows = inside if len(inside) >= 3 else [r for t, r in self.rows if getattr(self, "t_load", 0.0) <= t <= t2 + 0.02]
         for r in rows:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
@@ -155,7 +159,7 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
-                "window": "timed region" if len(inside) >= 3 else "warm-up replays + timed region"}
+                "window": "timed region" if len(inside) >= 3 else "timed region + identical replays around it"}
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -378,11 +382,26 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def keep_load_while(cond, graph, seconds=3.0):
+        """Replays the graph (untimed) while rank 0's `cond()` holds (at most `seconds`), the same number of times on every rank."""
+        t_stop = time.time() + seconds
+        while True:
+            flag = torch.tensor([1 if (rank == 0 and cond() and time.time() < t_stop) else 0], device=dev_t)
+            if G > 1:
+                dist.broadcast(flag, 0)
+            if int(flag.item()) == 0:
+                break
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+
     def timed_replays(graph, steps, warmup, sampler=None):
         if sampler:
             sampler.mark("load")
         for _ in range(warmup):
             graph.replay()
+        if sampler:
+            keep_load_while(lambda: len(sampler.rows) == 0, graph)       # nvidia-smi takes a moment to deliver its first sample
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if sampler:
@@ -394,6 +413,9 @@ def run_gpu_arm(args):
         barrier()
         if sampler:
             sampler.mark("end")
+            # a timed region shorter than three sampling periods: keep the identical load running until three samples exist
+            keep_load_while(lambda: sum(1 for t, _ in sampler.rows if t >= sampler.t_start) < 3, graph)
+            sampler.mark("end_load")
         ms = e0.elapsed_time(e1)
         if G > 1:
             t = torch.tensor([ms], device=dev_t)
@@ -401,7 +423,7 @@ def run_gpu_arm(args):
             ms = t.item()
         return ms
 
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank, enabled=(rank == 0)) as clocks:
         graph_full = capture(True)      # also gives nvidia-smi time to start sampling
         ms_total = timed_replays(graph_full, args.steps, args.warmup, clocks)
     ms_step = ms_total / args.steps
