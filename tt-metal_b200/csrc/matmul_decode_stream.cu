@@ -345,33 +345,32 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     // group like the others and arrives on both barriers without expanding anything - so every barrier sees the same
     // arrivals in the same order for every group.
     if (warp == kProducerWarp) {
-        // ---------------- producer (warp 0): packed weight tiles -> shared-memory ring, across segment borders ----------------
-        // Lane 0 waits for the group's ring slot and announces the bytes; lanes 0..2 then each send one stage's copy, so the
-        // copies of a group are issued side by side (one thread alone needs ~120 ns per copy, close to the whole budget of
-        // a stage).
-        const uint64_t policy = l2_policy_evict_first();
-        int gs = 0;
-        uint32_t ph = 0;
-        SegIter it;
-        it.start(p, block);
-        Seg s;
-        while (ok && it.next(p, block, s)) {
-            const TileRef tr = tile_ref(p, s.tile);
-            const int Ntj = (int)(p.Nv[tr.prob] >> 5);
-            const int64_t src_step = (int64_t)Ntj * TB;
-            const uint8_t *src = p.wv[tr.prob] + ((int64_t)s.kb0 * Ntj + (int64_t)tr.nt * 4) * TB + (int64_t)lane * src_step;
-            for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                const int r = min(kGroup, s.nit - i0);
-                int good = 1;
-                if (lane == 0) {
-                    good = mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim) ? 1 : 0;
-                    if (good) mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
+        // ---------------- producer: packed weight tiles -> shared-memory ring, across segment borders ----------------
+        // One thread. (Letting the whole warp take part - lane 0 waiting, lanes 0..2 issuing a group's copies side by
+        // side - shortens the first ring fill but costs the steady state ~5 %: warp 0 shares its scheduler with the two MMA
+        // issuers, whose single-thread loops feel every extra instruction issued next to them.)
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_first();
+            int gs = 0;
+            uint32_t ph = 0;
+            SegIter it;
+            it.start(p, block);
+            Seg s;
+            while (ok && it.next(p, block, s)) {
+                const TileRef tr = tile_ref(p, s.tile);
+                const int Ntj = (int)(p.Nv[tr.prob] >> 5);
+                const uint8_t *src = p.wv[tr.prob] + ((int64_t)s.kb0 * Ntj + (int64_t)tr.nt * 4) * TB;
+                const int64_t src_step = (int64_t)Ntj * TB;
+                for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
+                    const int r = min(kGroup, s.nit - i0);
+                    if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
+                    for (int j = 0; j < r; ++j) {
+                        bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
+                        src += src_step;
+                    }
+                    if (++gs == kPkG) { gs = 0; ph ^= 1; }
                 }
-                good = __shfl_sync(0xffffffffu, good, 0);
-                if (!good) { ok = false; break; }
-                if (lane < r) bulk_g2s(sbase + L::pk + (gs * kGroup + lane) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
-                src += kGroup * src_step;
-                if (++gs == kPkG) { gs = 0; ph ^= 1; }
             }
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp2) {
