@@ -136,6 +136,48 @@ def _workspace(st, nbytes, device_index):
     return st["ws"]
 
 
+_PLANS = {}          # launch descriptions of _fused_linear, keyed by the identity of the weights (which they keep alive)
+_PLANS_MAX = 8192
+
+
+def _fused_plan(op, x, weights, biases):
+    """Everything about a fused launch that depends only on the weights, the biases and the activation's shape: validated
+    once, then reused (a decode step calls the same few hundred launches over and over; rebuilding the argument arrays
+    costs more host time than the kernels take on several GPUs)."""
+    import ctypes
+    from ..peer import _rt
+    padded = tuple(x.shape.padded)
+    key = (tuple(id(w) for w in weights), tuple(id(b) for b in biases) if biases is not None else None, padded, tuple(x.shape))
+    plan = _PLANS.get(key)
+    if plan is not None:
+        return plan
+    ws_local = [_local(w) for w in weights]
+    rows, K, fmt = _check_linear_operands(op, x, ws_local)
+    n = len(ws_local)
+    if not 1 <= n <= 4:
+        raise RuntimeError(f"{op}: between one and four weights per launch")
+    Ns = [list(w.shape.padded)[-1] for w in ws_local]
+    arr_n = (ctypes.c_int64 * n)(*Ns)
+    arr_b = None
+    if biases is not None:
+        arr_b = (ctypes.c_void_p * n)(*[(_local(b).buffer_address() if b is not None else None) for b in biases])
+    lead, lead_padded = list(x.shape)[:-1], list(padded)[:-1]
+    offsets = [0]
+    for N in Ns:
+        offsets.append(offsets[-1] + rows * N)
+    plan = {
+        "keep": (list(weights), list(biases) if biases is not None else None),
+        "rows": rows, "K": K, "fmt": _DTYPE_CODE[fmt], "n": n, "Ns": Ns, "arr_n": arr_n, "arr_b": arr_b,
+        "arr_w": (ctypes.c_void_p * n)(*[w.buffer_address() for w in ws_local]),
+        "need": _rt.cdll.ttb_matmul_multi_workspace_bytes(_DTYPE_CODE[fmt], 1, rows, K, n, arr_n),
+        "offsets": offsets, "lead": lead, "lead_padded": lead_padded, "logical_N": [list(w.shape)[-1] for w in ws_local],
+    }
+    if len(_PLANS) >= _PLANS_MAX:
+        _PLANS.clear()
+    _PLANS[key] = plan
+    return plan
+
+
 def _fused_linear(op, input_tensor, weights, biases, activation, gather_first, ring_slots=8):
     """One launch of ttb_matmul_multi: up to four weights on one activation; optionally the first result is gathered over
     the mesh by the kernel's epilogue. Returns the list of results (MultiDeviceTensor when the input is one)."""
@@ -144,14 +186,9 @@ def _fused_linear(op, input_tensor, weights, biases, activation, gather_first, r
     multi = isinstance(input_tensor, MultiDeviceTensor)
     mesh = input_tensor.mesh if multi else None
     x = _local(input_tensor)
-    ws_local = [_local(w) for w in weights]
-    rows, K, fmt = _check_linear_operands(op, x, ws_local)
-    n = len(ws_local)
-    if not 1 <= n <= 4:
-        raise RuntimeError(f"{op}: between one and four weights per launch")
-    Ns = [list(w.shape.padded)[-1] for w in ws_local]
+    plan = _fused_plan(op, x, weights, biases)
+    rows, K, n, Ns = plan["rows"], plan["K"], plan["n"], plan["Ns"]
     dev = x.device()
-    cuda_dev = torch.device("cuda", dev.id())
     st = _mesh_state(mesh if multi else dev)
     G = mesh.get_num_devices() if multi else 1
     gather = None
@@ -172,35 +209,36 @@ def _fused_linear(op, input_tensor, weights, biases, activation, gather_first, r
     if slot is not None and st["pending"] is not None:
         st["ring"].stream_wait(st["pending"])              # keeps the ranks within one gather of each other
         st["pending"] = None
-    outs = [None if (gather is not None and j == 0) else torch.empty(rows * N, dtype=torch.bfloat16, device=cuda_dev) for j, N in enumerate(Ns)]
-    arr_w = (ctypes.c_void_p * n)(*[w.buffer_address() for w in ws_local])
-    arr_o = (ctypes.c_void_p * n)(*[(o.data_ptr() if o is not None else None) for o in outs])
-    arr_n = (ctypes.c_int64 * n)(*Ns)
-    arr_b = None
-    if biases is not None:
-        arr_b = (ctypes.c_void_p * n)(*[(_local(b).buffer_address() if b is not None else None) for b in biases])
-    need = _rt.cdll.ttb_matmul_multi_workspace_bytes(_DTYPE_CODE[fmt], 1, rows, K, n, arr_n)
+    # one allocation for all local outputs of the launch
+    first_local = 1 if gather is not None else 0
+    offsets = plan["offsets"]
+    total = offsets[n] - offsets[first_local]
+    block = torch.empty(max(total, 1), dtype=torch.bfloat16, device=torch.device("cuda", dev.id())) if total else None
+    base = block.data_ptr() if block is not None else 0
+    ptrs = [None if j < first_local else base + 2 * (offsets[j] - offsets[first_local]) for j in range(n)]
+    arr_o = (ctypes.c_void_p * n)(*ptrs)
+    need = plan["need"]
     ws = _workspace(st, need, dev.id()) if need else None
-    _check(_rt.cdll.ttb_matmul_multi(x.buffer_address(), 0, n, arr_w, _DTYPE_CODE[fmt], arr_b, arr_o, 0, 1, rows, K, arr_n,
+    _check(_rt.cdll.ttb_matmul_multi(x.buffer_address(), 0, n, plan["arr_w"], plan["fmt"], plan["arr_b"], arr_o, 0, 1, rows, K, plan["arr_n"],
                                      _ACT[activation], _MM_WORKSPACE_ZEROED | _MM_WEIGHTS_RESIDENT,
                                      ws.data_ptr() if ws is not None else None, need, gather, wait, None))
     if slot is not None:
         st["pending"] = slot
     results = []
-    lead, lead_padded = list(x.shape)[:-1], list(x.shape.padded)[:-1]
-    for j, (w, o, N) in enumerate(zip(ws_local, outs, Ns)):
-        if o is None:
-            t = _ttnn.wrap_device_memory(st["ring"].out_ptr(slot), T.Shape(lead + [G * list(w.shape)[-1]], lead_padded + [G * N]),
-                                         T.bfloat16, T.TILE_LAYOUT, dev)
+    lead, lead_padded = plan["lead"], plan["lead_padded"]
+    for j in range(n):
+        N, Nl = Ns[j], plan["logical_N"][j]
+        if ptrs[j] is None:
+            t = _ttnn.wrap_device_memory(st["ring"].out_ptr(slot), T.Shape(lead + [G * Nl], lead_padded + [G * N]), T.bfloat16, T.TILE_LAYOUT, dev)
             t = MultiDeviceTensor(t, mesh)
             t._gather_slot = slot
         else:
-            t = _ttnn.wrap_device_memory(o.data_ptr(), T.Shape(lead + [list(w.shape)[-1]], lead_padded + [N]), T.bfloat16, T.TILE_LAYOUT, dev)
+            t = _ttnn.wrap_device_memory(ptrs[j], T.Shape(lead + [Nl], lead_padded + [N]), T.bfloat16, T.TILE_LAYOUT, dev)
             if multi:
                 t = MultiDeviceTensor(t, mesh)
-                t._keepalive = o
+                t._keepalive = block
             else:
-                t = FusedOutput(t, o)
+                t = FusedOutput(t, block)
         results.append(t)
     return results
 
