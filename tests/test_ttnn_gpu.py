@@ -165,3 +165,31 @@ def test_linear_multi_equals_separate_linears(device):
         ttnn.linear_multi(a, ws + ws)                     # more than four weights
     with pytest.raises(RuntimeError):
         ttnn.linear_all_gather(a, ws[0])                  # needs multi-device tensors
+
+
+@pytest.mark.parametrize("dtype,ofmt", [(ttnn.bfloat8_b, 0), (ttnn.bfloat4_b, 1)])
+@pytest.mark.parametrize("shape", [(1, 1, 64, 96), (2, 3, 32, 32), (1, 1, 50, 70)])
+def test_to_layout_with_dtype_packs_on_the_device(device, orc, dtype, ofmt, shape):
+    """ttnn.to_layout(x, TILE_LAYOUT, dtype=bfloat8_b) on a device tensor (the reference's tilize with output_dtype,
+    ttnn/ttnn/operations/core.py:677-711): the packed bytes equal the host packer's on the tile-padded tensor."""
+    x = vectors.randn(51, shape, 0.05)
+    for src in (x, x.bfloat16()):
+        rm = ttnn.from_torch(src, layout=ttnn.ROW_MAJOR_LAYOUT, device=device)
+        t = ttnn.to_layout(rm, ttnn.TILE_LAYOUT, dtype=dtype)
+        assert t.dtype == dtype and t.layout == ttnn.TILE_LAYOUT and list(t.shape) == list(shape)
+        H, W = shape[-2], shape[-1]
+        Hp, Wp = (H + 31) // 32 * 32, (W + 31) // 32 * 32
+        outer = int(np.prod(shape[:-2]))
+        padded = np.zeros((outer, Hp, Wp), dtype=np.float32)
+        padded[:, :H, :W] = src.float().numpy().reshape(outer, H, W)
+        want = orc.pack(orc.tilize(padded, outer, Hp, Wp), ofmt)                   # host packer on the padded, tilized tensor
+        got = ttnn.to_torch(t)                                    # values: unpacked on the device
+        ref = torch.from_numpy(orc.untilize(orc.unpack(want, ofmt), outer, Hp, Wp).reshape(outer, Hp, Wp)[:, :H, :W].copy()).reshape(shape)
+        assert torch.equal(got, ref)
+        # and back: block-float tiles -> bfloat16 tiles on the device
+        back = ttnn.to_layout(t, ttnn.TILE_LAYOUT, dtype=ttnn.bfloat16)
+        assert back.dtype == ttnn.bfloat16 and torch.equal(ttnn.to_torch(back).float(), ref)
+    with pytest.raises(RuntimeError, match="Unsupported datatype conversion"):
+        ttnn.to_layout(ttnn.from_torch(x, layout=ttnn.ROW_MAJOR_LAYOUT), ttnn.TILE_LAYOUT, dtype=dtype)      # not on device
+    with pytest.raises(RuntimeError, match="Unsupported datatype conversion"):
+        ttnn.to_layout(rm, ttnn.ROW_MAJOR_LAYOUT, dtype=dtype)

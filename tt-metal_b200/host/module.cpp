@@ -150,6 +150,7 @@ PYBIND11_MODULE(_ttnn, m) {
     m.def("wrap_device_memory", &wrap_device_memory, py::arg("ptr"), py::arg("shape"), py::arg("dtype"), py::arg("layout"), py::arg("device"),
           py::keep_alive<0, 5>());
     m.def("to_layout", &to_layout);
+    m.def("to_tile_layout_as", &to_tile_layout_as);
     m.def("to_device", &to_device, py::keep_alive<0, 2>());
     m.def("from_device", &from_device);
 

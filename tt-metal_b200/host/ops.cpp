@@ -168,6 +168,43 @@ Tensor to_layout(const Tensor &t, Layout layout) {
     return on_device ? out : to_host_storage(out);
 }
 
+// to_layout(tensor, TILE_LAYOUT, dtype=...) on a device tensor: the reference's ttl.tensor.tilize(output_dtype=dtype)
+// (ttnn/ttnn/operations/core.py:677-711). Row-major (or already tiled) bfloat16 / float32 data becomes a tiled tensor of
+// `dtype`; for block-float targets the device packer applies exactly the host packer's arithmetic (one pass), with the zero
+// padding to tile multiples fused. Block-float sources unpack to bfloat16 / float32 tiles.
+Tensor to_tile_layout_as(const Tensor &t, DataType dtype) {
+    if (t.storage_type() != StorageType::DEVICE) throw_error(std::string("Unsupported datatype conversion to ") + to_string(dtype));
+    if (!t.is_allocated()) throw_error("ttnn.to_layout: the tensor has been deallocated");
+    if (dtype == t.dtype()) return to_layout(t, Layout::TILE);
+    Device *dev = t.device();
+    dev->make_current();
+    const Shape &shape = t.shape();
+    if (shape.rank() < 2) throw_error("ttnn.to_layout: TILE_LAYOUT needs at least 2 dimensions");
+    int64_t outer, H, W;
+    if (is_block_float(dtype)) {
+        if (t.dtype() != DataType::BFLOAT16 && t.dtype() != DataType::FLOAT32)
+            throw_error(std::string("Unsupported datatype conversion to ") + to_string(dtype));
+        const bool row_major = t.layout() == Layout::ROW_MAJOR;
+        if (row_major && shape.has_padding()) throw_error("ttnn.to_layout: unsupported padding on a row-major tensor");
+        Shape out_shape = row_major ? Shape(shape.dims()).tile_padded() : shape;
+        shape.as_outer_hw(outer, H, W, /*padded=*/!row_major);
+        auto dstb = allocate_device_buffer(dev, physical_bytes(out_shape, dtype, Layout::TILE));
+        check(ttb_pack_bfp(t.data(), ttb_dtype(t.dtype()), dstb->ptr, ttb_dtype(dtype), outer, H, W, row_major ? 1 : 0, /*two_pass=*/0, nullptr),
+              "ttnn.to_layout");
+        check(ttb_stream_synchronize(nullptr), "ttnn.to_layout");   // block-float tensors are complete when they are returned
+        return Tensor(dstb, out_shape, dtype, Layout::TILE);
+    }
+    if (is_block_float(t.dtype()) && (dtype == DataType::BFLOAT16 || dtype == DataType::FLOAT32)) {
+        if (t.layout() != Layout::TILE) throw_error(std::string("Unsupported datatype conversion to ") + to_string(dtype));
+        shape.as_outer_hw(outer, H, W, /*padded=*/true);
+        auto dstb = allocate_device_buffer(dev, physical_bytes(shape, dtype, Layout::TILE));
+        check(ttb_unpack_bfp(t.data(), ttb_dtype(t.dtype()), dstb->ptr, ttb_dtype(dtype), outer, H, W, /*dst_row_major=*/0, 0, nullptr), "ttnn.to_layout");
+        return Tensor(dstb, shape, dtype, Layout::TILE);
+    }
+    throw_error(std::string("Unsupported datatype conversion to ") + to_string(dtype));
+    return t;
+}
+
 Tensor to_device(const Tensor &t, Device *device) {
     if (!device) throw_error("ttnn.to_device: device must not be None");
     if (t.storage_type() == StorageType::DEVICE) {

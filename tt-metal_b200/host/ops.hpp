@@ -22,6 +22,7 @@ void to_host_buffer(const Tensor &t, void *dst);
 DataType host_dtype_of(const Tensor &t);
 
 Tensor to_layout(const Tensor &t, Layout layout);   // Tensor::to(Layout), tensor_impl.hpp:158-171
+Tensor to_tile_layout_as(const Tensor &t, DataType dtype);  // ttl.tensor.tilize(output_dtype=...), core.py:677-711
 Tensor to_device(const Tensor &t, Device *device);  // Tensor::to(Device*), tensor_impl.hpp:246-269
 Tensor from_device(const Tensor &t);                // Tensor::cpu(), tensor_impl.hpp:341-358
 // Device tensor over memory owned by the caller (used for collective outputs).

@@ -110,7 +110,11 @@ def to_layout(tensor, layout: T.Layout, dtype=None, memory_config=None, use_mult
         raise RuntimeError(f"Unsupported layout: {layout}")
     t = _unwrap(tensor)
     if dtype is not None and dtype != t.dtype:
-        raise RuntimeError("ttnn.to_layout: changing the data type while changing layout is not supported on this path")
+        # the reference converts the data type only while tilizing a device tensor (ttl.tensor.tilize(output_dtype=dtype),
+        # core.py:677-711); everything else is "Unsupported datatype conversion"
+        if t.storage_type() != T.StorageType.DEVICE or layout != T.TILE_LAYOUT:
+            raise RuntimeError(f"Unsupported datatype conversion to {dtype}")
+        return _rewrap(tensor, _ttnn.to_tile_layout_as(t, dtype))
     return _rewrap(tensor, _ttnn.to_layout(t, layout))
 
 
