@@ -110,10 +110,7 @@ static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t 
     for (int s = 1; s <= 32 && s <= nkb; ++s) {
         const int kbps = (nkb + s - 1) / s;
         if ((nkb + kbps - 1) / kbps != s) continue;
-#ifndef TTB_MIN_KBPS
-#define TTB_MIN_KBPS 8
-#endif
-        if (s > 1 && kbps < TTB_MIN_KBPS) break;
+        if (s > 1 && kbps < 8) break;
         const int rounds = (T * s + kStreamBlocks - 1) / kStreamBlocks;
         const double cost = rounds * (kbps + 6.0 + (s > 1 ? 13.0 + 4.5 * s : 0.0));
         if (cost < best_cost) { best_cost = cost; best_s = s; }

@@ -1,25 +1,23 @@
 // Streamed weight matmul for small row counts (decode), persistent form:
 //   out_j[rows, N_j] = act(a[rows, K] x W_j[K, N_j] + bias_j)   for up to four weights W_j that share the activation.
 //
-// The shared-memory-operand decode kernel (matmul_decode.cu) gives every block one 128-column tile and a fixed share of
-// K; when the tile count does not fill the SMs in whole waves, a quarter of the machine idles (112 tiles on 148 SMs),
-// and every small projection of a decoder layer pays its own launch. Here the work is one list: the 128-column tiles of
-// all weights of the launch, each cut along K into units of `sk_gran` K-blocks. The list is dealt out evenly, in order,
-// to one persistent block per SM. A block therefore works through a few segments - (tile, K range) pairs - with one
-// uninterrupted stream of packed weight tiles: the producer thread keeps prefetching across segment borders, so only
-// the first segment of a block pays the HBM latency. A tile whose K range is shared by several blocks is summed in
-// fp32 with vector reductions (or, in deterministic mode, from per-block partials in block order); the last block to
-// arrive finishes it (bias, activation, store, optional store into the other ranks' copies).
+// Giving every block one 128-column tile and a fixed share of K leaves a quarter of the machine idle whenever the tile
+// count does not fill the SMs in whole waves (112 tiles on 148 SMs), and makes every small projection of a decoder layer
+// pay its own launch. Here the work is one list: the 128-column tiles of all weights of the launch. At most one persistent
+// block per SM works through a few segments - (tile, K range) pairs, chosen by the host's plan (SegIter below) - with one
+// uninterrupted stream of packed weight tiles: the producer thread keeps prefetching across segment borders, so only the
+// first segment of a block pays the HBM latency. A tile whose K range is shared by several blocks is summed in fp32 from
+// per-block partials in block order (few sharers, or deterministic mode) or with vector reductions (many sharers); the
+// last block to arrive finishes it (bias, activation, store, optional store into the other ranks' copies).
 //
-// Roles (12 warps, as in matmul_decode.cu): warp 0 lane 0 streams packed tiles; warps 4 and 8 (lane 0) issue the MMAs
-// of the first and second K step of every stage into their own accumulators; the nine warps with warp % 4 != 0 expand
-// packed codes to bf16 operands. Warps 4..11 also run the epilogue of every segment (TMEM lane quadrant = warp % 4): the
-// MMA issuers take part, so no MMA can overwrite an accumulator that is still being read, while warps 1..3 keep
-// expanding ahead and the producer keeps streaming. Every wait is bounded.
+// Roles (12 warps): warp 0 lane 0 streams packed tiles; warps 4 and 8 (lane 0) issue the MMAs of the first and second K
+// step of every stage into their own accumulators; the nine warps with warp % 4 != 0 expand packed codes to bf16
+// operands. Warps 4..11 also run the epilogue of every segment (TMEM lane quadrant = warp % 4): the MMA issuers take
+// part, so no MMA can overwrite an accumulator that is still being read, while warps 1..3 keep expanding ahead and the
+// producer keeps streaming. Every wait is bounded.
 #include "decode_smem.cuh"
 
 namespace ttb {
-
 
 namespace {
 
@@ -29,7 +27,7 @@ using namespace decode_smem;
 constexpr int kEpiWarp0 = 4;                       // warps 4..11 run epilogues
 constexpr int kEpiThreads = 256;
 
-// Shared memory: the rings of matmul_decode.cu plus a staging slab for the gather epilogue. With 128 rows per block the
+// Shared memory: the packed ring, the operand rings and a staging slab for the gather epilogue. With 128 rows per block the
 // packed ring is shortened to make room.
 template <int FMT, int NB>
 struct StreamLayout {
@@ -144,10 +142,7 @@ struct EpiCtx {
 // Tiles shared by at most this many blocks are summed from per-block partials (plain stores, fixed order); tiles shared
 // by more use fp32 reductions in L2 (when every block of a launch flushes a partial tile at once, 16 KiB of reductions
 // per block cost several microseconds, plain stores a fraction of that).
-#ifndef TTB_PARTIALS_UP_TO
-#define TTB_PARTIALS_UP_TO 4
-#endif
-constexpr int kPartialsUpTo = TTB_PARTIALS_UP_TO;
+constexpr int kPartialsUpTo = 4;
 
 // ---------------- epilogue of one segment, run by warps 4..11 together; returns false after a wait that ran out ----------------
 template <int FMT, int NB>
