@@ -2,7 +2,7 @@
 // tensor memory instead of shared memory.
 //
 // out[rows, N] = act(a[rows, K] x W[K, N] + bias), rows in {32, 64, 128} per block, "swap-AB" as in
-// matmul_decode.cu: the MMA's M dimension (128 TMEM lanes) runs over weight columns, its N dimension over the
+// matmul_decode_stream.cu: the MMA's M dimension (128 TMEM lanes) runs over weight columns, its N dimension over the
 // activation rows.
 //
 // Why tensor memory: expanded to bf16 a weight is two bytes, and writing it to shared memory and having the MMA

@@ -7,7 +7,7 @@
 //     tensor cores' canonical K-major operand layout, so that a producer thread can fetch the [128*R x 32] activation
 //     block of a K step with one bulk copy; the same thread streams the packed weight tiles of the K step;
 //   * nine expand warps turn packed codes into bf16 in shared memory in the canonical N-contiguous operand layout
-//     (the expansion of matmul_decode.cu, here feeding the MMA's B operand);
+//     (the expansion of matmul_decode_stream.cu, here feeding the MMA's B operand);
 //   * one thread issues tcgen05.mma (M = 128 activation rows, N = 128 weight columns, K = 16 per instruction, 2*R per
 //     K block), accumulating in tensor memory; tcgen05.commit releases operand stages;
 //   * eight warps read the accumulators back with tcgen05.ld and apply bias, activation and the bf16 / fp32 store.
