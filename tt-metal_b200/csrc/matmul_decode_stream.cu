@@ -44,6 +44,9 @@ struct StreamLayout {
     static constexpr int nbars = 2 * kPkG + 2 * kAbGroups + 1;
     static constexpr int misc = bars + 8 * nbars;                // tmem base, abort flag, last-block flag
     static constexpr int total = misc + 16;
+    // Three teams of expand warps wait on the ring barriers with different phase parities; that is only right while a
+    // waiter is at most one phase behind, i.e. while no ring has fewer groups than there are teams.
+    static_assert(kExpandWarps / kGroup <= kPkG && kExpandWarps / kGroup <= kAbGroups, "ring shorter than the number of teams");
 };
 
 struct Seg {

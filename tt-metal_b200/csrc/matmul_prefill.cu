@@ -30,11 +30,24 @@ constexpr int kWarps = 12;  // warp 0 producer, warp 4 MMA issuer, warp 8 idle (
 constexpr int kThreads = 32 * kWarps;
 constexpr int kExpandWarps = 9;
 constexpr int kProducerWarp = 0, kMmaWarp = 4;
-constexpr int kGroup = 3;         // stages per barrier group
-constexpr int kPkGroups = 4;      // packed weight ring: 12 stages
-constexpr int kWGroups = 3;       // expanded weight ring: 9 stages of 8 KiB
-constexpr int kActGroups = 2;     // activation ring: 6 stages of R * 8 KiB
-constexpr int kWStageBytes = BN * BK * 2;
+// Ring configuration. H = 128-column halves per block (block width 128 * H). With H = 1 stages travel in groups of
+// three and the nine expand warps form three teams of three (one stage each); with H = 2 (twice the bytes per stage) in
+// groups of two, and eight expand warps form two teams of four (one half of one stage each).
+// A team takes every kTeams-th group. Several teams wait on the same ring barriers with different phase parities; a
+// parity wait is only right while the waiter is at most one phase behind, which holds as long as no ring has fewer groups
+// than there are teams (a team's previous group then already needed the phase before the one it waits for).
+template <int H>
+struct Cfg {
+    static constexpr int kGroup = H == 2 ? 2 : 3;       // stages per barrier group
+    static constexpr int kPkGroups = H == 2 ? 3 : 4;    // packed weight ring
+    static constexpr int kWGroups = H == 2 ? 2 : 3;     // expanded weight ring: stages of H * 8 KiB
+    static constexpr int kActGroups = H == 2 ? 3 : 2;   // activation ring: stages of R * 8 KiB
+    static constexpr int kTeams = H == 2 ? 2 : 3;       // teams of expand warps
+    static constexpr int kMembers = kGroup * H;         // warps per team: one 128-column half of one stage each
+    static constexpr int kWStageBytes = H * BN * BK * 2;
+    static_assert(kTeams <= kPkGroups && kTeams <= kWGroups, "a ring with fewer groups than teams breaks the parity waits");
+    static_assert(kTeams * kMembers <= kExpandWarps, "expand warps");
+};
 constexpr int kActSubBytes = BMS * BK * 2;       // one 128-row activation sub-block of a K step
 constexpr uint32_t kW_LBO = 128, kW_SBO = 512;   // weights (N-contiguous): K-groups adjacent, N-groups 512 B apart
 constexpr uint32_t kX_LBO = 128, kX_SBO = 512;   // activations (K-contiguous): K-groups adjacent, row-groups 512 B apart
@@ -42,21 +55,23 @@ constexpr uint32_t kX_LBO = 128, kX_SBO = 512;   // activations (K-contiguous): 
 template <int FMT>
 struct Pk {
     static constexpr int kTileBytes = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
-    static constexpr int kStageBytes = 4 * kTileBytes;
+    static constexpr int kRunBytes = 4 * kTileBytes;    // the four tiles of one 128-column half for one K block
 };
 
-template <int FMT, int R>
+template <int FMT, int R, int H>
 struct Layout {
+    using C = Cfg<H>;
+    static constexpr int kPkStageBytes = H * Pk<FMT>::kRunBytes;   // the halves of a block are adjacent in the weight
     static constexpr int kActStageBytes = R * kActSubBytes;
     static constexpr int pk = 0;
-    static constexpr int w = pk + kPkGroups * kGroup * Pk<FMT>::kStageBytes;
-    static constexpr int x = w + kWGroups * kGroup * kWStageBytes;
-    static constexpr int bars = x + kActGroups * kGroup * kActStageBytes;
+    static constexpr int w = pk + C::kPkGroups * C::kGroup * kPkStageBytes;
+    static constexpr int x = w + C::kWGroups * C::kGroup * C::kWStageBytes;
+    static constexpr int bars = x + C::kActGroups * C::kGroup * kActStageBytes;
     // barriers: full_pk, empty_pk [kPkGroups]; full_w, empty_w [kWGroups]; full_x, empty_x [kActGroups]; accum
-    static constexpr int nbars = 2 * kPkGroups + 2 * kWGroups + 2 * kActGroups + 1;
+    static constexpr int nbars = 2 * C::kPkGroups + 2 * C::kWGroups + 2 * C::kActGroups + 1;
     static constexpr int misc = bars + 8 * nbars;
     static constexpr int total = misc + 16;
-    static constexpr int kTmemCols = R * BN <= 128 ? 128 : 256;
+    static constexpr int kTmemCols = R * H * BN <= 128 ? 128 : R * H * BN <= 256 ? 256 : 512;
 };
 
 // Re-lays tiled (or row-major) bf16 activations [rows, K] into blocks of [128 rows x 32 K] = 8 KiB, each in the
@@ -134,10 +149,14 @@ struct PrefillArgs {
     int *status;
 };
 
-template <int FMT, int R>
+template <int FMT, int R, int H>
 __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const PrefillArgs p) {
-    using L = Layout<FMT, R>;
+    using L = Layout<FMT, R, H>;
+    using C = Cfg<H>;
     constexpr int TB = Pk<FMT>::kTileBytes;
+    constexpr int kGroup = C::kGroup, kPkGroups = C::kPkGroups, kWGroups = C::kWGroups, kActGroups = C::kActGroups;
+    constexpr int kWStageBytes = C::kWStageBytes;
+    constexpr int BNB = H * BN;   // block width in columns
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const uint32_t sbase = smem_u32(smem);
@@ -162,10 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPkGroups; ++s) {
             mbar_init(full_pk(s), 1);
-            mbar_init(empty_pk(s), kGroup);
+            mbar_init(empty_pk(s), C::kMembers);
         }
         for (int s = 0; s < kWGroups; ++s) {
-            mbar_init(full_w(s), kGroup);
+            mbar_init(full_w(s), C::kMembers);
             mbar_init(empty_w(s), 1);
         }
         for (int s = 0; s < kActGroups; ++s) {
@@ -189,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles and activation blocks -> shared memory ----------------
         if (lane == 0) {
-            const uint8_t *wsrc = p.w + (int64_t)ntile * 4 * TB;
+            const uint8_t *wsrc = p.w + (int64_t)ntile * 4 * H * TB;
             const int64_t w_step = (int64_t)p.Nt * TB;
             const uint8_t *xsrc = p.x + (int64_t)mblock * p.nkb * L::kActStageBytes;
             int gs = 0, gx = 0;
@@ -202,9 +221,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
                 bulk_g2s_plain(sbase + L::x + gx * kGroup * L::kActStageBytes, xsrc, r * L::kActStageBytes, full_x(gx));
                 xsrc += r * L::kActStageBytes;
                 if (!mbar_wait(empty_pk(gs), phs ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
-                mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
+                mbar_arrive_expect_tx(full_pk(gs), r * L::kPkStageBytes);
                 for (int j = 0; j < r; ++j) {
-                    bulk_g2s_plain(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, wsrc, 4 * TB, full_pk(gs));
+                    bulk_g2s_plain(sbase + L::pk + (gs * kGroup + j) * L::kPkStageBytes, wsrc, L::kPkStageBytes, full_pk(gs));
                     wsrc += w_step;
                 }
                 if (++gs == kPkGroups) { gs = 0; phs ^= 1; }
@@ -214,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc_bf16_f32(BMS, BN, /*a_mn_major=*/false, /*b_mn_major=*/true);
+            constexpr uint32_t idesc = instr_desc_bf16_f32(BMS, BNB, /*a_mn_major=*/false, /*b_mn_major=*/true);
             const uint64_t x_desc0 = smem_desc_noswizzle(sbase + L::x, kX_LBO, kX_SBO);
             const uint64_t w_desc0 = smem_desc_noswizzle(sbase + L::w, kW_LBO, kW_SBO);
             const uint32_t x_lo0 = (uint32_t)x_desc0, x_hi = (uint32_t)(x_desc0 >> 32);
@@ -224,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
             uint32_t phw = 0, phx = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);
-                for (int j = r; j < kGroup; ++j) mbar_arrive(full_w(gw));  // stand in for the stages a short last group lacks
+                for (int j = r * H; j < C::kMembers; ++j) mbar_arrive(full_w(gw));  // stand in for the stages a short last group lacks
                 if (!mbar_wait(full_x(gx), phx, abort_flag, p.status, 23)) { ok = false; break; }
                 if (!mbar_wait(full_w(gw), phw, abort_flag, p.status, 24)) { ok = false; break; }
                 tc_fence_after_sync();
@@ -237,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
                         for (int k16 = 0; k16 < BK / 16; ++k16) {
 #pragma unroll
                             for (int rr = 0; rr < R; ++rr)
-                                mma_bf16_ss(tmem_base + (uint32_t)(rr * BN),
+                                mma_bf16_ss(tmem_base + (uint32_t)(rr * BNB),
                                             mk(x_lo + ((j * L::kActStageBytes + rr * kActSubBytes + k16 * 2 * kX_LBO) >> 4), x_hi),
                                             mk(w_lo + ((j * kWStageBytes + k16 * 2 * kW_LBO) >> 4), w_hi), idesc,
                                             j > 0 || k16 > 0 || g > 0);
@@ -256,20 +275,21 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
         const int ew = (warp >> 2) * 3 + (warp & 3) - 1;
         const int lane_pk = lane * (FMT == TTB_BFLOAT8_B ? 16 : 8);
         const int lane_w = ((lane & 15) >> 3) * kW_LBO + (lane >> 4) * 2 * kW_SBO + (lane & 7) * 16;
-        // triplet ew / 3 takes every third group; within a group this warp expands stage ew % 3
-        for (int g = ew / kGroup; g < ngroups; g += kExpandWarps / kGroup) {
-            const int it = g * kGroup + ew % kGroup;
+        // team ew / kMembers takes every kTeams-th group; within a group this warp expands half `hh` of stage `st`
+        const int member = ew % C::kMembers, st = member / H, hh = member % H;
+        for (int g = ew / C::kMembers; ew < C::kTeams * C::kMembers && g < ngroups; g += C::kTeams) {
+            const int it = g * kGroup + st;
             if (it >= nit) break;  // short last group: the MMA issuer arrives in this warp's place
             const int gs = g % kPkGroups, gw = g % kWGroups;
-            const int s = gs * kGroup + ew % kGroup, t = gw * kGroup + ew % kGroup;
+            const int s = gs * kGroup + st, t = gw * kGroup + st;
             const uint32_t phs = (g / kPkGroups) & 1, phw = (g / kWGroups) & 1;
             int good = 1;
             if (lane == 0)
                 good = mbar_wait(empty_w(gw), phw ^ 1, abort_flag, p.status, 25) && mbar_wait(full_pk(gs), phs, abort_flag, p.status, 26);
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) { ok = false; break; }
-            const uint8_t *pst = smem + L::pk + s * Pk<FMT>::kStageBytes;
-            uint8_t *const wst = smem + L::w + t * kWStageBytes + lane_w;
+            const uint8_t *pst = smem + L::pk + s * L::kPkStageBytes + hh * Pk<FMT>::kRunBytes;
+            uint8_t *const wst = smem + L::w + t * kWStageBytes + hh * (BN * BK * 2) + lane_w;
             uint32_t Es[8];
             uint32_t codes[8][4];
 #pragma unroll
@@ -327,11 +347,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
             for (int rr = 0; rr < R; ++rr) {
                 const int64_t row = ((int64_t)mblock * R + rr) * BMS + quad * 32 + lane;
 #pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int col0 = half * 64 + cc * 16;
-                    const int64_t n0 = (int64_t)ntile * BN + col0;
+                for (int cc = 0; cc < BNB / 32; ++cc) {
+                    const int col0 = half * (BNB / 2) + cc * 16;
+                    const int64_t n0 = (int64_t)ntile * BNB + col0;
                     uint32_t r[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(rr * BN + col0), r);
+                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(rr * BNB + col0), r);
                     tmem_ld_wait();
                     float v[16];
                     TTB_DISPATCH_ACT(p.act, {
@@ -378,17 +398,18 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     }
 }
 
-template <int FMT, int R>
+template <int FMT, int R, int H>
 int32_t launch_one(const PrefillArgs &p, dim3 grid, cudaStream_t stream) {
-    constexpr int smem_bytes = Layout<FMT, R>::total + 128;
+    constexpr int smem_bytes = Layout<FMT, R, H>::total + 128;
+    static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_prefill_kernel<FMT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_prefill_kernel<FMT, R, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
-    matmul_prefill_kernel<FMT, R><<<grid, kThreads, smem_bytes, stream>>>(p);
+    matmul_prefill_kernel<FMT, R, H><<<grid, kThreads, smem_bytes, stream>>>(p);
     TTB_LAUNCH_CHECK("matmul_prefill");
     return TTB_OK;
 }
@@ -426,9 +447,16 @@ int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const v
     p.K = K; p.N = N; p.rows = rows; p.Nt = (int)(N / 32); p.nkb = (int)(K / BK);
     p.act = act; p.out_dtype = out_dtype; p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.status = status;
-    dim3 grid((unsigned)(rows / (BMS * R)), (unsigned)(N / BN));
-    if (w_dtype == TTB_BFLOAT8_B) return R == 2 ? launch_one<TTB_BFLOAT8_B, 2>(p, grid, stream) : launch_one<TTB_BFLOAT8_B, 1>(p, grid, stream);
-    return R == 2 ? launch_one<TTB_BFLOAT4_B, 2>(p, grid, stream) : launch_one<TTB_BFLOAT4_B, 1>(p, grid, stream);
+    // 256-column blocks halve how often the activations are fetched from L2 (once per block column): that traffic, not the
+    // tensor pipe, bounds the 128-column form (7.5 GB per launch for the Llama MLP shape).
+    const int H = (R == 2 && N % (2 * BN) == 0) ? 2 : 1;
+    dim3 grid((unsigned)(rows / (BMS * R)), (unsigned)(N / (BN * H)));
+    if (w_dtype == TTB_BFLOAT8_B) {
+        if (H == 2) return launch_one<TTB_BFLOAT8_B, 2, 2>(p, grid, stream);
+        return R == 2 ? launch_one<TTB_BFLOAT8_B, 2, 1>(p, grid, stream) : launch_one<TTB_BFLOAT8_B, 1, 1>(p, grid, stream);
+    }
+    if (H == 2) return launch_one<TTB_BFLOAT4_B, 2, 2>(p, grid, stream);
+    return R == 2 ? launch_one<TTB_BFLOAT4_B, 2, 1>(p, grid, stream) : launch_one<TTB_BFLOAT4_B, 1, 1>(p, grid, stream);
 }
 
 }  // namespace ttb
