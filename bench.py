@@ -499,10 +499,10 @@ def run_gpu_arm(args):
     # DRAM bytes per launch of the dominant kernel, from one profiler capture (dram__bytes_read.sum + dram__bytes_write.sum)
     # of the same kernel, scaled by the bytes a launch covers: the decode kernel moved 93.89 MB (88.15 read + 5.74 written)
     # for 89.21 MB of algorithmic bytes on the Falcon h_to_4h linear (every weight byte is read once, so traffic grows with
-    # the weight); the prefill kernel moved 448.3 MB for 400.6 MB on the Llama MLP prefill linear.
+    # the weight); the prefill kernel moved 525.6 MB (425.4 read + 100.3 written) for 400.6 MB on the Llama MLP prefill linear.
     alg_per_launch = bytes_per_step / launches_per_step
     if tensor_bound:
-        traffic, traffic_src = alg_per_launch * (448.3 / 400.6), "profiles/matmul_prefill_c4_llama70b_mlp.md (same launch)"
+        traffic, traffic_src = alg_per_launch * (525.6 / 400.6), "profiles/matmul_prefill_c4_llama70b_mlp.md (same launch)"
     else:
         traffic, traffic_src = alg_per_launch * (93.89 / 89.21), "profiles/matmul_decode_stream_c2_falcon_h_to_4h.md, scaled x(bytes per launch)"
     line = {
