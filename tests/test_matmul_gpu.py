@@ -143,7 +143,8 @@ def test_weights_with_large_magnitudes(ttb, orc):
 
 
 @pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
-@pytest.mark.parametrize("M,K,N", [(512, 64, 128), (512, 256, 256), (640, 96, 128), (1024, 160, 384), (2048, 512, 256)])
+@pytest.mark.parametrize("M,K,N", [(512, 64, 128), (512, 256, 256), (640, 96, 128), (1024, 160, 384), (2048, 512, 256),
+                                   (512, 64, 19200)])   # the last one: 150 blocks = one wave + a tail launch of small blocks
 def test_prefill_kernel_small_shapes(ttb, orc, w_dtype, M, K, N):
     """Row counts of 512 and more take the compute-bound tensor-core kernel (one or two 128-row accumulators per block)."""
     import torch

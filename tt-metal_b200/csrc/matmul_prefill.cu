@@ -147,6 +147,8 @@ struct PrefillArgs {
     int Nt, nkb;
     int act, out_dtype, out_row_major;
     int *status;
+    int x_R;            // 128-row sub-blocks per row block in the re-laid activations (the R relayout_activations was given)
+    int64_t col_base;   // first weight / output column this launch covers (a multiple of 256)
 };
 
 template <int FMT, int R, int H>
@@ -208,18 +210,28 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles and activation blocks -> shared memory ----------------
         if (lane == 0) {
-            const uint8_t *wsrc = p.w + (int64_t)ntile * 4 * H * TB;
+            const uint8_t *wsrc = p.w + ((p.col_base >> 5) + (int64_t)ntile * 4 * H) * TB;
             const int64_t w_step = (int64_t)p.Nt * TB;
-            const uint8_t *xsrc = p.x + (int64_t)mblock * p.nkb * L::kActStageBytes;
+            // this block's activation sub-blocks inside the re-laid buffer (laid out for row blocks of p.x_R sub-blocks)
+            const int64_t sub0 = (int64_t)mblock * R;
+            const int64_t x_stage_step = (int64_t)p.x_R * kActSubBytes;
+            const uint8_t *xsrc = p.x + ((sub0 / p.x_R) * p.nkb) * x_stage_step + (sub0 % p.x_R) * kActSubBytes;
+            const bool x_contiguous = p.x_R == R;
             int gs = 0, gx = 0;
             uint32_t phs = 0, phx = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);  // stages in this group (the last one may be short)
                 if (!mbar_wait(empty_x(gx), phx ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
                 mbar_arrive_expect_tx(full_x(gx), r * L::kActStageBytes);
-                // the r activation blocks of the group are adjacent in the re-laid buffer
-                bulk_g2s_plain(sbase + L::x + gx * kGroup * L::kActStageBytes, xsrc, r * L::kActStageBytes, full_x(gx));
-                xsrc += r * L::kActStageBytes;
+                if (x_contiguous) {
+                    // the r activation blocks of the group are adjacent in the re-laid buffer
+                    bulk_g2s_plain(sbase + L::x + gx * kGroup * L::kActStageBytes, xsrc, r * L::kActStageBytes, full_x(gx));
+                } else {
+                    for (int j = 0; j < r; ++j)
+                        bulk_g2s_plain(sbase + L::x + (gx * kGroup + j) * L::kActStageBytes, xsrc + j * x_stage_step, L::kActStageBytes,
+                                       full_x(gx));
+                }
+                xsrc += r * x_stage_step;
                 if (!mbar_wait(empty_pk(gs), phs ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
                 mbar_arrive_expect_tx(full_pk(gs), r * L::kPkStageBytes);
                 for (int j = 0; j < r; ++j) {
@@ -349,7 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
 #pragma unroll 1
                 for (int cc = 0; cc < BNB / 32; ++cc) {
                     const int col0 = half * (BNB / 2) + cc * 16;
-                    const int64_t n0 = (int64_t)ntile * BNB + col0;
+                    const int64_t n0 = p.col_base + (int64_t)ntile * BNB + col0;
                     uint32_t r[16];
                     tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(rr * BNB + col0), r);
                     tmem_ld_wait();
@@ -447,10 +459,28 @@ int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const v
     p.K = K; p.N = N; p.rows = rows; p.Nt = (int)(N / 32); p.nkb = (int)(K / BK);
     p.act = act; p.out_dtype = out_dtype; p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     p.status = status;
+    p.x_R = R; p.col_base = 0;
     // 256-column blocks halve how often the activations are fetched from L2 (once per block column): that traffic, not the
     // tensor pipe, bounds the 128-column form (7.5 GB per launch for the Llama MLP shape).
     const int H = (R == 2 && N % (2 * BN) == 0) ? 2 : 1;
     dim3 grid((unsigned)(rows / (BMS * R)), (unsigned)(N / (BN * H)));
+    // Whole waves: one block per SM runs at a time, so a handful of blocks left over after the last full wave would cost a
+    // whole block time (8 of 896 blocks on the Llama MLP shape: 14 %). The column blocks that do not fill a wave are
+    // given to a second launch with quarter-size blocks (128 x 128), whose tail is a quarter as long.
+    constexpr int kSms = 148;
+    const int64_t nblocks = (int64_t)grid.x * grid.y;
+    if (H == 2 && nblocks > kSms && nblocks % kSms != 0 && (nblocks % kSms) * 4 < kSms) {
+        const unsigned cols_main = (unsigned)((nblocks / kSms) * kSms / grid.x);   // column blocks of the main launch
+        if (cols_main > 0 && cols_main < grid.y) {
+            dim3 gmain(grid.x, cols_main);
+            int32_t rc = w_dtype == TTB_BFLOAT8_B ? launch_one<TTB_BFLOAT8_B, 2, 2>(p, gmain, stream) : launch_one<TTB_BFLOAT4_B, 2, 2>(p, gmain, stream);
+            if (rc != TTB_OK) return rc;
+            PrefillArgs q = p;
+            q.col_base = (int64_t)cols_main * 2 * BN;
+            dim3 gtail((unsigned)(rows / BMS), (unsigned)((N - q.col_base) / BN));
+            return w_dtype == TTB_BFLOAT8_B ? launch_one<TTB_BFLOAT8_B, 1, 1>(q, gtail, stream) : launch_one<TTB_BFLOAT4_B, 1, 1>(q, gtail, stream);
+        }
+    }
     if (w_dtype == TTB_BFLOAT8_B) {
         if (H == 2) return launch_one<TTB_BFLOAT8_B, 2, 2>(p, grid, stream);
         return R == 2 ? launch_one<TTB_BFLOAT8_B, 2, 1>(p, grid, stream) : launch_one<TTB_BFLOAT8_B, 1, 1>(p, grid, stream);
