@@ -39,8 +39,8 @@ constexpr int kProducerWarp = 0, kMmaWarp = 4;
 template <int H>
 struct Cfg {
     static constexpr int kGroup = H == 2 ? 2 : 3;       // stages per barrier group
-    static constexpr int kPkGroups = H == 2 ? 3 : 4;    // packed weight ring
-    static constexpr int kWGroups = H == 2 ? 2 : 3;     // expanded weight ring: stages of H * 8 KiB
+    static constexpr int kPkGroups = H == 2 ? 2 : 4;    // packed weight ring
+    static constexpr int kWGroups = 3;                  // expanded weight ring: stages of H * 8 KiB
     static constexpr int kActGroups = H == 2 ? 3 : 2;   // activation ring: stages of R * 8 KiB
     static constexpr int kTeams = H == 2 ? 2 : 3;       // teams of expand warps
     static constexpr int kMembers = kGroup * H;         // warps per team: one 128-column half of one stage each
