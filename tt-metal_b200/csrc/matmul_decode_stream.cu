@@ -15,9 +15,19 @@
 // operands. Warps 4..11 also run the epilogue of every segment (TMEM lane quadrant = warp % 4): the MMA issuers take
 // part, so no MMA can overwrite an accumulator that is still being read, while warps 1..3 keep expanding ahead and the
 // producer keeps streaming. Every wait is bounded.
+#include <cuda.h>
+
 #include "decode_smem.cuh"
 
 namespace ttb {
+
+// One tiled tensor map per weight of a launch: the packed weight seen as [K blocks][tiles per row][tile as 8-byte words], so
+// that the producer fetches the three stages of a group (three K blocks x four tiles) with ONE copy instruction instead of
+// three untiled bulk copies (a single thread needs ~120 ns per copy it issues; with one per stage the producer thread was
+// ~85 % busy. Measured effect on throughput: none - the expand warps bound the pipeline - but the producer now idles).
+struct alignas(64) WeightMaps {
+    CUtensorMap m[TTB_MAX_GROUP];
+};
 
 namespace {
 
@@ -284,7 +294,7 @@ __device__ __forceinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCt
 }
 
 template <int FMT, int NB>
-__global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel(const __grid_constant__ DecodeArgs p) {
+__global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel(const __grid_constant__ DecodeArgs p, const __grid_constant__ WeightMaps maps) {
     using L = StreamLayout<FMT, NB>;
     constexpr int TB = Pk<FMT>::kTileBytes;
     constexpr int kAcc = BK / 16;
@@ -344,9 +354,8 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     // arrivals in the same order for every group.
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles -> shared-memory ring, across segment borders ----------------
-        // One thread. (Letting the whole warp take part - lane 0 waiting, lanes 0..2 issuing a group's copies side by
-        // side - shortens the first ring fill but costs the steady state ~5 %: warp 0 shares its scheduler with the two MMA
-        // issuers, whose single-thread loops feel every extra instruction issued next to them.)
+        // One thread, one tensor-map copy per group. (Letting the whole warp take part costs the steady state ~5 %: warp 0
+        // shares its scheduler with the two MMA issuers, whose single-thread loops feel every instruction issued next to them.)
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
             int gs = 0;
@@ -356,17 +365,13 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
             Seg s;
             while (ok && it.next(p, block, s)) {
                 const TileRef tr = tile_ref(p, s.tile);
-                const int Ntj = (int)(p.Nv[tr.prob] >> 5);
-                const uint8_t *src = p.wv[tr.prob] + ((int64_t)s.kb0 * Ntj + (int64_t)tr.nt * 4) * TB;
-                const int64_t src_step = (int64_t)Ntj * TB;
+                const void *map = &maps.m[tr.prob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    const int r = min(kGroup, s.nit - i0);
                     if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_pk(gs), r * Pk<FMT>::kStageBytes);
-                    for (int j = 0; j < r; ++j) {
-                        bulk_g2s(sbase + L::pk + (gs * kGroup + j) * Pk<FMT>::kStageBytes, src, 4 * TB, full_pk(gs), policy);
-                        src += src_step;
-                    }
+                    // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
+                    // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
+                    mbar_arrive_expect_tx(full_pk(gs), kGroup * Pk<FMT>::kStageBytes);
+                    tma_load_3d(sbase + L::pk + gs * kGroup * Pk<FMT>::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
                     if (++gs == kPkG) { gs = 0; ph ^= 1; }
                 }
             }
@@ -571,7 +576,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
 }
 
 template <int FMT, int NB>
-int32_t launch_one(const DecodeArgs &p, bool overlap, cudaStream_t stream) {
+int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, bool overlap, cudaStream_t stream) {
     constexpr int smem_bytes = StreamLayout<FMT, NB>::total + 128;
     static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
@@ -591,7 +596,7 @@ int32_t launch_one(const DecodeArgs &p, bool overlap, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_stream_kernel<FMT, NB>, p));
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_stream_kernel<FMT, NB>, p, maps));
     TTB_LAUNCH_CHECK("matmul_decode_stream");
     return TTB_OK;
 }
@@ -599,8 +604,40 @@ int32_t launch_one(const DecodeArgs &p, bool overlap, cudaStream_t stream) {
 }  // namespace
 
 
+// Tensor maps of the launch's weights. cuTensorMapEncodeTiled is reached through the runtime's driver entry point (no link
+// against the driver library).
+static int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) {
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        TTB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(TTB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const cuuint64_t tile_bytes = (cuuint64_t)bfp_tile_bytes(fmt);
+    for (int j = 0; j < p.nprob; ++j) {
+        const cuuint64_t Nt = (cuuint64_t)(p.Nv[j] / 32), Kt = (cuuint64_t)p.Kt;
+        const cuuint64_t dims[3] = {tile_bytes / 8, Nt, Kt};
+        const cuuint64_t strides[2] = {tile_bytes, Nt * tile_bytes};
+        const cuuint32_t box[3] = {(cuuint32_t)(tile_bytes / 8), 4, (cuuint32_t)kGroup};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const CUresult r = encode(&maps.m[j], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<uint8_t *>(p.wv[j]), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(TTB_E_CUDA, "cuTensorMapEncodeTiled failed with %d for weight %d", (int)r, j);
+    }
+    for (int j = p.nprob; j < TTB_MAX_GROUP; ++j) maps.m[j] = maps.m[0];
+    return TTB_OK;
+}
+
 int32_t launch_decode_stream(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream) {
-#define TTB_STREAM(F, B) return launch_one<F, B>(p, overlap, stream)
+    WeightMaps maps;
+    if (int32_t rc = make_weight_maps(p, fmt, maps)) return rc;
+#define TTB_STREAM(F, B) return launch_one<F, B>(p, maps, overlap, stream)
     if (fmt == TTB_BFLOAT8_B) {
         if (nb == 32) TTB_STREAM(TTB_BFLOAT8_B, 32);
         if (nb == 64) TTB_STREAM(TTB_BFLOAT8_B, 64);

@@ -91,6 +91,16 @@ __device__ __forceinline__ void bulk_g2s_plain(uint32_t dst_smem, const void *sr
                  : "memory");
 }
 
+// Tiled tensor-map copy, three dimensions (x innermost), global -> shared, completion counted on an mbarrier. The x
+// coordinate times the element size must be a multiple of 16 bytes (callers here always pass x = 0).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void *tensor_map, int x, int y, int z, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(
+            dst_smem),
+        "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+        : "memory");
+}
+
 // ---- tensor memory -------------------------------------------------------------------------------
 // Whole-warp calls. `ncols` is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
