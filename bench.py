@@ -517,7 +517,7 @@ def run_gpu_arm(args):
                 "ms_per_step": e2e_s * 1e3,
                 "api": ("ttnn.from_torch -> ttnn.linear_multi / ttnn.linear x%d%s -> ttnn.to_torch" %
                         (NLAYERS * len(groups), "" if mesh is None else (", gather in the matmul epilogue" if fused_api else " + ttnn.all_gather")))},
-        "gpu_launches": launches_per_step * (3 if tensor_bound else 1) * args.steps,   # prefill: re-layout + main + tail launch
+        "gpu_launches": (launches_per_step * (3 if tensor_bound else 1) + (1 if ring is not None else 0)) * args.steps,   # prefill: re-layout + main + tail launch; fused gather: the step's closing wait kernel
         "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s" if tensor_bound else "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_src, "peak_kind": peak_kind, "kernel": "matmul_prefill_kernel" if tensor_bound else "matmul_decode_stream_kernel",
