@@ -233,6 +233,12 @@ int32_t ttb_matmul_multi(const void *a_dev, int32_t a_dtype, int32_t count, cons
                          const void *const *bias_dev, void *const *out_dev, int32_t out_dtype, int64_t batch, int64_t M,
                          int64_t K, const int64_t *N, int32_t activation, int32_t flags, void *workspace_dev,
                          int64_t workspace_bytes, const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream);
+/* The work decomposition ttb_matmul / ttb_matmul_multi use for a decode shape (no GPU needed). out[0..9] = rows per block,
+ * tiles (128 columns x rows per block) in the launch, persistent blocks, K pieces per tile (1 = whole tiles round by round
+ * plus a streamed remainder), K blocks (of 32) per piece, rounds of whole tiles / pieces, first tile of the streamed
+ * remainder (or the piece count), units of 8 K blocks in the streamed remainder, units per tile, partial-sum slots. */
+int32_t ttb_matmul_decode_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N,
+                               int32_t *out, int32_t out_len);
 /* Holds `stream` until the gather point's current use is complete on this rank (bounded). */
 int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream);
 /* CUDA IPC plumbing for the peer pointers: `handle` is a 64-byte buffer. `ptr_dev` must be the start of an allocation

@@ -48,6 +48,7 @@ _SIGS = {
     "ttb_matmul_peer_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_matmul_peer": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_peer_wait": (_i32, [_vp, _vp]),
+    "ttb_matmul_decode_plan": (_i32, [_i32, _i64, _i64, _i64, _i32, _vp, _vp, _i32]),
     "ttb_matmul_multi_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i32, _vp]),
     "ttb_matmul_multi": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_ipc_export": (_i32, [_vp, _vp]),

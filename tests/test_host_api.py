@@ -164,3 +164,61 @@ def test_mesh_mappers_over_two_gloo_ranks(tmp_path):
     for p in procs:
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0, out.decode()
+
+
+def _walk_plan(plan, nkb):
+    """Re-walks the decomposition of the persistent decode kernel on the CPU exactly as its blocks do (rounds of whole tiles
+    or pieces, then the evenly dealt remainder) and returns {tile: [(kb0, kb1, block), ...]}."""
+    nb, tiles, grid, pieces, kbps, waves, rem0, units, upt, slots = plan
+    q, r = (units // grid, units % grid) if grid else (0, 0)
+    begin = lambda b: b * q + min(b, r)
+    cover = {}
+    for b in range(grid):
+        for w in range(waves):
+            x = w * grid + b
+            if x < rem0:
+                if pieces > 1:
+                    part, tile = divmod(x, tiles)
+                    kb0 = part * kbps
+                    cover.setdefault(tile, []).append((kb0, min(nkb, kb0 + kbps), b))
+                else:
+                    cover.setdefault(x, []).append((0, nkb, b))
+        u, u_end = begin(b), begin(b + 1)
+        while u < u_end:
+            rt = u // upt
+            t0 = rt * upt
+            e = min(u_end, t0 + upt)
+            cover.setdefault(rem0 + rt, []).append(((u - t0) * 8, min(nkb, (e - t0) * 8), b))
+            u = e
+    return cover
+
+
+def test_decode_plan_covers_every_k_block_exactly_once():
+    """Host logic of the persistent decode kernel, no GPU: for single weights and groups of weights, every K block of every
+    128-column tile belongs to exactly one block, blocks never exceed the SM count, and the partial-sum slots suffice."""
+    import ctypes
+    import cabi
+    lib = cabi.load()
+    shapes = [(32, 4544, [18176]), (32, 8192, [8192]), (32, 8192, [8192, 1024, 1024]), (32, 8192, [28672, 28672]), (32, 28672, [8192]),
+              (32, 8192, [1024, 128, 128]), (32, 8192, [128]), (32, 4096, [4096, 1024, 1024]), (64, 4096, [14336, 14336]),
+              (128, 2048, [256]), (256, 16384, [7680]), (96, 1056, [384, 128]), (32, 32, [128]), (32, 8192, [3584, 3584])]
+    for M, K, Ns in shapes:
+        arr = (ctypes.c_int64 * len(Ns))(*Ns)
+        out = (ctypes.c_int32 * 10)()
+        assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, M, K, len(Ns), arr, out, 10) == 0
+        plan = list(out)
+        nb, tiles, grid, pieces, kbps, waves, rem0, units, upt, slots = plan
+        nkb = K // 32
+        assert nb in (32, 64, 128) and M % nb == 0 and tiles == sum(n // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148
+        cover = _walk_plan(plan, nkb)
+        assert sorted(cover) == list(range(tiles)), (M, K, Ns, plan)
+        shared = 0
+        for tile, segs in cover.items():
+            segs.sort()
+            assert segs[0][0] == 0 and segs[-1][1] == nkb and all(a[1] == b[0] for a, b in zip(segs, segs[1:])), (M, K, Ns, tile, segs)
+            assert all(s[1] > s[0] for s in segs)
+            shared += len(segs) if len(segs) > 1 else 0
+        assert shared <= slots or shared == 0, (M, K, Ns, plan, shared)
+    bad = (ctypes.c_int64 * 1)(96)
+    out = (ctypes.c_int32 * 10)()
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == -3

@@ -405,6 +405,20 @@ extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w
                                 (cudaStream_t)stream, gather, wait);
 }
 
+// The work decomposition a launch would use, for callers that want to know the launch geometry (and for tests, which
+// re-walk it on the CPU and check that every K block of every tile is covered exactly once).
+extern "C" int32_t ttb_matmul_decode_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N,
+                                          int32_t *out, int32_t out_len) {
+    using namespace ttb;
+    if (!N || !out || out_len < 10) return fail(TTB_E_INVALID, "ttb_matmul_decode_plan: needs N and room for 10 values");
+    if (batch <= 0 || M <= 0 || !decode_supported_multi(w_dtype, batch * M, K, count, N))
+        return fail(TTB_E_UNSUPPORTED, "ttb_matmul_decode_plan: not a decode shape");
+    const StreamPlan sp = stream_plan(batch * M, K, count, N);
+    const int32_t v[10] = {sp.nb, sp.tiles_total, sp.grid, sp.pieces, sp.kbps, sp.waves, sp.rem_tile0, (int32_t)sp.units, sp.upt, sp.slots};
+    for (int i = 0; i < 10; ++i) out[i] = v[i];
+    return TTB_OK;
+}
+
 // ---- several weights, one activation, one launch ------------------------------------------------------------------------
 extern "C" int64_t ttb_matmul_multi_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N) {
     using namespace ttb;
