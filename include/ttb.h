@@ -56,8 +56,10 @@ extern "C" {
 #define TTB_MM_A_ROW_MAJOR 1   /* activations are row-major [batch*M, K] instead of tiled        */
 #define TTB_MM_OUT_ROW_MAJOR 2 /* write the result row-major (the reference's untilize_out)      */
 #define TTB_MM_FORCE_GENERIC 4 /* use the shape-generic CUDA-core kernel (cross-check path)      */
-#define TTB_MM_DECODE_TMEM_OPERAND 16 /* bfloat8_b decode shapes: feed the expanded weights to the MMA through
-                                         tensor memory (ldmatrix.trans + tcgen05.st) instead of shared memory */
+#define TTB_MM_DECODE_TMEM_OPERAND 16 /* accepted for compatibility: bfloat8_b decode shapes always feed the expanded weights
+                                         to the MMA through tensor memory (ldmatrix.trans + tcgen05.st) */
+#define TTB_MM_DECODE_SMEM_OPERAND 128 /* bfloat8_b decode shapes: use the kernel that expands the weights into shared
+                                          memory instead (the one bfloat4_b weights always use); for cross-checks */
 #define TTB_MM_DETERMINISTIC 32 /* split-K partial sums are added in a fixed order (bit-reproducible results) instead
                                    of with floating-point reductions in arrival order */
 #define TTB_MM_WORKSPACE_ZEROED 8 /* the first 16 MiB + 64 KiB of the workspace are zero: freshly zeroed, or
@@ -79,6 +81,8 @@ int32_t ttb_set_device(int32_t device);
 int32_t ttb_get_device(int32_t *device);
 int32_t ttb_malloc(void **dev_ptr, size_t bytes);
 int32_t ttb_free(void *dev_ptr);
+/* Free and total device memory of the current device, as the CUDA allocator reports them (either pointer may be NULL). */
+int32_t ttb_mem_info(int64_t *free_bytes, int64_t *total_bytes);
 int32_t ttb_host_alloc(void **host_ptr, size_t bytes); /* pinned host memory */
 int32_t ttb_host_free(void *host_ptr);
 int32_t ttb_memcpy_h2d(void *dst_dev, const void *src_host, size_t bytes, void *stream);
@@ -102,6 +106,20 @@ int32_t ttb_tilize(const void *src_dev, void *dst_dev, int32_t elem_size, int64_
 /* Tiled [outer, Hp, Wp] -> row-major [outer, H, W] (the padding is dropped). */
 int32_t ttb_untilize(const void *src_dev, void *dst_dev, int32_t elem_size, int64_t outer, int64_t H, int64_t W,
                      void *stream);
+
+/* ---- pad / unpad of row-major tensors -----------------------------------------------------------
+ * ttb_pad: dst[out_shape] = pad value everywhere except the box starting at `start`, which receives src[in_shape]
+ * (four dimensions, row-major, elem_size 2 or 4 bytes; pad_bits holds the pad value's bit pattern in its low bits).
+ * ttb_unpad: dst = src[start[0]..end[0], ..., start[3]..end[3]] (both ends inclusive, as in the reference).
+ * Replace pad<T> / unpad<T> (tt_eager/tensor/tensor_impl.hpp:508-677), which run on host vectors. */
+int32_t ttb_pad(const void *src_dev, void *dst_dev, int32_t elem_size, const int64_t *in_shape, const int64_t *out_shape,
+                const int64_t *start, uint32_t pad_bits, void *stream);
+int32_t ttb_unpad(const void *src_dev, void *dst_dev, int32_t elem_size, const int64_t *in_shape, const int64_t *start,
+                  const int64_t *end, void *stream);
+
+/* Elementwise product of two bfloat16 buffers of `count` elements (any layout, as long as both share it): the unfused form of
+ * the gated MLP's multiply, tt_lib.tensor.mul in models/demos/llama2_70b/tt/llama_mlp_optimized.py:191-197. */
+int32_t ttb_mul_bf16(const void *a_dev, const void *b_dev, void *out_dev, int64_t count, void *stream);
 
 /* ---- block-float pack / unpack --------------------------------------------------------------
  * ttb_pack_bfp: src (TTB_FLOAT32 or TTB_BFLOAT16) -> packed tiles of `fmt` (TTB_BFLOAT8_B or
@@ -169,8 +187,16 @@ int32_t ttb_matmul_decode_static(const void *a_dev, int32_t a_dtype, const void 
                                  int32_t activation, int32_t flags, void *stream);
 
 /* Reads (and clears) the device-side status word that kernels with bounded waits set when a wait
- * ran out. Synchronises `stream`. Returns TTB_OK or TTB_E_TIMEOUT. */
+ * ran out. Synchronises `stream`. Returns TTB_OK or TTB_E_TIMEOUT. After TTB_E_TIMEOUT the matmul that gave up has
+ * produced no valid output and may have left arrival counters and accumulation tiles of its workspace non-zero:
+ * clear the workspace head (or drop TTB_MM_WORKSPACE_ZEROED for the next call) before reusing it. */
 int32_t ttb_check_status(void *stream);
+/* Limit of every bounded device-side wait (waits for peers' data, and the pipeline barriers inside the matmul kernels,
+ * which get twice this plus a margin), in SM clock cycles, for launches made after the call; 0 restores the built-in
+ * defaults (about ten seconds for peers, one second for barriers). Process-wide, not synchronised with concurrent
+ * launches from other host threads. Stands in for the host-side timeouts of the reference's device polling loops
+ * (a hung Tensix core is detected by the watcher / a dispatch timeout, tt_metal/impl/debug/watcher_server.cpp). */
+int32_t ttb_set_wait_limit_cycles(int64_t cycles);
 
 /* ---- all-gather helper ------------------------------------------------------------------------
  * After a rank-major gather of G slices [rows, cols_per_rank] (what an NCCL all-gather leaves),
@@ -180,6 +206,40 @@ int32_t ttb_check_status(void *stream);
  * (tt_eager/tt_dnn/op_library/all_gather/all_gather_op.cpp:18-104). */
 int32_t ttb_gather_interleave(const void *src_dev, void *dst_dev, int32_t elem_size, int32_t ranks, int64_t rows,
                               int64_t cols_per_rank, void *stream);
+
+/* ---- communicator (one process per GPU) ---------------------------------------------------------
+ * NCCL over NVLink behind plain C, for the general form of ttnn.all_gather. Replaces the ring set-up and the AllGather op of
+ * the reference (tt_eager/tt_dnn/op_library/all_gather/all_gather_op.cpp:18-104, ttnn/ttnn/operations/ccl.py:26-39).
+ * Rank 0 makes a unique id (TTB_COMM_ID_BYTES bytes) and hands it to the other ranks by any means; every rank then calls
+ * ttb_comm_init with its device current. Initialisation is non-blocking inside: the call polls the communicator's state and
+ * gives up after timeout_ms of host time (a peer that never joins) with TTB_E_TIMEOUT, having aborted the half-built
+ * communicator; timeout_ms < 0 waits without limit. ttb_comm_check polls a live communicator for an asynchronous error
+ * (TTB_E_CUDA) or for work still being enqueued (TTB_E_TIMEOUT after timeout_ms); after either, ttb_comm_abort is the only
+ * valid call. ttb_all_gather enqueues out[r * bytes_per_rank ...] = rank r's src on `stream` (rank-major concatenation of
+ * byte runs; tiled shards of one tile row and row-major single-row shards already are the gathered tensor, others go
+ * through ttb_gather_interleave). NCCL is loaded at first use (libnccl.so.2); where it is absent these calls return
+ * TTB_E_UNSUPPORTED and everything else works. */
+#define TTB_COMM_ID_BYTES 128
+int32_t ttb_comm_unique_id(void *id);
+int32_t ttb_comm_init(void **comm, int32_t ranks, int32_t rank, const void *unique_id, int64_t timeout_ms);
+int32_t ttb_comm_check(void *comm, int64_t timeout_ms);
+int32_t ttb_all_gather(void *comm, const void *src_dev, void *dst_dev, int64_t bytes_per_rank, void *stream);
+int32_t ttb_comm_abort(void *comm);   /* tears the communicator down without waiting for its peers; frees `comm` */
+int32_t ttb_comm_destroy(void *comm); /* orderly release after all work has completed; frees `comm` */
+/* The calls above reach the collective library through this table (result codes: 0 success, 7 still in progress, others
+ * errors). Passing a table replaces the library - tests use it to produce a peer that never joins or an asynchronous
+ * error on the host, with no GPU involved; NULL restores the real library. init_rank_config(comm, ranks, id, rank, user). */
+typedef struct ttb_comm_backend {
+    int (*get_unique_id)(void *id);
+    int (*init_rank_config)(void **comm, int ranks, const void *id, int rank, void *user);
+    int (*get_async_error)(void *comm, int *state);
+    int (*all_gather)(const void *src, void *dst, size_t count, int dtype, void *comm, void *stream);
+    int (*abort)(void *comm);
+    int (*destroy)(void *comm);
+    const char *(*error_string)(int code);
+    void *user;
+} ttb_comm_backend;
+int32_t ttb_comm_set_backend(const ttb_comm_backend *backend);
 
 /* ---- matmul with the all-gather in its epilogue (tensor-parallel decode) -------------------------
  * One process per GPU. Every rank computes its column slice out[:, rank*N : (rank+1)*N] of a gathered

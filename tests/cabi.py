@@ -14,6 +14,7 @@ BFLOAT16, FLOAT32, UINT32, BFLOAT8_B, BFLOAT4_B, UINT16 = 0, 1, 2, 3, 4, 6
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 MM_A_ROW_MAJOR, MM_OUT_ROW_MAJOR, MM_FORCE_GENERIC, MM_WORKSPACE_ZEROED, MM_DECODE_TMEM_OPERAND, MM_DETERMINISTIC = 1, 2, 4, 8, 16, 32
 MM_WEIGHTS_RESIDENT = 64
+MM_DECODE_SMEM_OPERAND = 128
 TILE_BYTES = {BFLOAT8_B: 1088, BFLOAT4_B: 576}
 
 _vp, _i32, _i64, _sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
@@ -37,6 +38,9 @@ _SIGS = {
     "ttb_buffer_bytes": (_i64, [_i32, _i64, _i64, _i64]),
     "ttb_tilize": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp]),
     "ttb_untilize": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp]),
+    "ttb_pad": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, ctypes.c_uint32, _vp]),
+    "ttb_unpad": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "ttb_mul_bf16": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "ttb_pack_bfp": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_unpack_bfp": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_matmul_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64, _i32]),
@@ -44,6 +48,8 @@ _SIGS = {
     "ttb_matmul_decode_static": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_matmul_decode_static_scratch_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_check_status": (_i32, [_vp]),
+    "ttb_set_wait_limit_cycles": (_i32, [_i64]),
+    "ttb_mem_info": (_i32, [ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
     "ttb_gather_interleave": (_i32, [_vp, _vp, _i32, _i32, _i64, _i64, _vp]),
     "ttb_matmul_peer_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_matmul_peer": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
@@ -51,6 +57,13 @@ _SIGS = {
     "ttb_matmul_decode_plan": (_i32, [_i32, _i64, _i64, _i64, _i32, _vp, _vp, _i32]),
     "ttb_matmul_multi_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i32, _vp]),
     "ttb_matmul_multi": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    "ttb_comm_unique_id": (_i32, [_vp]),
+    "ttb_comm_init": (_i32, [ctypes.POINTER(_vp), _i32, _i32, _vp, _i64]),
+    "ttb_comm_check": (_i32, [_vp, _i64]),
+    "ttb_all_gather": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "ttb_comm_abort": (_i32, [_vp]),
+    "ttb_comm_destroy": (_i32, [_vp]),
+    "ttb_comm_set_backend": (_i32, [_vp]),
     "ttb_ipc_export": (_i32, [_vp, _vp]),
     "ttb_ipc_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "ttb_ipc_close": (_i32, [_vp]),

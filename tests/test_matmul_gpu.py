@@ -117,18 +117,85 @@ def test_decode_shapes_of_the_benchmark_configurations(ttb, orc, M, K, N, w_dtyp
     check(y, y_ref)
 
 
-@pytest.mark.parametrize("M,K,N", [(32, 64, 128), (32, 96, 128), (32, 416, 256), (64, 256, 256), (128, 192, 128), (32, 4544, 18176), (32, 4096, 1024)])
-def test_tensor_memory_operand_kernel(ttb, orc, M, K, N):
-    """The bfloat8_b decode kernel that feeds weights to the MMA through tensor memory: same operands, fp32 accumulation,
-    so it must agree with the CUDA-core kernel up to summation order, including rows with exponents above 127."""
+def make_big_case(ttb, orc, seed, K, N, w_dtype, slice_cols=1024):
+    """A weight too large for the host oracle to pack whole in test time: generated and packed on the GPU, with a seeded
+    slice of `slice_cols` columns also packed and unpacked by the ORACLE and compared byte for byte with the same tiles
+    of the GPU result (the conversion tests pin the packer everywhere else). Returns the packed weight and the fp32
+    matrix of its unpacked values, both on the device."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(K, N, generator=g, device="cuda") * 0.02
+    packed = ttb.pack(w, w_dtype, 1, K, N)
+    w_ref = ttb.unpack(packed, w_dtype, 1, K, N).reshape(K, N)
+    cols = min(slice_cols, N)
+    c0 = ((seed * 7919) % (N - cols + 32)) // 32 * 32 if N > cols else 0
+    ofmt = 0 if w_dtype == cabi.BFLOAT8_B else 1
+    tb = cabi.TILE_BYTES[w_dtype]
+    want = orc.from_torch(w[:, c0:c0 + cols].contiguous().cpu().numpy(), ofmt, 1, K, cols)
+    got = packed.reshape(K // 32, N // 32, tb)[:, c0 // 32:(c0 + cols) // 32].contiguous().cpu().numpy().reshape(-1)
+    assert np.array_equal(got, want), "GPU-packed tiles differ from the oracle's on the checked column slice"
+    want_f = orc.to_torch(want, ofmt, 1, K, cols).reshape(K, cols)
+    assert np.array_equal(w_ref[:, c0:c0 + cols].cpu().numpy(), want_f), "GPU-unpacked values differ from the oracle's"
+    del w
+    return packed, w_ref
+
+
+# Llama-2-70B decode, the configuration the benchmark times: per layer and per GPU (G = 1, 2, 4, 8 column shards) one
+# launch for q/k/v, one for wo, one for w1/w3 and one for w2; batch 32, seed 4.
+LLAMA_SINGLE = [(8192, 8192 // G) for G in (1, 2, 4, 8)] + [(28672, 8192 // G) for G in (1, 2, 4, 8)]
+LLAMA_GROUPS = [(8192, [8192 // G, 1024 // G, 1024 // G]) for G in (1, 2, 4, 8)] + [(8192, [28672 // G, 28672 // G]) for G in (1, 2, 4, 8)]
+
+
+@pytest.mark.parametrize("K,N", LLAMA_SINGLE)
+def test_llama70b_decode_single_weight_launches(ttb, orc, K, N):
+    import torch
+    M = 32
+    packed, w_ref = make_big_case(ttb, orc, 4 + N, K, N, cabi.BFLOAT8_B)
+    x = vectors.randn(4, (M, K), 1.0).bfloat16()
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    y = ttb.untilize(ttb.matmul(a, packed, cabi.BFLOAT8_B, 1, M, K, N), 1, M, N).reshape(M, N)
+    check(y, x.float().cuda() @ w_ref)
+
+
+@pytest.mark.parametrize("K,Ns", LLAMA_GROUPS)
+def test_llama70b_decode_grouped_launches(ttb, orc, K, Ns):
+    """The q/k/v and w1/w3 launches of the timed step (ttb_matmul_multi), every output against the fp32 reference."""
+    import ctypes
+    import torch
+    M = 32
+    x = vectors.randn(4, (M, K), 1.0).bfloat16()
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    cases = [make_big_case(ttb, orc, 4 + 13 * j + N, K, N, cabi.BFLOAT8_B) for j, N in enumerate(Ns)]
+    outs = [torch.empty(M * N, dtype=torch.bfloat16, device="cuda") for N in Ns]
+    n = len(Ns)
+    arr_w = (ctypes.c_void_p * n)(*[c[0].data_ptr() for c in cases])
+    arr_o = (ctypes.c_void_p * n)(*[t.data_ptr() for t in outs])
+    arr_n = (ctypes.c_int64 * n)(*Ns)
+    nbytes = ttb.matmul_multi_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, n, arr_n)
+    ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    for rep in range(2):
+        ttb.check(ttb.cdll.ttb_matmul_multi(a.data_ptr(), cabi.BFLOAT16, n, arr_w, cabi.BFLOAT8_B, None, arr_o, cabi.BFLOAT16, 1, M, K, arr_n,
+                                            cabi.ACT_NONE, cabi.MM_WORKSPACE_ZEROED | cabi.MM_WEIGHTS_RESIDENT, ws.data_ptr(), nbytes, None, None, None))
+        ttb.check(ttb.check_status(None))
+        for j, N in enumerate(Ns):
+            check(ttb.untilize(outs[j], 1, M, N).reshape(M, N), x.float().cuda() @ cases[j][1])
+
+
+@pytest.mark.parametrize("M,K,N", [(32, 64, 128), (32, 96, 128), (32, 416, 256), (64, 256, 256), (128, 192, 128), (32, 4544, 18176), (32, 4096, 1024),
+                                   (256, 1024, 512), (64, 4096, 2048), (128, 8192, 1024), (96, 2048, 640)])
+def test_both_decode_kernels_agree_with_the_generic_kernel(ttb, orc, M, K, N):
+    """bfloat8_b decode shapes run on the kernel that feeds weights to the MMA through tensor memory (default) or on the
+    one that expands them into shared memory (MM_DECODE_SMEM_OPERAND): same operands, fp32 accumulation, so both must
+    agree with the CUDA-core kernel up to summation order, including rows with exponents above 127."""
     import torch
     x, w_dev, w_ref = make_case(ttb, orc, 17, M, K, N, cabi.BFLOAT8_B, w_std=0.02 if K != 96 else 3.0)
     a = ttb.tilize(x.cuda(), 1, M, K)
-    y1 = ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, out_fp32=True, flags=cabi.MM_DECODE_TMEM_OPERAND)
     y2 = ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, out_fp32=True, flags=cabi.MM_FORCE_GENERIC)
     scale = y2.abs().max().item()
-    assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-4 * scale)
-    check(ttb.untilize(y1, 1, M, N).reshape(M, N), x.float().cuda() @ w_ref.cuda())
+    for flags in (0, cabi.MM_DECODE_SMEM_OPERAND):
+        y1 = ttb.matmul(a, w_dev, cabi.BFLOAT8_B, 1, M, K, N, out_fp32=True, flags=flags)
+        assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-4 * scale)
+        check(ttb.untilize(y1, 1, M, N).reshape(M, N), x.float().cuda() @ w_ref.cuda())
 
 
 def test_weights_with_large_magnitudes(ttb, orc):
@@ -210,7 +277,7 @@ def test_batched_activations_share_the_weight(ttb, orc):
     check(y, x.float() @ w_ref)
 
 
-@pytest.mark.parametrize("flags", [cabi.MM_DETERMINISTIC, 0, cabi.MM_DECODE_TMEM_OPERAND])
+@pytest.mark.parametrize("flags", [cabi.MM_DETERMINISTIC, 0, cabi.MM_DECODE_SMEM_OPERAND, cabi.MM_DECODE_SMEM_OPERAND | cabi.MM_DETERMINISTIC])
 def test_repeated_launches_reuse_scratch(ttb, orc, flags):
     """Split-K scratch (arrival counters, accumulation tiles) must be back to zero after each launch. With
     MM_DETERMINISTIC the partial sums are added in a fixed order and repeated launches agree bit for bit; the default
@@ -242,7 +309,7 @@ def test_repeated_launches_reuse_scratch(ttb, orc, flags):
     assert rc == -4
 
 
-@pytest.mark.parametrize("tmem", [0, cabi.MM_DECODE_TMEM_OPERAND])
+@pytest.mark.parametrize("tmem", [0, cabi.MM_DECODE_SMEM_OPERAND])
 @pytest.mark.parametrize("M", [32, 128])
 def test_overlapped_launches_keep_their_dependencies(ttb, orc, tmem, M):
     """MM_WEIGHTS_RESIDENT lets a decode kernel start while the previous one drains. A chain in which every launch consumes

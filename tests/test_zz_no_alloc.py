@@ -47,9 +47,37 @@ def test_static_scratch_variant_matches_regular_entry_point_twice_in_a_row(ttb, 
     second = _static(ttb, a, w, w_dtype, M, K, N)
     scale = want.abs().max().item()
     for got in (first, second):
-        # same kernel, same fixed reduction order: the tolerance of the kernel-agreement tests is far from needed
+        # Same kernel and operands; the static entry always adds the split-K partial sums in block order, ttb_matmul may
+        # add them in arrival order, so the two can differ in the last bits: the tolerance of the kernel-agreement tests.
         assert torch.allclose(got, want, rtol=1e-4, atol=1e-4 * scale)
-    assert torch.equal(first, second)
+    assert torch.equal(first, second)      # the static entry itself is bit-reproducible
+    # What the name promises: a further call neither takes nor returns device memory (cudaMemGetInfo before and after,
+    # with the output buffer allocated beforehand).
+    import ctypes
+    out = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    before, after = ctypes.c_int64(), ctypes.c_int64()
+    ttb.check(ttb.mem_info(ctypes.byref(before), None))
+    ttb.check(ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), w_dtype, None, out.data_ptr(), cabi.FLOAT32,
+                                                1, M, K, N, 0, 0, None))
+    ttb.check(ttb.check_status(None))
+    ttb.check(ttb.mem_info(ctypes.byref(after), None))
+    assert before.value == after.value
+    assert torch.equal(out, first)
+
+
+def test_static_scratch_variant_takes_the_layout_flags(ttb, orc):
+    """Row-major activations in, row-major result out, through the allocation-free entry point."""
+    import torch
+    from test_matmul_gpu import check, make_case
+    M, K, N = 32, 4096, 1024
+    x, w_dev, w_ref = make_case(ttb, orc, 81, M, K, N, cabi.BFLOAT8_B)
+    out = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    xd = x.cuda().contiguous()
+    ttb.check(ttb.cdll.ttb_matmul_decode_static(xd.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(),
+                                                cabi.FLOAT32, 1, M, K, N, 0, cabi.MM_A_ROW_MAJOR | cabi.MM_OUT_ROW_MAJOR, None))
+    ttb.check(ttb.check_status(None))
+    check(out.reshape(M, N), x.float() @ w_ref)
 
 
 def test_static_scratch_variant_refuses_what_it_cannot_serve(ttb):

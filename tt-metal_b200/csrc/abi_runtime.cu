@@ -47,6 +47,13 @@ int32_t ttb_malloc(void **dev_ptr, size_t bytes) {
     TTB_CUDA_TRY(cudaMalloc(dev_ptr, bytes));
     return TTB_OK;
 }
+int32_t ttb_mem_info(int64_t *free_bytes, int64_t *total_bytes) {
+    size_t f = 0, t = 0;
+    TTB_CUDA_TRY(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = (int64_t)f;
+    if (total_bytes) *total_bytes = (int64_t)t;
+    return TTB_OK;
+}
 int32_t ttb_free(void *dev_ptr) {
     if (dev_ptr) TTB_CUDA_TRY(cudaFree(dev_ptr));
     return TTB_OK;

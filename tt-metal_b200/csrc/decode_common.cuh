@@ -1,10 +1,26 @@
 // Pieces shared by the two decode (small row count) matmul kernels: launch arguments, activation addressing and
 // the epilogue's finish-and-store step.
 #pragma once
+#include <cuda.h>
+
 #include "epilogue.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ttb {
+
+struct DecodeArgs;
+// One tiled tensor map per weight of a launch: the packed weight seen as [K blocks][tiles per row][tile as 8-byte words], so
+// that a producer thread fetches the three stages of a group (three K blocks x four tiles) with ONE copy instruction.
+struct alignas(64) WeightMaps {
+    CUtensorMap m[TTB_MAX_GROUP];
+};
+int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps);
+// The activation [rows, K] (tiled or row-major bf16) as a tensor map whose box is three K blocks of 32 rows, delivered in
+// the MMA's K-major operand layout with the 32-byte swizzle: [K block][16-column half][row][16 values].
+struct alignas(64) ActMap {
+    CUtensorMap m;
+};
+int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map);
 
 struct DecodeArgs {
     const uint8_t *w;
@@ -47,7 +63,17 @@ struct DecodeArgs {
     int sk_waves, sk_rem_tile0;      // rounds of whole tiles (tile = round * sk_grid + block), first tile of the split remainder
     int sk_tiles;                    // tiles in the list (all row chunks)
     int sk_units, sk_q, sk_r;        // units of the streamed remainder; units / blocks and units % blocks
+    // ---- limit of the bounded waits in SM clocks (0 = the built-in defaults), set by ttb_set_wait_limit_cycles ----
+    long long wait_limit;
 };
+
+// Limits of the two kinds of bounded waits of a launch. The barrier waits inside a block outlast the wait for the peers:
+// the roles downstream of the expand warps sit in barrier waits while those wait for activations from other GPUs.
+__device__ __forceinline__ long long peer_wait_limit(const DecodeArgs &p) { return p.wait_limit > 0 ? p.wait_limit : 20000000000LL; }
+__device__ __forceinline__ long long barrier_wait_limit(const DecodeArgs &p) {
+    if (p.wait_limit > 0) return 2 * p.wait_limit + 1000000LL;
+    return p.wait_arrived ? 25000000000LL : 2000000000LL;
+}
 
 // Where a finished tile goes: one weight's output tensor (or its slice of a gathered tensor).
 struct OutView {
@@ -70,9 +96,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *addr) {
 
 // Bounded wait for the peers' slices of a gathered activation (one lane calls it). Returns false and raises the
 // status word after `limit_cycles`, or as soon as another thread of the block gave up.
-__device__ __forceinline__ bool peer_wait(const DecodeArgs &p, volatile int *abort_flag, int code,
-                                          long long limit_cycles = 20000000000LL) {
+__device__ __forceinline__ bool peer_wait(const DecodeArgs &p, volatile int *abort_flag, int code) {
     if (!p.wait_arrived) return true;
+    const long long limit_cycles = peer_wait_limit(p);
     const unsigned expected = *reinterpret_cast<const volatile unsigned *>(p.wait_expected);
     const long long t0 = clock64();
     for (unsigned spin = 1;; ++spin) {

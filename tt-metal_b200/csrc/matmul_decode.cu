@@ -9,6 +9,10 @@ namespace ttb {
 
 __device__ int g_status_word = 0;
 
+// Limit of the bounded device-side waits in SM clocks; 0 = each wait's built-in default. Read at launch time.
+static long long g_wait_limit_cycles = 0;
+long long wait_limit_cycles() { return g_wait_limit_cycles; }
+
 using namespace decode_smem;
 
 // The head of the workspace holds one arrival counter per output tile; the partial sums follow.
@@ -17,7 +21,7 @@ static constexpr int64_t kCounterBytes = 65536;
 // partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
 static constexpr int64_t kAccumBytes = 16 << 20;
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, bool overlap, cudaStream_t stream);
+int32_t launch_decode_tmem(const DecodeArgs &p, int nb, bool overlap, cudaStream_t stream);
 
 // Device address of the status word on the current device (looked up once per device).
 int32_t status_word_address(int **out) {
@@ -40,35 +44,6 @@ static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
            K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes;
-}
-
-// Chooses how many blocks share one output tile along K so that the grid fills the 148 SMs in whole waves.
-void decode_plan(int64_t rows, int64_t K, int64_t N, int *splits_out, int *kb_per_split_out, int *tiles_out, int *nb_out) {
-    const int nb = decode_rows_per_block(rows);
-    const int tiles = (int)(N / BN) * (int)(rows / nb);
-    const int nkb = (int)(K / BK);
-    const int sms = 148;
-    int best_s = 1;
-    double best_cost = 1e30;
-    for (int s = 1; s <= 32 && s <= nkb; ++s) {
-        const int kbps = (nkb + s - 1) / s;
-        const int real_s = (nkb + kbps - 1) / kbps;
-        if (real_s != s) continue;
-        if (s > 1 && kbps < 16) break;
-        const int blocks = tiles * s;
-        const int waves = (blocks + sms - 1) / sms;
-        // time model in units of one K-block: each wave costs its blocks' K-blocks plus a fixed fill/drain
-        // overhead; split partials add a small reduction cost.
-        // in units of one K-block's streaming time (~0.16 us): a wave costs ~4 us to fill and drain, the last block of a
-        // tile spends ~0.25 us per partial on the reduction
-        const double cost = waves * (kbps + 25.0) + (s > 1 ? 6.0 + 1.5 * s : 0.0);
-        if (cost < best_cost) { best_cost = cost; best_s = s; }
-    }
-    const int kbps = (nkb + best_s - 1) / best_s;
-    *splits_out = (nkb + kbps - 1) / kbps;
-    *kb_per_split_out = kbps;
-    *tiles_out = tiles;
-    *nb_out = nb;
 }
 
 // ---- streamed decomposition (matmul_decode_stream.cu) ----------------------------------------------------------------
@@ -171,23 +146,9 @@ int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const i
     return kCounterBytes + (compact ? 0 : kAccumBytes) + stream_partial_bytes(sp);
 }
 
-// Bytes of the tile-split kernels' ordered-mode partials (0 when K is not split).
-static int64_t decode_partial_bytes(int64_t rows, int64_t K, int64_t N) {
-    int s, kbps, tiles, nb;
-    decode_plan(rows, K, N, &s, &kbps, &tiles, &nb);
-    return s == 1 ? 0 : (int64_t)tiles * s * BN * nb * 4;
-}
-static bool decode_accumulate_ok(int64_t rows, int64_t N) { return rows * N * 4 <= kAccumBytes; }
-
 int64_t decode_workspace_bytes_compact(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes_multi(rows, K, 1, &N, true); }
 
-// A single weight may run on either decomposition (the tensor-memory-operand kernel keeps the tile split): enough for both.
-int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) {
-    const int64_t pb = decode_partial_bytes(rows, K, N);
-    const int64_t a = pb ? kCounterBytes + kAccumBytes + pb : 0;
-    const int64_t b = decode_workspace_bytes_multi(rows, K, 1, &N, false);
-    return a > b ? a : b;
-}
+int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes_multi(rows, K, 1, &N, false); }
 
 int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *w, int w_dtype, const void *const *bias, void *const *out,
                                    int out_dtype, int64_t rows, int64_t K, const int64_t *N, int act, int flags, void *workspace,
@@ -200,40 +161,12 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
     p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     if (int32_t rc = status_word_address(&p.status)) return rc;
+    p.wait_limit = g_wait_limit_cycles;
     bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
     if (wait) {
         p.wait_arrived = wait->arrived; p.wait_expected = wait->expected;
     }
     const int nb = decode_rows_per_block(rows);
-    const bool tile_split = nprob == 1 && !compact && !gather && !wait && w_dtype == TTB_BFLOAT8_B &&
-                            ((flags & TTB_MM_DECODE_TMEM_OPERAND) || nb == 128);
-    if (tile_split) {
-        // tensor-memory-operand kernel: one block per (tile, K share)
-        const int64_t N0 = N[0];
-        int tiles, nb2;
-        decode_plan(rows, K, N0, &p.splits, &p.kb_per_split, &tiles, &nb2);
-        p.w = (const uint8_t *)w[0]; p.bias = (const uint16_t *)(bias ? bias[0] : nullptr); p.out = out[0];
-        p.N = N0; p.Nt = (int)(N0 / 32);
-        p.out_n0 = 0; p.out_N = N0; p.out_Nt = p.Nt;
-        p.ordered = (flags & TTB_MM_DETERMINISTIC) != 0 || !decode_accumulate_ok(rows, N0);
-        if (p.splits > 1) {
-            const int64_t need = decode_workspace_bytes(rows, K, N0);
-            if (!workspace || workspace_bytes < need)
-                return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
-                            (long long)workspace_bytes);
-            if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return fail(TTB_E_INVALID, "ttb_matmul: workspace must be 256-byte aligned");
-            p.counters = (int *)workspace;
-            p.accum = (float *)((uint8_t *)workspace + kCounterBytes);
-            p.partial = (float *)((uint8_t *)workspace + kCounterBytes + kAccumBytes);
-            if (!counters_are_zero) {
-                const int64_t zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * N0 * 4);
-                TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
-                overlap = false;
-            }
-        }
-        dim3 grid((unsigned)(N0 / BN), (unsigned)p.splits, (unsigned)(rows / nb));
-        return launch_decode_tmem(p, nb, grid, overlap, stream);
-    }
     // streamed decomposition
     const StreamPlan sp = stream_plan(rows, K, nprob, N);
     p.nprob = nprob;
@@ -281,6 +214,9 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
             overlap = false;   // only kernels may separate a launch from the one it overlaps with
         }
     }
+    // bfloat8_b weights of 32-row blocks reach the MMA through tensor memory; bfloat4_b, larger row blocks (and bfloat8_b
+    // on request) through shared memory
+    if (w_dtype == TTB_BFLOAT8_B && nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND)) return launch_decode_tmem(p, nb, overlap, stream);
     return launch_decode_stream(p, w_dtype, nb, overlap, stream);
 }
 
@@ -400,7 +336,7 @@ extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w
     if (wait && (!wait->arrived || !wait->expected))
         return fail(TTB_E_INVALID, "ttb_matmul_peer: incomplete wait description");
     return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
-                                flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT),
+                                flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT | TTB_MM_DECODE_SMEM_OPERAND),
                                 workspace, workspace_bytes, (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false,
                                 (cudaStream_t)stream, gather, wait);
 }
@@ -459,17 +395,17 @@ extern "C" int32_t ttb_matmul_multi(const void *a, int32_t a_dtype, int32_t coun
     }
     if (wait && (!wait->arrived || !wait->expected)) return fail(TTB_E_INVALID, "ttb_matmul_multi: incomplete wait description");
     return launch_matmul_decode_multi(a, count, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
-                                      flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT),
+                                      flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT | TTB_MM_DECODE_SMEM_OPERAND),
                                       workspace, workspace_bytes, (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false,
                                       (cudaStream_t)stream, gather, wait);
 }
 
 namespace {
-__global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *expected_ptr, int *status) {
+__global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *expected_ptr, int *status, long long limit) {
     const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(expected_ptr);
     const long long t0 = clock64();
     while ((int)(ttb::ld_acquire_sys(arrived) - expected) < 0) {
-        if (clock64() - t0 > 20000000000LL) {
+        if (clock64() - t0 > limit) {
             atomicCAS(status, 0, 7);
             return;
         }
@@ -478,12 +414,19 @@ __global__ void peer_wait_kernel(const uint32_t *arrived, const uint32_t *expect
 }
 }  // namespace
 
+extern "C" int32_t ttb_set_wait_limit_cycles(int64_t cycles) {
+    if (cycles < 0) return ttb::fail(TTB_E_INVALID, "ttb_set_wait_limit_cycles: the limit must be zero (defaults) or positive");
+    ttb::g_wait_limit_cycles = cycles;
+    return TTB_OK;
+}
+
 extern "C" int32_t ttb_peer_wait(const ttb_peer_wait_t *wait, void *stream) {
     using namespace ttb;
     if (!wait || !wait->arrived || !wait->expected) return fail(TTB_E_INVALID, "ttb_peer_wait: incomplete wait description");
     int *status = nullptr;
     if (int32_t rc = status_word_address(&status)) return rc;
-    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(wait->arrived, wait->expected, status);
+    const long long limit = wait_limit_cycles() > 0 ? wait_limit_cycles() : 20000000000LL;
+    peer_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(wait->arrived, wait->expected, status, limit);
     TTB_LAUNCH_CHECK("peer_wait");
     return TTB_OK;
 }

@@ -15,19 +15,9 @@
 // operands. Warps 4..11 also run the epilogue of every segment (TMEM lane quadrant = warp % 4): the MMA issuers take
 // part, so no MMA can overwrite an accumulator that is still being read, while warps 1..3 keep expanding ahead and the
 // producer keeps streaming. Every wait is bounded.
-#include <cuda.h>
-
 #include "decode_smem.cuh"
 
 namespace ttb {
-
-// One tiled tensor map per weight of a launch: the packed weight seen as [K blocks][tiles per row][tile as 8-byte words], so
-// that the producer fetches the three stages of a group (three K blocks x four tiles) with ONE copy instruction instead of
-// three untiled bulk copies (a single thread needs ~120 ns per copy it issues; with one per stage the producer thread was
-// ~85 % busy. Measured effect on throughput: none - the expand warps bound the pipeline - but the producer now idles).
-struct alignas(64) WeightMaps {
-    CUtensorMap m[TTB_MAX_GROUP];
-};
 
 namespace {
 
@@ -318,7 +308,7 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     const int block = (int)blockIdx.x;
     // Limit of every barrier wait, in clocks: about a second, but longer than the peer wait when the activations come from
     // other GPUs (the roles downstream of the expand warps sit in barrier waits while those wait for the peers).
-    const long long lim = p.wait_arrived ? 25000000000LL : 2000000000LL;
+    const long long lim = barrier_wait_limit(p);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPkG; ++s) {
@@ -606,7 +596,7 @@ int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, bool overlap, cu
 
 // Tensor maps of the launch's weights. cuTensorMapEncodeTiled is reached through the runtime's driver entry point (no link
 // against the driver library).
-static int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) {
+int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -623,7 +613,7 @@ static int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) 
         const cuuint64_t Nt = (cuuint64_t)(p.Nv[j] / 32), Kt = (cuuint64_t)p.Kt;
         const cuuint64_t dims[3] = {tile_bytes / 8, Nt, Kt};
         const cuuint64_t strides[2] = {tile_bytes, Nt * tile_bytes};
-        const cuuint32_t box[3] = {(cuuint32_t)(tile_bytes / 8), 4, (cuuint32_t)kGroup};
+        const cuuint32_t box[3] = {(cuuint32_t)(tile_bytes / 8), 4, 3};   // three K blocks = one group of stages in both kernels
         const cuuint32_t estr[3] = {1, 1, 1};
         const CUresult r = encode(&maps.m[j], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<uint8_t *>(p.wv[j]), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -631,6 +621,48 @@ static int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) 
         if (r != CUDA_SUCCESS) return fail(TTB_E_CUDA, "cuTensorMapEncodeTiled failed with %d for weight %d", (int)r, j);
     }
     for (int j = p.nprob; j < TTB_MAX_GROUP; ++j) maps.m[j] = maps.m[0];
+    return TTB_OK;
+}
+
+static int32_t tensor_map_encoder(void **out) {
+    static void *encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        TTB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(TTB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = fn;
+    }
+    *out = encode;
+    return TTB_OK;
+}
+
+int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map) {
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void *fn = nullptr;
+    if (int32_t rc = tensor_map_encoder(&fn)) return rc;
+    EncodeFn encode = reinterpret_cast<EncodeFn>(fn);
+    CUresult r;
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    void *base = const_cast<uint16_t *>(p.a);
+    if (p.a_row_major) {
+        // [rows][K]: 16 values, rows, 16-column chunks
+        const cuuint64_t dims[3] = {16, (cuuint64_t)rows, (cuuint64_t)(p.K / 16)};
+        const cuuint64_t strides[2] = {(cuuint64_t)p.K * 2, 32};
+        const cuuint32_t box[3] = {16, 32, 6};
+        r = encode(&map.m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // tiles of 2048 bytes in (row tile, K tile) order; inside: 16 values, 16 face rows, upper / lower faces, left / right faces
+        const cuuint64_t dims[5] = {16, 16, 2, 2, (cuuint64_t)((rows / 32) * p.Kt)};
+        const cuuint64_t strides[4] = {32, 1024, 512, 2048};
+        const cuuint32_t box[5] = {16, 16, 2, 2, 3};
+        r = encode(&map.m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return fail(TTB_E_CUDA, "cuTensorMapEncodeTiled failed with %d for the activation", (int)r);
     return TTB_OK;
 }
 

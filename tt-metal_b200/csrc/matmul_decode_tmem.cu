@@ -1,61 +1,159 @@
-// Weight-streaming decode matmul for bfloat8_b weights with the weight operand fed to the tensor cores through
-// tensor memory instead of shared memory.
+// Streamed decode matmul for bfloat8_b weights, weight operand through tensor memory, persistent form:
+//   out_j[rows, N_j] = act(a[rows, K] x W_j[K, N_j] + bias_j)   for up to four weights W_j that share the activation.
 //
-// out[rows, N] = act(a[rows, K] x W[K, N] + bias), rows in {32, 64, 128} per block, "swap-AB" as in
-// matmul_decode_stream.cu: the MMA's M dimension (128 TMEM lanes) runs over weight columns, its N dimension over the
-// activation rows.
+// Same work decomposition as matmul_decode_stream.cu (one list of 128-column tiles over all weights of the launch, at most
+// one persistent block per SM working through (tile, K range) segments, partial sums of shared tiles exchanged through
+// scratch, optional store of finished tiles into the other ranks' copies), "swap-AB": the MMA's M dimension (128 TMEM
+// lanes) runs over weight columns, its N dimension over the activation rows.
 //
-// Why tensor memory: expanded to bf16 a weight is two bytes, and writing it to shared memory and having the MMA
-// fetch it back costs four bytes of shared-memory traffic per weight - more than the shared-memory pipe can move at
-// the rate HBM delivers the one packed byte. Here the packed tile goes through shared memory once (bulk copy in,
-// ldmatrix out) and the bf16 values go registers -> tensor memory -> MMA:
-//   * ldmatrix.m16n16.trans.b8 reads a 16x16 face of 8-bit codes transposed, so that a lane holds four consecutive
-//     K values of one weight column - the order the MMA's A operand wants (TMEM lane = column n, TMEM column = K pair);
-//   * the codes become bf16 with one byte-permute, one mask and one packed multiply per pair (subnormal trick:
-//     (sign << 15) | mantissa is the weight divided by 2^E), the per-row powers of two coming from a warp-wide
-//     table of the tile's 64 exponents (one pair per lane, fetched by shuffle);
-//   * tcgen05.st.16x256b has exactly the fragment layout ldmatrix produced, so the expanded registers go to tensor
-//     memory without any shuffle; tcgen05.mma then takes A from tensor memory and the activations (B) from shared memory.
-// A warp can only write the 32 TMEM lanes of its quadrant (warp % 4), i.e. one tile column of the 128-wide block, so
-// the twelve expand warps form three teams of four (one warp per quadrant): team t expands every third group of three
-// K-blocks, all three stages in one turn. One mbarrier per group keeps the producer thread, the MMA-issuing thread and
-// the expand warps to one wait / commit / arrival per three stages.
-// Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
+// Why tensor memory: expanded to bf16 a weight is two bytes; writing it to shared memory and letting the MMA fetch it
+// back costs four bytes of shared-memory traffic per packed byte that HBM delivers. Here a packed tile crosses shared
+// memory once (bulk copy in, ldmatrix out) and the bf16 values go registers -> tensor memory -> MMA:
+//   * ldmatrix.m16n16.trans.b8 reads a 16x16 face of 8-bit codes transposed, so that a lane holds four consecutive K
+//     values of one weight column - the order the MMA's A operand wants (TMEM lane = column n, TMEM column = K pair);
+//   * the codes become bf16 with one byte-permute, one mask and one packed multiply per pair ((sign << 15) | mantissa is,
+//     read as bf16, the weight divided by 2^E); the per-row powers of two come from a warp-wide table of the tile's 64
+//     exponents (one pair per lane, fetched by shuffle);
+//   * tcgen05.st.16x256b has exactly the fragment layout ldmatrix produced; tcgen05.mma takes A from tensor memory and
+//     the activations (B) from shared memory.
+//
+// Roles (20 warps). A warp can only touch the 32 TMEM lanes of its quadrant (warp % 4) = one of the four packed tiles of
+// a stage, so the expand warps 0..11 form three teams of four; team t expands every third group of three K blocks.
+// They do nothing else: no global loads, no epilogue. Warps 12..15 run the epilogues (one per TMEM lane quadrant) on one
+// of two accumulator sets while the MMAs of the next segment fill the other. Warp 16 (one thread) streams the packed
+// tiles with one tensor-map copy per group; warp 19 (one thread) streams the activations of the same group with another
+// tensor-map copy that delivers them in the MMA's swizzled K-major operand layout; warps 17 and 18 (one thread each)
+// issue the MMAs of the first and second K step of every stage into their own accumulators.
+// One ring of eight groups carries everything a group needs - packed tiles and activations in shared memory, expanded
+// weights in tensor memory - and is released as a whole by the commit of the group's MMAs.
+// Every wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include "decode_common.cuh"
 
 namespace ttb {
+
+#ifdef TTB_TIMELINE
+// Scratch instrumentation (never part of the product build): clock stamps of block 0's roles per group of stages.
+__device__ long long g_tl[12][2048];
+#define TL(role, g) do { if (blockIdx.x == 0 && (g) < 2048) g_tl[role][g] = clock64(); } while (0)
+#else
+#define TL(role, g) do { } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
 
-constexpr int BN = 128;  // weight columns per block (MMA M, TMEM lanes)
+constexpr int BN = 128;  // weight columns per tile (MMA M, TMEM lanes)
 constexpr int BK = 32;   // K per stage: one row of four packed tiles
-constexpr int kSets = 3;                       // expand-warp sets = stages per group
-constexpr int kExpandWarps = 4 * kSets;        // warps 0..11; quadrant = warp % 4, set = warp / 4
-constexpr int kProducerWarp = 12, kMmaWarp = 13;
-constexpr int kThreads = 32 * 14;
-constexpr int kEpilogueThreads = 32 * kExpandWarps;
+constexpr int kGroup = 3;                      // stages per group (one barrier round trip per group)
+constexpr int kTeams = 3;                      // expand teams of four warps
+constexpr int kExpandWarps = 4 * kTeams;       // warps 0..11; quadrant = warp % 4, team = warp / 4
+constexpr int kEpiWarp0 = kExpandWarps;        // warps 12..15
+constexpr int kEpiThreads = 128;
+constexpr int kProducerWarp = kEpiWarp0 + 4, kMmaWarp = kProducerWarp + 1, kLoaderWarp = kProducerWarp + 3;   // two MMA issuers
+constexpr int kThreads = 32 * (kLoaderWarp + 1);
 constexpr int kTile = kBfp8TileBytes;
 constexpr int kStageBytes = 4 * kTile;         // 4352
-constexpr int kPkGroups = 8;                   // packed ring: 24 stages = 102 KiB in flight
-constexpr int kAGroups = 4;                    // TMEM A ring: 12 stages x 16 columns
-constexpr int kAColsPerStage = BK / 2;
-constexpr uint32_t kB_LBO = 128, kB_SBO = 512;  // activations, K-contiguous canonical layout without swizzle
+constexpr int kAColsPerStage = BK / 2;         // TMEM columns of one expanded stage (two bf16 per column)
+constexpr uint32_t kB_SBO = 256;               // activations: 32-byte rows, eight rows per swizzle atom
 
 template <int NB>
 struct Layout {
+    static constexpr int kRing = 8;                                // groups in flight
     static constexpr int kBStageBytes = NB * BK * 2;
     static constexpr int pk = 0;
-    static constexpr int b = pk + kPkGroups * kSets * kStageBytes;
-    static constexpr int bars = b + kAGroups * kSets * kBStageBytes;
-    static constexpr int nbars = 2 * kPkGroups + 2 * kAGroups + 1;
-    static constexpr int misc = bars + 8 * nbars;
-    static constexpr int total = misc + 16;
-    static constexpr int kAccCols = 2 * NB;                        // one accumulator per K step of a stage
-    static constexpr int kACol0 = kAccCols;                        // the A ring follows the accumulators
-    static constexpr int kTmemColsUsed = kAccCols + kAGroups * kSets * kAColsPerStage;
+    static constexpr int b = pk + kRing * kGroup * kStageBytes;    // (a multiple of 256: the swizzled operand needs it)
+    static constexpr int stage = b + kRing * kGroup * kBStageBytes;   // [NB x 128] bf16 tiled slab for the gather epilogue
+    static constexpr int bars = stage + NB * BN * 2;
+    // full_pk[kRing], full_a[kRing], empty[kRing], acc_full[2], acc_empty[2]
+    static constexpr int nbars = 3 * kRing + 4;
+    static constexpr int misc = bars + 8 * nbars;                  // tmem base, abort flag, last-block flag, two accumulator-ready flags
+    static constexpr int total = misc + 32;
+    // One accumulator per K step of a stage, each fed by its own issuing thread (a single thread needs ~100 cycles per
+    // MMA it issues; two MMAs per stage would make it the slowest role); the epilogue adds the two.
+    static constexpr int kAccs = 2;
+    static constexpr int kAccCols = 2 * kAccs * NB;                // two sets of kAccs accumulators
+    static constexpr int kACol0 = kAccCols;                        // the A ring follows them
+    static constexpr int kTmemColsUsed = kAccCols + kRing * kGroup * kAColsPerStage;
     static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;
+    static_assert(NB == 32, "one tile row of activations per block");
+    static_assert(kTmemColsUsed <= 512, "tensor memory budget");
+    static_assert(b % 256 == 0 && kBStageBytes % 1024 == 0, "alignment of the swizzled activation operand");
+    // The teams wait on the ring barriers with different phase parities, which is only right while a waiter is at most
+    // one phase behind, i.e. while the ring has at least as many groups as there are teams.
+    static_assert(kTeams <= kRing, "ring shorter than the number of teams");
 };
+
+struct Seg {
+    int tile, kb0, nit, contributors, slot0, slot;
+};
+
+__device__ __forceinline__ int unit_begin(const DecodeArgs &p, int b) { return b * p.sk_q + min(b, p.sk_r); }
+__device__ __forceinline__ int block_of_unit(const DecodeArgs &p, int u) {
+    const int big = p.sk_r * (p.sk_q + 1);
+    return u < big ? u / (p.sk_q + 1) : p.sk_r + (u - big) / p.sk_q;
+}
+
+// A block's segments in order (the plan is described in matmul_decode_stream.cu: pieces taken round by round, or whole
+// tiles round by round followed by the block's share of the evenly streamed remainder).
+struct SegIter {
+    int w, u, u_end;
+    __device__ __forceinline__ void start(const DecodeArgs &p, int block) {
+        w = 0;
+        u = unit_begin(p, block);
+        u_end = unit_begin(p, block + 1);
+    }
+    __device__ __forceinline__ bool next(const DecodeArgs &p, int block, Seg &s) {
+        while (w < p.sk_waves) {
+            const int q = w * p.sk_grid + block;
+            ++w;
+            if (q < p.sk_rem_tile0) {
+                if (p.splits > 1) {
+                    const int part = q / p.sk_tiles;
+                    s.tile = q - part * p.sk_tiles;
+                    s.kb0 = part * p.kb_per_split;
+                    s.nit = min(p.nkb, s.kb0 + p.kb_per_split) - s.kb0;
+                    s.contributors = p.splits;
+                    s.slot0 = s.tile * p.splits;
+                    s.slot = s.slot0 + part;
+                } else {
+                    s.tile = q; s.kb0 = 0; s.nit = p.nkb;
+                    s.contributors = 1; s.slot0 = 0; s.slot = 0;
+                }
+                return true;
+            }
+        }
+        if (u >= u_end) return false;
+        const int rt = u / p.sk_upt;
+        const int t0 = rt * p.sk_upt;
+        const int e = min(u_end, t0 + p.sk_upt);
+        s.tile = p.sk_rem_tile0 + rt;
+        s.kb0 = (u - t0) * p.sk_gran;
+        s.nit = min(p.nkb, (e - t0) * p.sk_gran) - s.kb0;
+        const int fb = block_of_unit(p, t0);
+        s.contributors = block_of_unit(p, t0 + p.sk_upt - 1) - fb + 1;
+        s.slot0 = rt + fb;
+        s.slot = rt + block;
+        u = e;
+        return true;
+    }
+};
+
+struct TileRef {
+    int prob, nt, rchunk;
+};
+__device__ __forceinline__ TileRef tile_ref(const DecodeArgs &p, int tile) {
+    TileRef r;
+    const int per = p.tstart[p.nprob];
+    r.rchunk = tile / per;
+    const int t = tile - r.rchunk * per;
+    r.prob = 0;
+#pragma unroll
+    for (int j = 1; j < TTB_MAX_GROUP; ++j)
+        if (j < p.nprob && t >= p.tstart[j]) r.prob = j;
+    r.nt = t - p.tstart[r.prob];
+    return r;
+}
 
 __device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
@@ -79,53 +177,234 @@ __device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
-// Four codes (consecutive K of one column) -> two packed bf16 pairs, each multiplied by its pair of row scales.
-__device__ __forceinline__ void expand4(uint32_t codes, uint32_t s01, uint32_t s23, uint32_t &o01, uint32_t &o23) {
-    uint32_t x01 = __byte_perm(codes, 0u, 0x1100u) & 0x807f807fu;
-    uint32_t x23 = __byte_perm(codes, 0u, 0x3322u) & 0x807f807fu;
-    __nv_bfloat162 v01 = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&x01), *reinterpret_cast<__nv_bfloat162 *>(&s01));
-    __nv_bfloat162 v23 = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&x23), *reinterpret_cast<__nv_bfloat162 *>(&s23));
-    o01 = *reinterpret_cast<uint32_t *>(&v01);
-    o23 = *reinterpret_cast<uint32_t *>(&v23);
-}
 __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
     __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
     return *reinterpret_cast<uint32_t *>(&v);
 }
+// Four codes (consecutive K of one column) -> two packed bf16 pairs, each multiplied by its pair of row scales.
+__device__ __forceinline__ void expand4(uint32_t codes, uint32_t s01, uint32_t s23, uint32_t &o01, uint32_t &o23) {
+    o01 = mul2(__byte_perm(codes, 0u, 0x1100u) & 0x807f807fu, s01);
+    o23 = mul2(__byte_perm(codes, 0u, 0x3322u) & 0x807f807fu, s23);
+}
+
+// One packed tile (1088 bytes at shared address `tile`) -> the 32 TMEM lanes of this warp's quadrant, 16 columns at a_col.
+// BIG: some exponent of the tile exceeds 127 (a row maximum of 2 or more), whose power of two needs a second factor.
+template <bool BIG>
+__device__ __forceinline__ void expand_tile(uint32_t tile, uint32_t a_col, uint32_t ld_off, uint32_t eh, int sh0) {
+    const uint32_t my_scale = (__vminu2(eh, 0x007f007fu) + 0x007f007fu) << 7;   // 2^min(E, 127) per half
+    const uint32_t my_t = BIG ? (__vmaxu2(__vminu2(eh, 0x00fe00feu), 0x007f007fu) << 7) : 0u;
+    uint32_t top[4], bot[4];
+    ldmatrix_x2_trans_b8(tile + ld_off, top);         // faces 0 (left) and 1 (right): K 0..15
+    ldmatrix_x2_trans_b8(tile + ld_off + 512u, bot);  // faces 2 and 3: K 16..31
+#pragma unroll
+    for (int f = 0; f < 4; ++f) {
+        // face f = 2 * kh + nh; registers {2*nh, 2*nh+1} of the kh-th load: columns lane/4 and lane/4 + 8
+        const uint32_t c0 = (f >> 1) ? bot[2 * (f & 1)] : top[2 * (f & 1)];
+        const uint32_t c1 = (f >> 1) ? bot[2 * (f & 1) + 1] : top[2 * (f & 1) + 1];
+        const uint32_t s01 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0);
+        const uint32_t s23 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0 + 1);
+        uint32_t o[4];
+        expand4(c0, s01, s23, o[0], o[1]);
+        expand4(c1, s01, s23, o[2], o[3]);
+        if (BIG) {
+            const uint32_t t01 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0);
+            const uint32_t t23 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0 + 1);
+            o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
+        }
+        // TMEM lanes 32*quad + 16*nh + {lane/4, lane/4 + 8}; columns: stage base + 8*kh + 2*(lane%4) + {0, 1}
+        tmem_st_16x256b(a_col + ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8), o[0], o[1], o[2], o[3]);
+    }
+}
+__device__ __noinline__ void expand_tile_big(uint32_t tile, uint32_t a_col, uint32_t ld_off, uint32_t eh, int sh0) {
+    expand_tile<true>(tile, a_col, ld_off, eh, sh0);
+}
+
+struct EpiCtx {
+    uint8_t *smem;
+    uint32_t tmem_base, acc_full0, acc_empty0;
+    volatile int *abort_flag;
+    volatile int *last_flag;
+    long long lim;
+};
+
+constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks exchange plain partial tiles (fixed order)
+
+// Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
+// that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
+template <int NB>
+__device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, bool ok) {
+    using L = Layout<NB>;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x - 32 * kEpiWarp0;
+    const int quad = warp & 3;
+    const int buf = seg_idx & 1;
+    const uint32_t acc_full = c.acc_full0 + 8u * buf, acc_empty = c.acc_empty0 + 8u * buf;
+    // one thread waits for the accumulator; the other 127 sleep in a hardware barrier instead of polling
+    volatile int *const ready = c.last_flag + 1 + buf;
+    if (tid == 0) *ready = (ok && mbar_wait(acc_full, (uint32_t)((seg_idx >> 1) & 1), c.abort_flag, p.status, 15, c.lim)) ? 1 : 0;
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+    const bool eok = *ready != 0;
+    tc_fence_after_sync();
+    const TileRef tr = tile_ref(p, s.tile);
+    const int64_t row0 = (int64_t)tr.rchunk * NB;
+    const int64_t n = (int64_t)tr.nt * BN + quad * 32 + lane;
+    const bool gathered = p.ranks > 1 && tr.prob == 0;
+    OutView ov;
+    ov.out = p.outv[tr.prob];
+    ov.bias = p.biasv[tr.prob];
+    ov.n0 = gathered ? p.out_n0 : 0;
+    ov.N = gathered ? p.out_N : p.Nv[tr.prob];
+    ov.Nt = (int)(ov.N >> 5);
+    uint16_t *const stage = gathered ? reinterpret_cast<uint16_t *>(c.smem + L::stage) : nullptr;
+    const int contributors = s.contributors;
+    const bool partials = p.ordered || contributors <= kPartialsUpTo;
+    float *const acc_tile = p.accum + (int64_t)s.tile * BN * NB;
+    const uint32_t t_acc = c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * L::kAccs * NB);
+    constexpr int naccs = L::kAccs;   // every segment holds at least one stage, i.e. one MMA per issuer
+    auto read_accumulator = [&](int col0, float (&v)[16]) {   // sum of the segment's accumulators, 16 rows of this lane's column
+        uint32_t r[16];
+        tmem_ld16(t_acc + (uint32_t)col0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+#pragma unroll
+        for (int a = 1; a < L::kAccs; ++a) {
+            if (a < naccs) {
+                tmem_ld16(t_acc + (uint32_t)(a * NB + col0), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
+            }
+        }
+    };
+    auto release_accumulator = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+    };
+    bool finished = contributors == 1;
+    if (contributors > 1) {
+        // phase 1: hand this block's share over (partial tile or reductions), then learn whether it arrived last
+        if (eok) {
+#pragma unroll
+            for (int cc = 0; cc < NB / 16; ++cc) {
+                const int col0 = cc * 16;
+                float v[16];
+                read_accumulator(col0, v);
+                if (partials) {
+                    float4 *dst = reinterpret_cast<float4 *>(p.partial + ((int64_t)s.slot * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                } else {
+                    float *dst = acc_tile + (quad * 32 + lane) * NB + col0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+        }
+        release_accumulator();
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0) {
+            *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
+            __threadfence();   // acquire side: the other blocks' partial sums, published before their tickets, are visible to
+                               // every thread that passes the next barrier
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        finished = *c.last_flag != 0;
+    }
+    // phase 2: whoever holds the complete sum - the only block of an unshared tile, or the last arriver - finishes the tile
+    if (finished && (eok || contributors > 1)) {
+#pragma unroll
+        for (int cc = 0; cc < NB / 16; ++cc) {
+            const int col0 = cc * 16;
+            float v[16];
+            if (contributors == 1) {
+                read_accumulator(col0, v);
+            } else if (partials) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                // up to four blocks' partials per round: all loads of a round are issued before the first add; the adds
+                // stay in block order
+#pragma unroll 1
+                for (int c0 = 0; c0 < contributors; c0 += 4) {
+                    const float4 *src = reinterpret_cast<const float4 *>(
+                        p.partial + ((int64_t)(s.slot0 + c0) * BN + quad * 32 + lane) * NB + col0);
+                    constexpr int64_t kSlot = (int64_t)BN * NB / 4;   // float4 per slot
+                    const int cnt = min(4, contributors - c0);
+                    float4 x0[4], x1[4], x2[4], x3[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        x0[j] = __ldcg(src + j);
+                        x1[j] = cnt > 1 ? __ldcg(src + kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        x2[j] = cnt > 2 ? __ldcg(src + 2 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        x3[j] = cnt > 3 ? __ldcg(src + 3 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    auto add = [&](const float4 (&x)[4]) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            v[4 * j] += x[j].x; v[4 * j + 1] += x[j].y; v[4 * j + 2] += x[j].z; v[4 * j + 3] += x[j].w;
+                        }
+                    };
+                    add(x0);
+                    if (cnt > 1) add(x1);
+                    if (cnt > 2) add(x2);
+                    if (cnt > 3) add(x3);
+                }
+            } else {
+                float4 *acc = reinterpret_cast<float4 *>(acc_tile + (quad * 32 + lane) * NB + col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 x = __ldcg(acc + j);
+                    v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+                    acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);   // leave zeros for the next launch
+                }
+            }
+            finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+        }
+        if (contributors > 1 && tid == 0) p.counters[s.tile] = 0;
+    }
+    if (contributors == 1) release_accumulator();
+    if (gathered) {
+        // one decision for the four warps, so that all of them take part in gather_send's barriers
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0) *c.last_flag = (finished && *c.abort_flag == 0) ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (*c.last_flag) gather_send<NB>(p, stage, row0, tr.nt, tid, kEpiThreads);   // ends with a barrier: the slab is free again
+    }
+    return eok;
+}
 
 template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const DecodeArgs p) {
+__global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const __grid_constant__ DecodeArgs p, const __grid_constant__ WeightMaps maps, const __grid_constant__ ActMap amap) {
     using L = Layout<NB>;
+    constexpr int kRing = L::kRing;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::bars;
-    auto full_pk = [&](int s) { return bar0 + 8u * s; };
-    auto empty_pk = [&](int s) { return bar0 + 8u * (kPkGroups + s); };
-    auto full_a = [&](int s) { return bar0 + 8u * (2 * kPkGroups + s); };
-    auto empty_a = [&](int s) { return bar0 + 8u * (2 * kPkGroups + kAGroups + s); };
-    const uint32_t accum_bar = bar0 + 8u * (2 * kPkGroups + 2 * kAGroups);
+    auto full_pk = [&](int s) { return bar0 + 8u * s; };                 // packed tiles and activations of the group have landed
+    auto full_a = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's weights are expanded in tensor memory
+    auto empty = [&](int s) { return bar0 + 8u * (2 * kRing + s); };      // the group's MMAs are complete: its slot is free
+    const uint32_t acc_full0 = bar0 + 8u * (3 * kRing), acc_empty0 = acc_full0 + 16u;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
     volatile int *last_flag = reinterpret_cast<volatile int *>(smem + L::misc + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntile = blockIdx.x, split = blockIdx.y, rchunk = blockIdx.z;
-    const int kb0 = split * p.kb_per_split;
-    const int nit = min(p.nkb, kb0 + p.kb_per_split) - kb0;
-    const int ngroups = (nit + kSets - 1) / kSets;
-    const int64_t row0 = (int64_t)rchunk * NB;
+    const int block = (int)blockIdx.x;
+    const long long lim = barrier_wait_limit(p);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPkGroups; ++s) {
-            mbar_init(full_pk(s), 1);
-            mbar_init(empty_pk(s), 4);
+        for (int s = 0; s < kRing; ++s) {
+            mbar_init(full_pk(s), 2);     // the two producer threads, each with its byte count
+            mbar_init(full_a(s), 4);      // the four expand warps of the group's team
+            mbar_init(empty(s), 2);       // the two MMA issuers' commits
         }
-        for (int s = 0; s < kAGroups; ++s) {
-            mbar_init(full_a(s), 4);
-            mbar_init(empty_a(s), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(acc_full0 + 8u * s, 2);
+            mbar_init(acc_empty0 + 8u * s, 4);
         }
-        mbar_init(accum_bar, 1);
         *abort_flag = 0;
         *last_flag = 0;
         fence_mbar_init();
@@ -139,238 +418,176 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
-    // As in the shared-memory kernel: the next kernel may start while this grid drains, and only the packed weights are
-    // read before grid_dep_wait().
+    // The next kernel on the stream may start while this grid drains; before grid_dep_wait() a role reads nothing but
+    // packed weights.
     grid_dep_launch();
 
     if (warp == kProducerWarp) {
-        // ---------------- producer: packed weight tiles -> shared-memory ring, three stages per barrier ----------------
+        // ---------------- packed weight tiles -> shared-memory ring, across segment borders ----------------
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
-            const uint8_t *src = p.w + ((int64_t)kb0 * p.Nt + (int64_t)ntile * 4) * kTile;
-            const int64_t src_step = (int64_t)p.Nt * kTile;
-            int gs = 0;
+            int gs = 0, tlg = 0;
+            (void)tlg;
             uint32_t ph = 0;
-            for (int g = 0; g < ngroups; ++g) {
-                const int r = min(kSets, nit - g * kSets);
-                if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
-                mbar_arrive_expect_tx(full_pk(gs), r * kStageBytes);
-                for (int j = 0; j < r; ++j) {
-                    bulk_g2s(sbase + L::pk + (gs * kSets + j) * kStageBytes, src, kStageBytes, full_pk(gs), policy);
-                    src += src_step;
+            SegIter it;
+            it.start(p, block);
+            Seg s;
+            while (ok && it.next(p, block, s)) {
+                const TileRef tr = tile_ref(p, s.tile);
+                const void *map = &maps.m[tr.prob];
+                for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
+                    if (!mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 11, lim)) { ok = false; break; }
+                    TL(0, tlg); ++tlg;
+                    // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
+                    // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
+                    mbar_arrive_expect_tx(full_pk(gs), kGroup * kStageBytes);
+                    tma_load_3d(sbase + L::pk + gs * kGroup * kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
+                    if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
-                if (++gs == kPkGroups) { gs = 0; ph ^= 1; }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer: A from tensor memory, B (activations) from shared memory ----------------
+    } else if (warp == kLoaderWarp) {
+        // ---------------- activations -> shared memory, one tensor-map copy per group ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/false, /*b_mn_major=*/false);
-            const uint64_t b_desc0 = smem_desc_noswizzle(sbase + L::b, kB_LBO, kB_SBO);
-            const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-            auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
-            int ga = 0;
+            grid_dep_wait();   // the activations are the previous kernel's output
+            if (p.wait_arrived) {
+                if (!peer_wait(p, abort_flag, 6)) ok = false;
+                fence_proxy_async_global();   // what the peers stored, seen by the acquire above, is read by the copy unit next
+            }
+            int gs = 0, tlg = 0;
+            (void)tlg;
             uint32_t ph = 0;
-            for (int g = 0; g < ngroups; ++g) {
-                const int r = min(kSets, nit - g * kSets);
-                if (!mbar_wait(full_a(ga), ph, abort_flag, p.status, 12)) { ok = false; break; }
+            SegIter it;
+            it.start(p, block);
+            Seg s;
+            while (ok && it.next(p, block, s)) {
+                const int rchunk = s.tile / p.tstart[p.nprob];
+                for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
+                    if (!mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 17, lim)) { ok = false; break; }
+                    TL(4, tlg); ++tlg;
+                    mbar_arrive_expect_tx(full_pk(gs), kGroup * L::kBStageBytes);
+                    const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
+                    if (p.a_row_major)
+                        tma_load_3d_plain(dst, &amap.m, 0, rchunk * NB, (s.kb0 + i0) * 2, full_pk(gs));
+                    else
+                        tma_load_5d(dst, &amap.m, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_pk(gs));
+                    if (++gs == kRing) { gs = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+        // ---------------- MMA issuers: A from tensor memory, B (activations) from shared memory ----------------
+        // Issuer k16 multiplies the k16-th half of every stage's K block into its own accumulator.
+        if (lane == 0) {
+            const int k16 = warp - kMmaWarp;
+            constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/false, /*b_mn_major=*/false);
+            const uint64_t b_desc0 = smem_desc_sw32(sbase + L::b + k16 * (L::kBStageBytes / 2), kB_SBO);
+            const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+            const uint32_t a_col0 = tmem_base + (uint32_t)(L::kACol0 + k16 * 8);
+            auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
+            int gs = 0, seg_idx = 0, tlg = 0;
+            (void)tlg;
+            uint32_t ph = 0;
+            SegIter it;
+            it.start(p, block);
+            Seg s;
+            for (; ok && it.next(p, block, s); ++seg_idx) {
+                const int buf = seg_idx & 1;
+                if (!mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, p.status, 16, lim)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t a_col = tmem_base + (uint32_t)(L::kACol0 + ga * kSets * kAColsPerStage);
-                const uint32_t b_lo = b_lo0 + (uint32_t)ga * ((kSets * L::kBStageBytes) >> 4);
-#pragma unroll
-                for (int j = 0; j < kSets; ++j) {
-                    if (j < r) {
-#pragma unroll
-                        for (int k16 = 0; k16 < BK / 16; ++k16)
-                            mma_bf16_ts(tmem_base + (uint32_t)(k16 * NB), a_col + (uint32_t)(j * kAColsPerStage + k16 * 8),
-                                        mk(b_lo + ((j * L::kBStageBytes + k16 * 2 * kB_LBO) >> 4), b_hi), idesc, j > 0 || g > 0);
-                    }
+                const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + k16) * NB);
+                for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
+                    const int r = min(kGroup, s.nit - i0);
+                    if (k16 == 0) { TL(1, tlg); }
+                    // expanded weights; the activations of the group landed before its expansion could start, and waiting on
+                    // their barrier here (complete by now) makes them visible to this thread's MMAs
+                    if (!mbar_wait(full_a(gs), ph, abort_flag, p.status, 12, lim) || !mbar_wait(full_pk(gs), ph, abort_flag, p.status, 18, lim)) { ok = false; break; }
+                    if (k16 == 0) { TL(2, tlg); }
+                    tc_fence_after_sync();
+                    const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)gs * ((kGroup * L::kBStageBytes) >> 4);
+                    mma_bf16_ts(d_tmem, a_col, mk(b_lo, b_hi), idesc, i0 > 0);
+                    if (r > 1) mma_bf16_ts(d_tmem, a_col + kAColsPerStage, mk(b_lo + (L::kBStageBytes >> 4), b_hi), idesc, true);
+                    if (r > 2) mma_bf16_ts(d_tmem, a_col + 2 * kAColsPerStage, mk(b_lo + 2 * (L::kBStageBytes >> 4), b_hi), idesc, true);
+                    mma_commit(empty(gs));
+                    if (k16 == 0) { TL(3, tlg); }
+                    ++tlg;
+                    if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
-                mma_commit(empty_a(ga));
-                if (++ga == kAGroups) { ga = 0; ph ^= 1; }
+                if (ok) mma_commit(acc_full0 + 8u * buf);
             }
-            if (ok) mma_commit(accum_bar);
         }
+    } else if (warp >= kEpiWarp0) {
+        // ---------------- epilogue warps ----------------
+        grid_dep_wait();   // the epilogues touch scratch and outputs
+        if (p.ranks > 1 && blockIdx.x == 0 && warp == kEpiWarp0 && lane == 0) *p.expected = *p.expected + p.launch_arrivals;
+        const EpiCtx ectx = {smem, tmem_base, acc_full0, acc_empty0, abort_flag, last_flag, lim};
+        int seg_idx = 0;
+        SegIter it;
+        it.start(p, block);
+        Seg s;
+        for (; it.next(p, block, s); ++seg_idx) ok = epilogue<NB>(p, ectx, s, seg_idx, ok);
     } else {
-        // ---------------- expand warps: packed codes -> bf16 in tensor memory; activations -> shared memory ----------------
-        // Team warp / 4 (four warps, one per TMEM lane quadrant = tile column) takes every third group and expands all
-        // of its stages in one turn, so the per-turn costs (barrier polls, fences, arrivals) are paid once per three stages.
+        // ---------------- expand warps: packed codes -> bf16 in tensor memory ----------------
         const int team = warp >> 2, quad = warp & 3;
-        constexpr int kActChunks = NB / 32;  // 16-byte activation chunks per lane per stage (NB rows x 4 chunks over 4 warps)
-        uint4 act_regs[kSets][kActChunks];
-        // per-lane source pointers of this lane's chunks at K-block 0 of the block's K range; K-block it is it * step further
-        const uint16_t *act_src[kActChunks];
-#pragma unroll
-        for (int q = 0; q < kActChunks; ++q) {
-            const int c = q * 128 + quad * 32 + lane;
-            act_src[q] = p.a + act_chunk_base(p, row0 + c % NB, c / NB) + (int64_t)kb0 * act_chunk_step(p);
-        }
-        const int act_step = act_chunk_step(p);
-        grid_dep_wait();
-        auto load_act = [&](int g) {
-#pragma unroll
-            for (int j = 0; j < kSets; ++j) {
-                const int it = g * kSets + j;
-                if (it < nit) {
-#pragma unroll
-                    for (int q = 0; q < kActChunks; ++q)
-                        act_regs[j][q] = __ldg(reinterpret_cast<const uint4 *>(act_src[q] + (int64_t)it * act_step));
-                }
-            }
-        };
-        if (team < ngroups) load_act(team);
         // ldmatrix row addresses: lanes 0-15 give the rows of the left face, 16-31 of the right face
         const uint32_t ld_off = 64u + (uint32_t)(lane >> 4) * 256u + (uint32_t)(lane & 15) * 16u;
         const int sh0 = 2 * (lane & 3);  // within a face's 8 scale pairs: this lane's K rows are 4*(lane%4) .. +3
         const uint32_t st_lane = (uint32_t)(quad * 32) << 16;
-        for (int g = team; g < ngroups; g += kSets) {
-            const int r = min(kSets, nit - g * kSets);
-            const int gs = g % kPkGroups, ga = g % kAGroups;
-            const uint32_t phs = (g / kPkGroups) & 1, pha = (g / kAGroups) & 1;
-            int good = 1;
-            if (lane == 0)
-                good = mbar_wait(empty_a(ga), pha ^ 1, abort_flag, p.status, 13) && mbar_wait(full_pk(gs), phs, abort_flag, p.status, 14);
-            good = __shfl_sync(0xffffffffu, good, 0);
-            if (!good) { ok = false; break; }
-#pragma unroll
-            for (int j = 0; j < kSets; ++j) {
-                if (j < r) {
-                    const uint32_t tile = sbase + L::pk + (gs * kSets + j) * kStageBytes + quad * kTile;
-                    // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
-                    const uint32_t e2 = *reinterpret_cast<const uint16_t *>(smem + (tile - sbase) + 2 * lane);
-                    const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
-                    const uint32_t my_scale = (__vminu2(eh, 0x007f007fu) + 0x007f007fu) << 7;   // 2^min(E, 127) per half
-                    const bool big = __any_sync(0xffffffffu, ((eh | (eh >> 16)) & 0x80u) != 0u);
-                    uint32_t top[4], bot[4];
-                    ldmatrix_x2_trans_b8(tile + ld_off, top);         // faces 0 (left) and 1 (right): K 0..15
-                    ldmatrix_x2_trans_b8(tile + ld_off + 512u, bot);  // faces 2 and 3: K 16..31
-                    const uint32_t a_col = tmem_base + st_lane + (uint32_t)(L::kACol0 + (ga * kSets + j) * kAColsPerStage);
-#pragma unroll
-                    for (int f = 0; f < 4; ++f) {
-                        // face f = 2 * kh + nh; registers {2*nh, 2*nh+1} of the kh-th load: columns lane/4 and lane/4 + 8
-                        const uint32_t c0 = (f >> 1) ? bot[2 * (f & 1)] : top[2 * (f & 1)];
-                        const uint32_t c1 = (f >> 1) ? bot[2 * (f & 1) + 1] : top[2 * (f & 1) + 1];
-                        const uint32_t s01 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0);
-                        const uint32_t s23 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0 + 1);
-                        uint32_t o[4];
-                        expand4(c0, s01, s23, o[0], o[1]);
-                        expand4(c1, s01, s23, o[2], o[3]);
-                        if (big) {
-                            // exponents above 127 (row maximum of 2 or more): second factor 2^(E - 127)
-                            const uint32_t my_t = __vmaxu2(__vminu2(eh, 0x00fe00feu), 0x007f007fu) << 7;
-                            const uint32_t t01 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0);
-                            const uint32_t t23 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0 + 1);
-                            o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
-                        }
-                        // TMEM lanes 32*quad + 16*nh + {lane/4, lane/4 + 8}; columns: stage base + 8*kh + 2*(lane%4) + {0, 1}
-                        tmem_st_16x256b(a_col + ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8), o[0], o[1], o[2], o[3]);
-                    }
-                    // activations of this K-block (fetched one turn ahead): this warp stores a quarter of the block
-                    uint8_t *const bst = smem + L::b + (ga * kSets + j) * L::kBStageBytes;
-#pragma unroll
-                    for (int q = 0; q < kActChunks; ++q) {
-                        const int c = q * 128 + quad * 32 + lane;
-                        const int m = c % NB, kc = c / NB;
-                        *reinterpret_cast<uint4 *>(bst + (m >> 3) * kB_SBO + kc * kB_LBO + (m & 7) * 16) = act_regs[j][q];
-                    }
+        const uint32_t pk_quad = sbase + L::pk + quad * kTile;
+        const uint32_t a_col_q = tmem_base + st_lane + (uint32_t)L::kACol0;
+        // the block's groups are numbered across segments; team t takes groups t, t + 3, ...
+        SegIter it;
+        it.start(p, block);
+        Seg cur = {0, 0, 0, 1, 0, 0};
+        int cur_g0 = 0, cur_ng = 0;
+        auto locate = [&](int G) {   // advances `cur` to the segment that holds group G; false once the block's work ends
+            while (G >= cur_g0 + cur_ng) {
+                cur_g0 += cur_ng;
+                if (!it.next(p, block, cur)) {
+                    cur_ng = 0;
+                    return false;
                 }
+                cur_ng = (cur.nit + kGroup - 1) / kGroup;
             }
+            return true;
+        };
+        int G = team;
+        int gs = G % kRing;
+        uint32_t phs = (uint32_t)(G / kRing) & 1u;
+        while (locate(G)) {
+            const int r = min(kGroup, cur.nit - (G - cur_g0) * kGroup);
+            int good = 1;
+            if (lane == 0 && quad == 0) { TL(7, G); }
+            // (the producers waited for the slot to be free before they filled it: the group's place in tensor memory is free too)
+            if (lane == 0) good = mbar_wait(full_pk(gs), phs, abort_flag, p.status, 14, lim);
+            if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
+            if (lane == 0 && quad == 0) { TL(9, G); }
+            tc_fence_after_sync();
+            uint32_t tile = pk_quad + (uint32_t)(gs * kGroup * kStageBytes);
+            uint32_t a_col = a_col_q + (uint32_t)(gs * kGroup * kAColsPerStage);
+#pragma unroll 1
+            for (int j = 0; j < r; ++j) {
+                // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
+                uint32_t e2;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e2) : "r"(tile + 2u * lane));
+                const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
+                if (__any_sync(0xffffffffu, (eh & 0x00800080u) != 0u))
+                    expand_tile_big(tile, a_col, ld_off, eh, sh0);
+                else
+                    expand_tile<false>(tile, a_col, ld_off, eh, sh0);
+                tile += kStageBytes;
+                a_col += kAColsPerStage;
+            }
+            if (lane == 0 && quad == 0) { TL(10, G); }
             tmem_st_wait();
-            fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_a(ga));
-            if (lane == 1) mbar_arrive(empty_pk(gs));
-            if (g + kSets < ngroups) load_act(g + kSets);
-        }
-    }
-
-    if (warp < kExpandWarps) {
-        // ---------------- epilogue: TMEM lane quadrant warp % 4; the three warps of a quadrant share the columns ----------------
-        const int tid = threadIdx.x;
-        const int set = warp >> 2, quad = warp & 3;
-        grid_dep_wait();
-        {
-            int good = ok ? 1 : 0;
-            if (lane == 0 && good && nit > 0) good = mbar_wait(accum_bar, 0, abort_flag, p.status, 15);
-            ok = __shfl_sync(0xffffffffu, good, 0) != 0;
-        }
-        tc_fence_after_sync();
-        const int64_t n = (int64_t)ntile * BN + quad * 32 + lane;
-        const int tile_id = rchunk * gridDim.x + ntile;
-        if (ok && nit > 0) {
-            for (int cc = set; cc < NB / 16; cc += kSets) {
-                const int col0 = cc * 16;
-                float v[16];
-                uint32_t r0[16], r1[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, r0);
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(NB + col0), r1);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]) + __uint_as_float(r1[j]);
-                if (p.splits == 1) {
-                    finish_and_store<NB>(p, v, row0, col0, n);
-                } else if (p.ordered) {
-                    float4 *dst = reinterpret_cast<float4 *>(
-                        p.partial + (((int64_t)tile_id * p.splits + split) * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else {
-                    float *dst = p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) red_add_f32x4(dst + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-            }
-        }
-        if (p.splits > 1) {
-            // The last block to arrive for this output tile adds all partials in split order and finishes.
-            __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
-            if (tid == 0) *last_flag = (atomicAdd(p.counters + tile_id, 1) == p.splits - 1) ? 1 : 0;
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
-            if (*last_flag) {
-                __threadfence();
-                for (int cc = set; cc < NB / 16; cc += kSets) {
-                    const int col0 = cc * 16;
-                    float v[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                    if (p.ordered) {
-                        // four splits per round: all sixteen loads are issued before the first add, the adds stay in split order
-                        for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
-                            float4 x[4][4];
-    #pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const int sp = min(sp0 + u, p.splits - 1);
-                                const float4 *src = reinterpret_cast<const float4 *>(
-                                    p.partial + (((int64_t)tile_id * p.splits + sp) * BN + quad * 32 + lane) * NB + col0);
-    #pragma unroll
-                                for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(src + j);
-                            }
-    #pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                if (sp0 + u < p.splits) {
-    #pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        v[4 * j] += x[u][j].x; v[4 * j + 1] += x[u][j].y; v[4 * j + 2] += x[u][j].z; v[4 * j + 3] += x[u][j].w;
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-                        // the tile's sums are complete: read them and leave zeros behind for the next launch
-                        float4 *acc = reinterpret_cast<float4 *>(p.accum + ((int64_t)tile_id * BN + quad * 32 + lane) * NB + col0);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float4 x = __ldcg(acc + j);
-                            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
-                            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                    }
-                    finish_and_store<NB>(p, v, row0, col0, n);
-                }
-                if (tid == 0) p.counters[tile_id] = 0;  // leave the scratch ready for the next launch
-            }
+            if (lane == 0) mbar_arrive(full_a(gs));
+            if (lane == 0 && quad == 0) { TL(11, G); }
+            G += kTeams;
+            gs += kTeams;
+            if (gs >= kRing) { gs -= kRing; phs ^= 1u; }
         }
     }
 
@@ -378,8 +595,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
     tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag) {
-        // A wait ran out: give copies and MMAs still in flight a bounded time to land before the block's
-        // shared memory and tensor memory are released.
+        // A wait ran out: give copies and MMAs still in flight a bounded time to land before the block's shared memory
+        // and tensor memory are released.
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
         __syncthreads();
@@ -391,8 +608,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const D
 }
 
 template <int NB>
-int32_t launch_one(const DecodeArgs &p, dim3 grid, bool overlap, cudaStream_t stream) {
-    constexpr int smem_bytes = Layout<NB>::total + 128;
+int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, const ActMap &amap, bool overlap, cudaStream_t stream) {
+    constexpr int smem_bytes = Layout<NB>::total + 1024;
+    static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));
@@ -401,7 +619,7 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, bool overlap, cudaStream_t st
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
+    cfg.gridDim = dim3((unsigned)p.sk_grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -410,17 +628,27 @@ int32_t launch_one(const DecodeArgs &p, dim3 grid, bool overlap, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<NB>, p));
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<NB>, p, maps, amap));
     TTB_LAUNCH_CHECK("matmul_decode_tmem");
     return TTB_OK;
 }
 
 }  // namespace
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, dim3 grid, bool overlap, cudaStream_t stream) {
-    if (nb == 32) return launch_one<32>(p, grid, overlap, stream);
-    if (nb == 64) return launch_one<64>(p, grid, overlap, stream);
-    return launch_one<128>(p, grid, overlap, stream);
+#ifdef TTB_TIMELINE
+extern "C" int32_t ttb_debug_timeline(void *host) {
+    TTB_CUDA_TRY(cudaMemcpyFromSymbol(host, g_tl, sizeof(g_tl)));
+    return TTB_OK;
+}
+#endif
+
+int32_t launch_decode_tmem(const DecodeArgs &p, int nb, bool overlap, cudaStream_t stream) {
+    WeightMaps maps;
+    if (int32_t rc = make_weight_maps(p, TTB_BFLOAT8_B, maps)) return rc;
+    if (nb != 32) return fail(TTB_E_UNSUPPORTED, "the tensor-memory-operand decode kernel serves 32-row blocks");
+    ActMap amap;
+    if (int32_t rc = make_act_map(p, (int64_t)(p.sk_tiles / p.tstart[p.nprob]) * 32, amap)) return rc;
+    return launch_one<32>(p, maps, amap, overlap, stream);
 }
 
 }  // namespace ttb

@@ -34,6 +34,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is incomplete (it wakes
+// early when the phase completes): a waiting thread then issues an instruction every few microseconds instead of spinning
+// through the issue slots of the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait. Gives up after `limit_cycles` SM clocks or as soon as another thread of the block
 // has given up (*abort_flag != 0); on giving up it raises the block's abort flag, records `code`
 // in the global status word and returns false. The caller then skips to the kernel's teardown.
@@ -42,15 +59,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0u) {
+        if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
+        if ((spin & 7u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 atomicCAS(status_word, 0, code);
                 return false;
             }
-            __nanosleep(32);
         }
     }
 }
@@ -101,6 +117,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void *tenso
         : "memory");
 }
 
+// The same with five dimensions.
+__device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const void *tensor_map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst_smem),
+        "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_plain(uint32_t dst_smem, const void *tensor_map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+        "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+// Makes writes of other GPUs (or of earlier kernels) that this thread has observed through generic loads visible to the
+// asynchronous proxy, i.e. to tensor-map copies this thread issues afterwards.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
 // ---- tensor memory -------------------------------------------------------------------------------
 // Whole-warp calls. `ncols` is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -121,6 +154,14 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ uint64_t smem_desc_noswizzle(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+
+// K-major operand with the 32-byte swizzle: rows of 32 bytes (16 bf16 = one MMA K step), eight rows form a 256-byte atom
+// inside which the 16-byte half of a row is exchanged for rows 4..7 (address bit 4 ^= bit 7) - the pattern a tensor-map
+// copy with CU_TENSOR_MAP_SWIZZLE_32B writes. `sbo` = bytes between 8-row groups; the leading offset is unused (1).
+// The operand must start on a 256-byte boundary. Bits [61,64): 6 = 32-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t addr, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | (6ull << 61);
 }
 
 // Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator.

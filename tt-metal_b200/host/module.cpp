@@ -116,6 +116,15 @@ PYBIND11_MODULE(_ttnn, m) {
         .def("to", [](const Tensor &t, Device *d) { return to_device(t, d); }, py::keep_alive<0, 2>())
         .def("to", [](const Tensor &t, Device *d, const MemoryConfig &) { return to_device(t, d); }, py::keep_alive<0, 2>())
         .def("cpu", [](const Tensor &t) { return from_device(t); })
+        .def("pad", [](const Tensor &t, const std::vector<int64_t> &output_tensor_shape, const std::vector<int64_t> &input_tensor_start,
+                       float pad_value) { return pad(t, output_tensor_shape, input_tensor_start, pad_value); },
+             py::arg("output_tensor_shape"), py::arg("input_tensor_start"), py::arg("pad_value"))
+        .def("unpad", [](const Tensor &t, const std::vector<int64_t> &output_tensor_start, const std::vector<int64_t> &output_tensor_end) {
+                 return unpad(t, output_tensor_start, output_tensor_end);
+             }, py::arg("output_tensor_start"), py::arg("output_tensor_end"))
+        .def("pad_to_tile", [](const Tensor &t, float pad_value) { return pad_to_tile(t, pad_value); }, py::arg("pad_value"))
+        .def("unpad_from_tile", [](const Tensor &t, const std::vector<int64_t> &output_tensor_shape) { return unpad_from_tile(t, output_tensor_shape); },
+             py::arg("output_tensor_shape"))
         .def("host_dtype", [](const Tensor &t) { return host_dtype_of(t); })
         .def("copy_to_host_pointer", [](const Tensor &t, uint64_t ptr) {
             py::gil_scoped_release release;
@@ -154,6 +163,7 @@ PYBIND11_MODULE(_ttnn, m) {
     m.def("to_device", &to_device, py::keep_alive<0, 2>());
     m.def("from_device", &from_device);
 
+    m.def("mul", &multiply, py::arg("input_tensor_a"), py::arg("input_tensor_b"));
     m.def("matmul", &matmul, py::arg("input_tensor_a"), py::arg("input_tensor_b"), py::kw_only(), py::arg("dtype") = std::nullopt,
           py::arg("program_config") = std::nullopt);
     m.def("linear", &linear, py::arg("input_tensor_a"), py::arg("input_tensor_b"), py::kw_only(), py::arg("bias") = std::nullopt,

@@ -1,5 +1,6 @@
 #include "ops.hpp"
 
+#include <algorithm>
 #include <cstring>
 
 namespace ttnn_b200 {
@@ -67,6 +68,9 @@ Tensor from_host_buffer(const void *src, const std::vector<int64_t> &dims, DataT
     auto staged = upload(dev, src, src_bytes);
     Tensor out;
     if (layout == Layout::ROW_MAJOR) {
+        // the source (possibly a temporary of the caller, possibly pinned: then the copy is truly asynchronous) may be
+        // released or overwritten as soon as this returns
+        check(ttb_stream_synchronize(nullptr), "ttnn.from_torch");
         out = Tensor(staged, logical, dtype, layout);
     } else {
         Shape shape = logical.tile_padded();
@@ -224,6 +228,143 @@ Tensor from_device(const Tensor &t) {
 Tensor wrap_device_memory(uint64_t ptr, const Shape &shape, DataType dtype, Layout layout, Device *device) {
     if (!device) throw_error("ttnn: wrap_device_memory needs a device");
     return Tensor(borrow_device_buffer(device, reinterpret_cast<void *>(ptr), physical_bytes(shape, dtype, layout)), shape, dtype, layout);
+}
+
+// ---- pad / unpad -----------------------------------------------------------------------------------------
+namespace {
+
+std::vector<int64_t> as4(const std::vector<int64_t> &v, int64_t fill, const char *what) {
+    if (v.empty() || v.size() > 4) throw_error(std::string(what) + ": shapes have one to four dimensions");
+    std::vector<int64_t> out(4 - v.size(), fill);
+    out.insert(out.end(), v.begin(), v.end());
+    return out;
+}
+
+uint32_t pad_bits(DataType d, float v) {
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    switch (d) {
+        case DataType::FLOAT32: return u;
+        case DataType::BFLOAT16: return u >> 16;                       // the reference's bfloat16(float) truncates (bfloat16.hpp:27-38)
+        case DataType::UINT32: return (uint32_t)v;
+        case DataType::UINT16: return (uint32_t)(uint16_t)v;
+        default: return u;
+    }
+}
+
+// Runs `body(src_dev, dst_dev)` on fp32 views of a block-float tensor in stored order and packs the result again.
+template <typename F>
+Tensor through_fp32(const Tensor &d, Device *dev, int64_t out_volume, const Shape &out_shape, F body, const char *op) {
+    const int fmt = static_cast<int>(d.dtype());
+    const int64_t in_volume = d.shape().padded_volume();
+    if (in_volume % 1024 || out_volume % 1024) throw_error(std::string(op) + ": block-float tensors hold whole groups of 1024 values");
+    auto in32 = allocate_device_buffer(dev, in_volume * 4);
+    auto out32 = allocate_device_buffer(dev, out_volume * 4);
+    auto dstb = allocate_device_buffer(dev, physical_bytes(out_shape, d.dtype(), d.layout()));
+    check(ttb_unpack_bfp(d.data(), fmt, in32->ptr, TTB_FLOAT32, 1, 32, in_volume / 32, 0, 0, nullptr), op);
+    body(in32->ptr, out32->ptr);
+    check(ttb_pack_bfp(out32->ptr, TTB_FLOAT32, dstb->ptr, fmt, 1, 32, out_volume / 32, 0, 0, nullptr), op);
+    check(ttb_stream_synchronize(nullptr), op);
+    return Tensor(dstb, out_shape, d.dtype(), d.layout());
+}
+
+}  // namespace
+
+Tensor pad(const Tensor &t, const std::vector<int64_t> &output_shape, const std::vector<int64_t> &input_start, float pad_value) {
+    const char *op = "Tensor.pad";
+    if (!t.is_allocated()) throw_error(std::string(op) + ": the tensor has been deallocated");
+    if (t.layout() != Layout::ROW_MAJOR) throw_error(std::string(op) + ": Tensor layout must be ROW_MAJOR for padding");
+    const std::vector<int64_t> in = as4(t.shape().padded(), 1, op), out = as4(output_shape, 1, op), st = as4(input_start, 0, op);
+    for (int i = 0; i < 4; ++i)
+        if (st[i] < 0 || in[i] + st[i] > out[i]) throw_error(std::string(op) + ": the input tensor does not fit the output shape at the given start");
+    const bool on_device = t.storage_type() == StorageType::DEVICE;
+    Tensor d = on_device ? t : to_device_storage(t, current_or_default_device());
+    Device *dev = d.device();
+    dev->make_current();
+    const Shape out_shape(std::vector<int64_t>(out.end() - (std::ptrdiff_t)std::max(output_shape.size(), t.shape().rank()), out.end()));
+    const int64_t out_volume = out[0] * out[1] * out[2] * out[3];
+    Tensor result;
+    if (is_block_float(d.dtype())) {
+        uint32_t bits;
+        std::memcpy(&bits, &pad_value, 4);
+        result = through_fp32(d, dev, out_volume, out_shape, [&](void *src, void *dst) {
+            check(ttb_pad(src, dst, 4, in.data(), out.data(), st.data(), bits, nullptr), op);
+        }, op);
+    } else {
+        auto dstb = allocate_device_buffer(dev, out_volume * element_size(d.dtype()));
+        check(ttb_pad(d.data(), dstb->ptr, element_size(d.dtype()), in.data(), out.data(), st.data(), pad_bits(d.dtype(), pad_value), nullptr), op);
+        result = Tensor(dstb, out_shape, d.dtype(), Layout::ROW_MAJOR);
+    }
+    return on_device ? result : to_host_storage(result);
+}
+
+Tensor unpad(const Tensor &t, const std::vector<int64_t> &start, const std::vector<int64_t> &end) {
+    const char *op = "Tensor.unpad";
+    if (!t.is_allocated()) throw_error(std::string(op) + ": the tensor has been deallocated");
+    if (t.layout() != Layout::ROW_MAJOR) throw_error(std::string(op) + ": Tensor layout must be ROW_MAJOR for unpadding");
+    const std::vector<int64_t> in = as4(t.shape().padded(), 1, op), st = as4(start, 0, op), en = as4(end, 0, op);
+    std::vector<int64_t> out(4);
+    for (int i = 0; i < 4; ++i) {
+        if (st[i] < 0 || en[i] < st[i] || en[i] >= in[i]) throw_error(std::string(op) + ": the slice must lie inside the tensor, start <= end");
+        out[i] = en[i] - st[i] + 1;
+    }
+    const bool on_device = t.storage_type() == StorageType::DEVICE;
+    Tensor d = on_device ? t : to_device_storage(t, current_or_default_device());
+    Device *dev = d.device();
+    dev->make_current();
+    const Shape out_shape(std::vector<int64_t>(out.end() - (std::ptrdiff_t)std::max(start.size(), t.shape().rank()), out.end()));
+    const int64_t out_volume = out[0] * out[1] * out[2] * out[3];
+    Tensor result;
+    if (is_block_float(d.dtype())) {
+        result = through_fp32(d, dev, out_volume, out_shape, [&](void *src, void *dst) {
+            check(ttb_unpad(src, dst, 4, in.data(), st.data(), en.data(), nullptr), op);
+        }, op);
+    } else {
+        auto dstb = allocate_device_buffer(dev, out_volume * element_size(d.dtype()));
+        check(ttb_unpad(d.data(), dstb->ptr, element_size(d.dtype()), in.data(), st.data(), en.data(), nullptr), op);
+        result = Tensor(dstb, out_shape, d.dtype(), Layout::ROW_MAJOR);
+    }
+    return on_device ? result : to_host_storage(result);
+}
+
+Tensor pad_to_tile(const Tensor &t, float pad_value) {
+    const Shape &s = t.shape();
+    if (s.rank() < 2) throw_error("Tensor.pad_to_tile: at least two dimensions are needed");
+    std::vector<int64_t> out = s.padded();
+    out[out.size() - 2] = (out[out.size() - 2] + 31) / 32 * 32;
+    out[out.size() - 1] = (out[out.size() - 1] + 31) / 32 * 32;
+    Tensor p = pad(t, out, std::vector<int64_t>(out.size(), 0), pad_value);
+    // the result remembers the extents it was padded from, like Shape(..., Padding) in the reference
+    Tensor r = p;
+    return r.reshape(Shape(s.padded(), out));
+}
+
+Tensor unpad_from_tile(const Tensor &t, const std::vector<int64_t> &output_shape) {
+    const std::vector<int64_t> &in = t.shape().padded();
+    if (output_shape.size() != in.size() || in.size() < 2) throw_error("Tensor.unpad_from_tile: the output shape must have the tensor's rank");
+    const size_t r = in.size();
+    for (size_t i = 0; i + 2 < r; ++i)
+        if (in[i] != output_shape[i]) throw_error("Tensor.unpad_from_tile: Input shape must match output shape apart from last 2 dims");
+    if (in[r - 2] % 32 || in[r - 1] % 32) throw_error("Tensor.unpad_from_tile: Last 2 dims of input shape must be multiples of 32");
+    if (!(in[r - 2] - 32 < output_shape[r - 2] && output_shape[r - 2] <= in[r - 2] && in[r - 1] - 32 < output_shape[r - 1] && output_shape[r - 1] <= in[r - 1]))
+        throw_error("Tensor.unpad_from_tile: Last 2 dims of output must be within range to have been padded to input");
+    std::vector<int64_t> end(output_shape);
+    for (auto &v : end) v -= 1;
+    return unpad(t, std::vector<int64_t>(r, 0), end);
+}
+
+Tensor multiply(const Tensor &a, const Tensor &b) {
+    const char *op = "ttnn.mul";
+    if (a.storage_type() != StorageType::DEVICE || b.storage_type() != StorageType::DEVICE) throw_error(std::string(op) + ": both tensors must be on device");
+    if (!a.is_allocated() || !b.is_allocated()) throw_error(std::string(op) + ": tensors must be allocated");
+    if (a.device() != b.device()) throw_error(std::string(op) + ": operands must be on the same device");
+    if (a.dtype() != DataType::BFLOAT16 || b.dtype() != DataType::BFLOAT16) throw_error(std::string(op) + ": both tensors must be bfloat16");
+    if (!(a.shape() == b.shape()) || a.layout() != b.layout()) throw_error(std::string(op) + ": both tensors must have the same shape and layout");
+    Device *dev = a.device();
+    dev->make_current();
+    auto outb = allocate_device_buffer(dev, a.buffer_bytes());
+    check(ttb_mul_bf16(a.data(), b.data(), outb->ptr, a.shape().padded_volume(), nullptr), op);
+    return Tensor(outb, a.shape(), a.dtype(), a.layout());
 }
 
 // ---- matmul / linear ----------------------------------------------------------------------------------

@@ -28,6 +28,18 @@ Tensor from_device(const Tensor &t);                // Tensor::cpu(), tensor_imp
 // Device tensor over memory owned by the caller (used for collective outputs).
 Tensor wrap_device_memory(uint64_t ptr, const Shape &shape, DataType dtype, Layout layout, Device *device);
 
+// Tensor::pad / unpad / pad_to_tile / unpad_from_tile (tt_eager/tensor/tensor.cpp:209-254, tensor_impl.hpp:508-677,
+// tensor_impl.cpp:200-283): row-major tensors of up to four dimensions; block-float tensors go through fp32 as in the
+// reference (unpack in stored order, pad, pack in stored order). `end` is inclusive.
+Tensor pad(const Tensor &t, const std::vector<int64_t> &output_shape, const std::vector<int64_t> &input_start, float pad_value);
+Tensor unpad(const Tensor &t, const std::vector<int64_t> &start, const std::vector<int64_t> &end);
+Tensor pad_to_tile(const Tensor &t, float pad_value);
+Tensor unpad_from_tile(const Tensor &t, const std::vector<int64_t> &output_shape);
+
+// Elementwise product of two bfloat16 device tensors of one shape and layout (ttl.tensor.mul as the gated MLP uses it,
+// models/demos/llama2_70b/tt/llama_mlp_optimized.py:191-197).
+Tensor multiply(const Tensor &a, const Tensor &b);
+
 // ttnn::operations::matmul::{matmul, linear} (ttnn/cpp/ttnn/operations/matmul.hpp:44-213) on top of
 // tt::operations::primary::matmul (tt_eager/tt_dnn/op_library/bmm/bmm_op.cpp:828-1149).
 Tensor matmul(const Tensor &a, const Tensor &b, std::optional<DataType> dtype, const std::optional<MatmulProgramConfig> &program_config);

@@ -20,7 +20,7 @@ from .multi_device import (DeviceMesh, MultiDeviceTensor, open_device_mesh, clos
                            ShardTensorToMesh, ReplicateTensorToMesh, ConcatMeshToTensor, ListMeshToTensor)
 from .operations.core import (from_torch, to_torch, to_layout, to_device, from_device, deallocate, reshape, dump_tensor,
                               load_tensor, as_tensor, is_tensor_storage_on_device)
-from .operations.matmul import (matmul, linear, MatmulProgramConfig, MatmulDefaultProgramConfig, MatmulMultiCoreReuseProgramConfig,
+from .operations.matmul import (matmul, linear, mul, MatmulProgramConfig, MatmulDefaultProgramConfig, MatmulMultiCoreReuseProgramConfig,
                                 MatmulMultiCoreReuseMultiCastProgramConfig, MatmulMultiCoreReuseMultiCast1DProgramConfig)
 from .operations.ccl import all_gather, linear_all_gather, linear_multi, wait_for_gather
 

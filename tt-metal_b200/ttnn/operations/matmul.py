@@ -78,3 +78,11 @@ def linear(input_tensor_a, input_tensor_b, *, bias=None, memory_config: T.Memory
     mesh, (a, b, bias_t) = _split(input_tensor_a, input_tensor_b, bias)
     out = _ttnn.linear(a, b, bias=bias_t, dtype=dtype, activation=activation, program_config=program_config)
     return MultiDeviceTensor(out, mesh) if mesh is not None else out
+
+
+def mul(input_tensor_a, input_tensor_b, *, memory_config: T.MemoryConfig = T.DRAM_MEMORY_CONFIG, dtype: Optional[T.DataType] = None):
+    """Elementwise product of two bfloat16 device tensors of one shape: the gate multiply of the gated MLP when it is not
+    fused into the matmul (ttnn.linear_gated does that in one launch)."""
+    mesh, (a, b, _) = _split(input_tensor_a, input_tensor_b)
+    out = _ttnn.mul(a, b)
+    return MultiDeviceTensor(out, mesh) if mesh is not None else out
