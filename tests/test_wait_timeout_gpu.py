@@ -48,7 +48,7 @@ def test_negative_limit_is_refused(ttb):
 
 
 @pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
-@pytest.mark.parametrize("M,K,N", [(32, 2048, 512), (64, 1024, 256)])
+@pytest.mark.parametrize("M,K,N", [(32, 2048, 512), (64, 4096, 256), (32, 256, 18176)])
 def test_matmul_waiting_for_peers_gives_up_and_the_next_one_is_right(ttb, orc, short_waits, w_dtype, M, K, N):
     """A decode matmul whose activations "come from other GPUs" that never deliver: every role of every block leaves through
     the kernel's teardown, the status says so, and after clearing the workspace head (the header's rule after a timeout)
@@ -58,8 +58,8 @@ def test_matmul_waiting_for_peers_gives_up_and_the_next_one_is_right(ttb, orc, s
     a = ttb.tilize(x.cuda(), 1, M, K)
     counters, wt = _dead_gather_point()
     nbytes = ttb.matmul_peer_workspace_bytes(w_dtype, 1, M, K, N)
-    assert nbytes > 0                                      # K is split over blocks: the scratch is in play
-    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    assert (nbytes > 0) == (N < 18176)                     # K split over blocks (scratch in play), and one block per tile
+    ws = torch.zeros(max(nbytes, 65536 + (16 << 20)), dtype=torch.uint8, device="cuda")
     out = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
     ttb.check(ttb.cdll.ttb_matmul_peer(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), w_dtype, None, out.data_ptr(), cabi.BFLOAT16,
                                        1, M, K, N, 0, cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None, ctypes.byref(wt), None))

@@ -65,12 +65,13 @@ struct Layout {
     static constexpr int b = pk + kRing * kGroup * kStageBytes;    // (a multiple of 256: the swizzled operand needs it)
     static constexpr int stage = b + kRing * kGroup * kBStageBytes;   // [NB x 128] bf16 tiled slab for the gather epilogue
     static constexpr int bars = stage + NB * BN * 2;
-    // full_pk[kRing], full_a[kRing], empty[kRing], acc_full[2], acc_empty[2]
+    // full_pk[kRing], full_a[kRing], empty[kRing / 2] (per pair of groups), acc_full[2], acc_empty[2]
     static constexpr int nbars = 3 * kRing + 4;
     static constexpr int misc = bars + 8 * nbars;                  // tmem base, abort flag, last-block flag, two accumulator-ready flags
     static constexpr int total = misc + 32;
-    // One accumulator per K step of a stage, each fed by its own issuing thread (a single thread needs ~100 cycles per
-    // MMA it issues; two MMAs per stage would make it the slowest role); the epilogue adds the two.
+    // Issuing costs a thread ~46 cycles per MMA and ~300 per commit, whatever the MMA's size. Two issuing threads take
+    // alternate pairs of groups (six stages, twelve MMAs, one commit that frees the pair's ring slots), each into its own
+    // accumulator, so that no ordering between the two is needed; the epilogue adds the accumulators.
     static constexpr int kAccs = 2;
     static constexpr int kAccCols = 2 * kAccs * NB;                // two sets of kAccs accumulators
     static constexpr int kACol0 = kAccCols;                        // the A ring follows them
@@ -81,7 +82,7 @@ struct Layout {
     static_assert(b % 256 == 0 && kBStageBytes % 1024 == 0, "alignment of the swizzled activation operand");
     // The teams wait on the ring barriers with different phase parities, which is only right while a waiter is at most
     // one phase behind, i.e. while the ring has at least as many groups as there are teams.
-    static_assert(kTeams <= kRing, "ring shorter than the number of teams");
+    static_assert(kTeams <= kRing && kRing % 2 == 0, "ring shorter than the number of teams");
 };
 
 struct Seg {
@@ -232,7 +233,7 @@ constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks e
 // Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
 // that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
 template <int NB>
-__device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, bool ok) {
+__device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, const int g0, bool ok) {
     using L = Layout<NB>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tid = threadIdx.x - 32 * kEpiWarp0;
@@ -260,16 +261,22 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     const bool partials = p.ordered || contributors <= kPartialsUpTo;
     float *const acc_tile = p.accum + (int64_t)s.tile * BN * NB;
     const uint32_t t_acc = c.tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * L::kAccs * NB);
-    constexpr int naccs = L::kAccs;   // every segment holds at least one stage, i.e. one MMA per issuer
+    // Which issuers had a group in this segment: issuer h owns the groups G (numbered over the block's whole work, g0 =
+    // this segment's first) with (G / 2) % 2 == h. Three consecutive groups always touch both.
+    const int ng = (s.nit + kGroup - 1) / kGroup;
+    bool used[L::kAccs];
+#pragma unroll
+    for (int h = 0; h < L::kAccs; ++h) {
+        used[h] = ng >= 3;
+        for (int G = g0; G < g0 + min(ng, 2); ++G) used[h] = used[h] || ((G >> 1) & 1) == h;
+    }
     auto read_accumulator = [&](int col0, float (&v)[16]) {   // sum of the segment's accumulators, 16 rows of this lane's column
-        uint32_t r[16];
-        tmem_ld16(t_acc + (uint32_t)col0, r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
 #pragma unroll
-        for (int a = 1; a < L::kAccs; ++a) {
-            if (a < naccs) {
+        for (int a = 0; a < L::kAccs; ++a) {
+            if (used[a]) {
+                uint32_t r[16];
                 tmem_ld16(t_acc + (uint32_t)(a * NB + col0), r);
                 tmem_ld_wait();
 #pragma unroll
@@ -385,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     const uint32_t bar0 = sbase + L::bars;
     auto full_pk = [&](int s) { return bar0 + 8u * s; };                 // packed tiles and activations of the group have landed
     auto full_a = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's weights are expanded in tensor memory
-    auto empty = [&](int s) { return bar0 + 8u * (2 * kRing + s); };      // the group's MMAs are complete: its slot is free
+    auto empty = [&](int s) { return bar0 + 8u * (2 * kRing + (s >> 1)); };   // the MMAs of the pair of groups {s & ~1, s | 1} are complete: both slots are free
     const uint32_t acc_full0 = bar0 + 8u * (3 * kRing), acc_empty0 = acc_full0 + 16u;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
@@ -399,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         for (int s = 0; s < kRing; ++s) {
             mbar_init(full_pk(s), 2);     // the two producer threads, each with its byte count
             mbar_init(full_a(s), 4);      // the four expand warps of the group's team
-            mbar_init(empty(s), 2);       // the two MMA issuers' commits
+            if ((s & 1) == 0) mbar_init(empty(s), 1);   // the commit of the issuer that owns the pair
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(acc_full0 + 8u * s, 2);
@@ -436,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 const TileRef tr = tile_ref(p, s.tile);
                 const void *map = &maps.m[tr.prob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if (!mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 11, lim)) { ok = false; break; }
+                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 11, lim)) { ok = false; break; }
                     TL(0, tlg); ++tlg;
                     // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
                     // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
@@ -463,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             while (ok && it.next(p, block, s)) {
                 const int rchunk = s.tile / p.tstart[p.nprob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if (!mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 17, lim)) { ok = false; break; }
+                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 17, lim)) { ok = false; break; }
                     TL(4, tlg); ++tlg;
                     mbar_arrive_expect_tx(full_pk(gs), kGroup * L::kBStageBytes);
                     const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
@@ -477,13 +484,13 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ---------------- MMA issuers: A from tensor memory, B (activations) from shared memory ----------------
-        // Issuer k16 multiplies the k16-th half of every stage's K block into its own accumulator.
+        // Issuer h takes the pairs of groups whose pair number is h modulo 2 and accumulates them in accumulator h.
         if (lane == 0) {
-            const int k16 = warp - kMmaWarp;
+            const int h = warp - kMmaWarp;
             constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/false, /*b_mn_major=*/false);
-            const uint64_t b_desc0 = smem_desc_sw32(sbase + L::b + k16 * (L::kBStageBytes / 2), kB_SBO);
+            const uint64_t b_desc0 = smem_desc_sw32(sbase + L::b, kB_SBO);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-            const uint32_t a_col0 = tmem_base + (uint32_t)(L::kACol0 + k16 * 8);
+            const uint32_t a_col0 = tmem_base + (uint32_t)L::kACol0;
             auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
             int gs = 0, seg_idx = 0, tlg = 0;
             (void)tlg;
@@ -495,25 +502,34 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 const int buf = seg_idx & 1;
                 if (!mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, p.status, 16, lim)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + k16) * NB);
+                const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + h) * NB);
+                bool fresh = true;   // this issuer's accumulator holds nothing of this segment yet
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    const int r = min(kGroup, s.nit - i0);
-                    if (k16 == 0) { TL(1, tlg); }
-                    // expanded weights; the activations of the group landed before its expansion could start, and waiting on
-                    // their barrier here (complete by now) makes them visible to this thread's MMAs
-                    if (!mbar_wait(full_a(gs), ph, abort_flag, p.status, 12, lim) || !mbar_wait(full_pk(gs), ph, abort_flag, p.status, 18, lim)) { ok = false; break; }
-                    if (k16 == 0) { TL(2, tlg); }
-                    tc_fence_after_sync();
-                    const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
-                    const uint32_t b_lo = b_lo0 + (uint32_t)gs * ((kGroup * L::kBStageBytes) >> 4);
-                    mma_bf16_ts(d_tmem, a_col, mk(b_lo, b_hi), idesc, i0 > 0);
-                    if (r > 1) mma_bf16_ts(d_tmem, a_col + kAColsPerStage, mk(b_lo + (L::kBStageBytes >> 4), b_hi), idesc, true);
-                    if (r > 2) mma_bf16_ts(d_tmem, a_col + 2 * kAColsPerStage, mk(b_lo + 2 * (L::kBStageBytes >> 4), b_hi), idesc, true);
-                    mma_commit(empty(gs));
-                    if (k16 == 0) { TL(3, tlg); }
+                    if (((gs >> 1) & 1) == h) {
+                        const int r = min(kGroup, s.nit - i0);
+                        if (h == 0) { TL(1, tlg); }
+                        // expanded weights; the activations of the group landed before its expansion could start, and waiting
+                        // on their barrier here (complete by now) makes them visible to this thread's MMAs
+                        if (!mbar_wait(full_a(gs), ph, abort_flag, p.status, 12, lim) || !mbar_wait(full_pk(gs), ph, abort_flag, p.status, 18, lim)) { ok = false; break; }
+                        if (h == 0) { TL(2, tlg); }
+                        tc_fence_after_sync();
+                        const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
+                        const uint32_t b_lo = b_lo0 + (uint32_t)gs * ((kGroup * L::kBStageBytes) >> 4);
+#pragma unroll
+                        for (int j = 0; j < kGroup; ++j) {
+                            if (j < r) {
+                                mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage), mk(b_lo + (uint32_t)((j * L::kBStageBytes) >> 4), b_hi), idesc, !(fresh && j == 0));
+                                mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage + 8), mk(b_lo + (uint32_t)((j * L::kBStageBytes + L::kBStageBytes / 2) >> 4), b_hi), idesc, true);
+                            }
+                        }
+                        fresh = false;
+                        if (gs & 1) mma_commit(empty(gs));   // second group of the pair: one commit frees both slots
+                        if (h == 0) { TL(3, tlg); }
+                    }
                     ++tlg;
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
+                // (an issuer that had no group in this segment still commits: its arrival is part of the barrier's count)
                 if (ok) mma_commit(acc_full0 + 8u * buf);
             }
         }
@@ -522,11 +538,14 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         grid_dep_wait();   // the epilogues touch scratch and outputs
         if (p.ranks > 1 && blockIdx.x == 0 && warp == kEpiWarp0 && lane == 0) *p.expected = *p.expected + p.launch_arrivals;
         const EpiCtx ectx = {smem, tmem_base, acc_full0, acc_empty0, abort_flag, last_flag, lim};
-        int seg_idx = 0;
+        int seg_idx = 0, g0 = 0;
         SegIter it;
         it.start(p, block);
         Seg s;
-        for (; it.next(p, block, s); ++seg_idx) ok = epilogue<NB>(p, ectx, s, seg_idx, ok);
+        for (; it.next(p, block, s); ++seg_idx) {
+            ok = epilogue<NB>(p, ectx, s, seg_idx, g0, ok);
+            g0 += (s.nit + kGroup - 1) / kGroup;
+        }
     } else {
         // ---------------- expand warps: packed codes -> bf16 in tensor memory ----------------
         const int team = warp >> 2, quad = warp & 3;

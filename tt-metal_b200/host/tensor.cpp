@@ -204,6 +204,16 @@ std::shared_ptr<DeviceBuffer> borrow_device_buffer(Device *device, void *ptr, in
     return b;
 }
 
+std::shared_ptr<DeviceBuffer> view_device_buffer(const std::shared_ptr<DeviceBuffer> &parent, void *ptr, int64_t bytes) {
+    auto b = std::make_shared<DeviceBuffer>();
+    b->device = parent->device;
+    b->ptr = ptr;
+    b->bytes = bytes;
+    b->owned = false;
+    b->parent = parent;
+    return b;
+}
+
 int64_t physical_bytes(const Shape &shape, DataType dtype, Layout layout) {
     if (is_block_float(dtype)) {
         if (shape.padded_volume() % 1024) throw_error("ttnn: block-float tensors must hold whole 32x32 tiles");

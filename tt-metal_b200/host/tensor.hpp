@@ -120,6 +120,7 @@ struct DeviceBuffer {
     int64_t bytes = 0;
     Device *device = nullptr;
     bool owned = true;
+    std::shared_ptr<DeviceBuffer> parent;   // set for a view into another buffer, which it keeps alive
     ~DeviceBuffer();
 };
 
@@ -161,5 +162,7 @@ std::shared_ptr<DeviceBuffer> allocate_device_buffer(Device *device, int64_t byt
 void release_cached_blocks();
 // Wraps device memory owned by someone else (e.g. a collective's output buffer); never freed here.
 std::shared_ptr<DeviceBuffer> borrow_device_buffer(Device *device, void *ptr, int64_t bytes);
+// A part of `parent` (several results of one launch share one allocation); keeps the parent alive.
+std::shared_ptr<DeviceBuffer> view_device_buffer(const std::shared_ptr<DeviceBuffer> &parent, void *ptr, int64_t bytes);
 
 }  // namespace ttnn_b200
