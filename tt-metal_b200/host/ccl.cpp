@@ -9,13 +9,13 @@ namespace ttnn_b200 {
 // ---- communicator ------------------------------------------------------------------------------------------
 std::string Comm::make_unique_id() {
     std::string id(TTB_COMM_ID_BYTES, '\0');
-    check(ttb_comm_unique_id(id.data()), "ttnn: communicator id");
+    ttnn_b200::check(ttb_comm_unique_id(id.data()), "ttnn: communicator id");
     return id;
 }
 
 Comm::Comm(int ranks, int rank, const std::string &unique_id, int64_t timeout_ms) : ranks_(ranks), rank_(rank) {
     if ((int)unique_id.size() != TTB_COMM_ID_BYTES) throw_error("ttnn: a communicator id has " + std::to_string(TTB_COMM_ID_BYTES) + " bytes");
-    check(ttb_comm_init(&handle_, ranks, rank, unique_id.data(), timeout_ms), "ttnn.open_device_mesh");
+    ttnn_b200::check(ttb_comm_init(&handle_, ranks, rank, unique_id.data(), timeout_ms), "ttnn.open_device_mesh");
 }
 
 Comm::~Comm() {
@@ -135,7 +135,8 @@ int activation_code_of(const std::optional<std::string> &act) {
 }  // namespace
 
 std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
-                                 const std::optional<std::string> &activation, GatherRing *ring, int wait_slot, int *gather_slot) {
+                                 const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot,
+                                 int *gather_slot) {
     const char *op = "ttnn.linear_multi";
     const int n = (int)weights.size();
     if (n < 1 || n > TTB_MAX_GROUP) throw_error(std::string(op) + ": between one and four weights per launch");
@@ -174,11 +175,12 @@ std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &wei
     }
     Device *dev = x.device();
     dev->make_current();
-    const int G = ring ? ring->ranks() : 1;
+    if ((gather_first || wait_slot >= 0) && !ring) throw_error(std::string(op) + ": gathering or waiting needs the mesh's ring of gather points");
+    const int G = gather_first ? ring->ranks() : 1;
     int slot = -1;
-    if (ring) slot = ring->take((int64_t)G * rows * N[0] * 2);
+    if (gather_first) slot = ring->take((int64_t)G * rows * N[0] * 2);
     // one allocation for all local outputs of the launch
-    const int first_local = ring ? 1 : 0;
+    const int first_local = gather_first ? 1 : 0;
     int64_t total = 0;
     for (int j = first_local; j < n; ++j) total += rows * N[j];
     std::shared_ptr<DeviceBuffer> block = total ? allocate_device_buffer(dev, total * 2) : nullptr;
@@ -191,7 +193,7 @@ std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &wei
     void *ws = need > 0 ? dev->workspace(need) : nullptr;
     check(ttb_matmul_multi(x.data(), TTB_BFLOAT16, n, w_ptr, static_cast<int>(fmt), any_bias ? b_ptr : nullptr, o_ptr, TTB_BFLOAT16, 1, rows, K, N,
                            activation_code_of(activation), TTB_MM_WORKSPACE_ZEROED | TTB_MM_WEIGHTS_RESIDENT, ws, need,
-                           ring ? ring->gather(slot) : nullptr, (ring && wait_slot >= 0) ? ring->wait(wait_slot) : nullptr, nullptr),
+                           gather_first ? ring->gather(slot) : nullptr, wait_slot >= 0 ? ring->wait(wait_slot) : nullptr, nullptr),
           op);
     if (gather_slot) *gather_slot = slot;
     std::vector<int64_t> lead(x.shape().dims().begin(), x.shape().dims().end() - 1), lead_p(xp.begin(), xp.end() - 1);

@@ -67,11 +67,12 @@ class GatherRing {
     std::vector<ttb_peer_wait_t> waits_;
 };
 
-// [linear(x, w, bias=b, activation=act) for (w, b) in zip(weights, biases)] as one launch (ttb_matmul_multi). With `ring`
-// the first result is gathered over the ranks by the kernel's epilogue into the ring's next point, whose index is returned
-// in *gather_slot; `wait_slot` >= 0 names the point the activation came from (the kernel waits for it itself).
-// `gated`: the launch holds exactly two weights and returns the single tensor silu(x w0 + b0) * (x w1 + b1).
+// [linear(x, w, bias=b, activation=act) for (w, b) in zip(weights, biases)] as one launch (ttb_matmul_multi). With
+// `gather_first` the first result is gathered over the ranks by the kernel's epilogue into the ring's next point, whose index
+// is returned in *gather_slot; `wait_slot` >= 0 names the point of `ring` the activation came from (the kernel waits for it
+// itself).
 std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
-                                 const std::optional<std::string> &activation, GatherRing *ring, int wait_slot, int *gather_slot);
+                                 const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot,
+                                 int *gather_slot);
 
 }  // namespace ttnn_b200

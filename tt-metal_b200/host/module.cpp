@@ -5,6 +5,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "ccl.hpp"
 #include "ops.hpp"
 
 namespace py = pybind11;
@@ -163,6 +164,43 @@ PYBIND11_MODULE(_ttnn, m) {
     m.def("to_device", &to_device, py::keep_alive<0, 2>());
     m.def("from_device", &from_device);
 
+    // ---- tensor parallel: communicator, all_gather, gather ring, fused linears -------------------------------------
+    py::class_<Comm>(m, "Comm")
+        .def(py::init([](int ranks, int rank, py::bytes unique_id, int64_t timeout_ms) {
+                 std::string id = unique_id;
+                 py::gil_scoped_release release;
+                 return std::make_unique<Comm>(ranks, rank, id, timeout_ms);
+             }),
+             py::arg("ranks"), py::arg("rank"), py::arg("unique_id"), py::arg("timeout_ms") = 120000)
+        .def_static("make_unique_id", []() { return py::bytes(Comm::make_unique_id()); })
+        .def_property_readonly("ranks", &Comm::ranks)
+        .def_property_readonly("rank", &Comm::rank)
+        .def("check", &Comm::check, py::arg("timeout_ms") = 10000)
+        .def("abort", &Comm::abort);
+    m.def("plan_all_gather",
+          [](const Shape &shape, DataType dtype, Layout layout, int dim, int ranks) {
+              const GatherPlan g = plan_all_gather(shape, dtype, layout, dim, ranks);
+              return py::make_tuple(g.interleave, g.rows, g.row_bytes, g.out_shape);
+          },
+          py::arg("shape"), py::arg("dtype"), py::arg("layout"), py::arg("dim"), py::arg("ranks"));
+    m.def("all_gather", &all_gather, py::arg("tensor"), py::arg("dim"), py::arg("comm"));
+    py::class_<GatherRing>(m, "GatherRing")
+        .def(py::init<int, std::vector<uint64_t>, int, int64_t, int64_t>(), py::arg("rank"), py::arg("arena_bases"), py::arg("slots"),
+             py::arg("counter_bytes"), py::arg("slot_bytes"))
+        .def_property_readonly("slots", &GatherRing::slots)
+        .def_property_readonly("slot_bytes", &GatherRing::slot_bytes)
+        .def("take", &GatherRing::take)
+        .def("stream_wait", &GatherRing::stream_wait)
+        .def("out_ptr", [](const GatherRing &r, int slot) { return reinterpret_cast<uint64_t>(r.out_ptr(slot)); });
+    m.def("linear_multi",
+          [](const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
+             const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot) {
+              int slot = -1;
+              std::vector<Tensor> out = linear_multi(x, weights, biases, activation, ring, gather_first, wait_slot, &slot);
+              return py::make_tuple(out, slot);
+          },
+          py::arg("input_tensor"), py::arg("weights"), py::arg("biases"), py::arg("activation").none(true), py::arg("ring").none(true),
+          py::arg("gather_first") = false, py::arg("wait_slot") = -1);
     m.def("mul", &multiply, py::arg("input_tensor_a"), py::arg("input_tensor_b"));
     m.def("matmul", &matmul, py::arg("input_tensor_a"), py::arg("input_tensor_b"), py::kw_only(), py::arg("dtype") = std::nullopt,
           py::arg("program_config") = std::nullopt);

@@ -41,6 +41,40 @@ class DeviceMesh:
         else:
             self.local_index = 0
         self.device = _ttnn.open_device(self.device_ids[self.local_index]) if torch.cuda.is_available() else None
+        self._comm = None          # NCCL communicator behind the C ABI, made at first use
+        self._ring = None          # ring of gather points of the fused linears
+        self.pending = None        # (ring, point) of the last gathering launch no later launch has waited for yet
+
+    def communicator(self, timeout_ms: int = 120000):
+        """The mesh's communicator (ttb_comm_* behind _ttnn.Comm), created collectively at first use: rank 0 makes the id,
+        the process group carries it to the others (bootstrap only), every rank joins within `timeout_ms`."""
+        if self._comm is None:
+            import torch.distributed as dist
+            n = len(self.device_ids)
+            box = [_ttnn.Comm.make_unique_id() if self.local_index == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.process_group, 0) if self.process_group is not None else 0,
+                                       group=self.process_group)
+            self._comm = _ttnn.Comm(n, self.local_index, box[0], timeout_ms)
+        return self._comm
+
+    def current_ring(self):
+        return self._ring
+
+    def gather_ring(self, nbytes: int, slots: int = 8):
+        """The ring of gather points, large enough for a gathered tensor of `nbytes`. Growing it is collective: the point
+        still pending in the old ring is settled on the stream, the ranks meet, and the old ring goes away once no tensor
+        refers to it any more (tensors keep the ring they were gathered in)."""
+        if self._ring is None or self._ring.slot_bytes < nbytes:
+            from .peer import GatherRing
+            import torch.distributed as dist
+            if self._ring is not None:
+                if self.pending is not None:
+                    self.pending[0].stream_wait(self.pending[1])
+                    self.pending = None
+                self.device.synchronize()
+                dist.barrier(group=self.process_group)
+            self._ring = GatherRing(self.local_index, len(self.device_ids), max(nbytes, 1 << 20), slots=slots, group=self.process_group)
+        return self._ring
 
     def get_num_devices(self) -> int:
         return len(self.device_ids)

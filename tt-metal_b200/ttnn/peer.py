@@ -95,6 +95,10 @@ class GatherRing:
         self._next = 0
         self._gathers = [self._make_gather(s) for s in range(slots)]
         self._waits = [self._make_wait(s) for s in range(slots)]
+        # the same ring for the C++ host layer (ttnn.linear_multi / linear_all_gather): it takes the points in its own order,
+        # so one ring object serves either the ctypes callers (take / gather / wait below) or the host layer, not both
+        from . import _ttnn
+        self.native = _ttnn.GatherRing(rank, [int(b) for b in self.bases], slots, self.counter_bytes, self.slot_bytes)
 
     def _make_gather(self, s):
         g = PeerGather()
@@ -133,9 +137,19 @@ class GatherRing:
         _check(_rt.cdll.ttb_peer_wait(ctypes.byref(self._waits[s]), stream))
 
     def close(self):
+        """Unmaps the peers' arenas and frees this rank's. Only after every rank has stopped launching into this ring (the
+        mesh replaces a ring behind a barrier), since peers store into this rank's arena."""
         for r, b in enumerate(self.bases):
             if r != self.rank and b:
                 _rt.cdll.ttb_ipc_close(b)
         if self._own:
             _rt.cdll.ttb_free(self._own)
-        self.bases, self._own = [], None
+        self.bases, self._own, self.native = [], None, None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_own", None):
+                _rt.cdll.ttb_device_synchronize()
+                self.close()
+        except Exception:
+            pass
