@@ -164,6 +164,14 @@ int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_
                    void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,
                    int32_t activation, int32_t flags, void *workspace_dev, int64_t workspace_bytes, void *stream);
 
+/* Batched matmul with a batched second operand: out[b, M, N] = a[b, M, K] x w[b, K, N] for b < batch, every operand tiled,
+ * `a` bfloat16, `w` bfloat8_b / bfloat4_b / bfloat16 (one packed [K, N] matrix after the other), fp32 accumulation, bfloat16 or
+ * float32 output. Stands in for tt::tt_metal::bmm and the batched form of tt::operations::primary::matmul
+ * (tt_eager/tt_dnn/op_library/bmm/bmm_op.hpp:388-456, bmm_op.cpp:518-626; attention's Q K^T and P V products,
+ * tests/tt_eager/python_api_testing/unit_testing/misc/test_matmul.py:204-320). Runs on the CUDA cores. */
+int32_t ttb_bmm(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, void *out_dev, int32_t out_dtype, int64_t batch,
+                int64_t M, int64_t K, int64_t N, void *stream);
+
 /* Decode matmul for callers that cannot allocate device memory.
  * This entry point has no counterpart in the reference. It computes exactly what ttb_matmul computes for the decode
  * shapes (bfloat16 activations of at most 256 rows in total, bfloat8_b / bfloat4_b weights, N a multiple of 128), but

@@ -193,3 +193,62 @@ def test_to_layout_with_dtype_packs_on_the_device(device, orc, dtype, ofmt, shap
         ttnn.to_layout(ttnn.from_torch(x, layout=ttnn.ROW_MAJOR_LAYOUT), ttnn.TILE_LAYOUT, dtype=dtype)      # not on device
     with pytest.raises(RuntimeError, match="Unsupported datatype conversion"):
         ttnn.to_layout(rm, ttnn.ROW_MAJOR_LAYOUT, dtype=dtype)
+
+
+def _unpacked(t, ofmt, orc):
+    """fp32 values of a block-float ttnn tensor, by the ORACLE's unpacker on the tensor's own bytes."""
+    shape = list(t.shape.with_tile_padding())
+    outer = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+    return torch.from_numpy(orc.to_torch(np.frombuffer(t.buffer(), np.uint8), ofmt, outer, shape[-2], shape[-1]).reshape(shape).copy())
+
+
+def test_batched_matmul_with_block_float_operands_and_output(device, orc):
+    """The attention-style bmm of tests/tt_eager/python_api_testing/unit_testing/misc/test_matmul.py:204-320: both operands
+    bfloat8_b with the same batch dimensions, bfloat8_b output (dtype defaults to the first operand's). The output bytes are
+    the host packer's applied to the fp32 product: checked against the oracle packing of an fp32 torch matmul of the
+    oracle-unpacked operands."""
+    B, H, M, K, N = 2, 4, 96, 64, 128
+    a = vectors.randn(31, (B, H, M, K), 1.0)
+    b = vectors.randn(32, (B, H, K, N), 1.0)
+    at = ttnn.from_torch(a, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    bt = ttnn.from_torch(b, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    out = ttnn.matmul(at, bt)
+    assert out.dtype == ttnn.bfloat8_b and list(out.shape) == [B, H, M, N]
+    ref = _unpacked(at, oracle.BFP8_B, orc) @ _unpacked(bt, oracle.BFP8_B, orc)
+    got = ttnn.to_torch(out)
+    pcc = oracle.comp_pcc(ref.numpy(), got.numpy())
+    assert pcc >= 0.9999, pcc
+    # bit-level: pack-after-matmul. The fp32 product itself differs from torch's in summation order (a few ulps), which
+    # moves a packed code by at most one step: compare the unpacked values within one code step of each row's exponent.
+    want = orc.to_torch(orc.from_torch(ref.numpy(), oracle.BFP8_B, B * H, M, N), oracle.BFP8_B, B * H, M, N).reshape(B, H, M, N)
+    step = np.abs(want).reshape(B, H, M, N // 16, 16).max(-1, keepdims=True) / 64.0
+    assert np.all(np.abs(got.numpy() - want).reshape(B, H, M, N // 16, 16) <= step + 1e-12)
+    # bfloat16 output on request, float32 too
+    out16 = ttnn.matmul(at, bt, dtype=ttnn.bfloat16)
+    assert out16.dtype == ttnn.bfloat16
+    assert oracle.comp_pcc(ref.numpy(), ttnn.to_torch(out16).float().numpy()) >= 0.9999
+    with pytest.raises(RuntimeError):
+        ttnn.matmul(at, ttnn.from_torch(b[:1], dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device))   # batch mismatch
+
+
+@pytest.mark.parametrize("out_dtype,ofmt", [(ttnn.bfloat8_b, 0), (ttnn.bfloat4_b, 1)])
+def test_linear_with_block_float_activation_and_output(device, orc, out_dtype, ofmt):
+    """bfloat8_b activations (the reference admits them, tt_eager/tt_dnn/op_library/bmm/bmm_op.cpp:839) are expanded exactly;
+    a block-float output equals the device packer applied to the float32 result of the same matmul, bit for bit."""
+    M, K, N = 32, 1024, 512
+    x = vectors.randn(41, (1, 1, M, K), 1.0)
+    w = vectors.randn(42, (K, N), 0.05)
+    xt = ttnn.from_torch(x, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    wt = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    y32 = ttnn.linear(xt, wt, dtype=ttnn.float32, activation="relu")
+    yq = ttnn.linear(xt, wt, dtype=out_dtype, activation="relu")
+    assert yq.dtype == out_dtype and list(yq.shape) == [1, 1, M, N]
+    want = orc.from_torch(ttnn.to_torch(y32).numpy(), ofmt, 1, M, N)          # host packer on the fp32 result
+    assert np.array_equal(np.frombuffer(yq.buffer(), np.uint8), want)
+    ref = torch.relu(_unpacked(xt, oracle.BFP8_B, orc).reshape(M, K) @ _unpacked(wt, oracle.BFP8_B, orc).reshape(K, N))
+    assert oracle.comp_pcc(ref.numpy(), ttnn.to_torch(y32).reshape(M, N).numpy()) >= 0.9999
+    # the packed result feeds the next linear directly
+    w2 = ttnn.from_torch(vectors.randn(43, (N, 128), 0.05), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    z = ttnn.linear(yq, w2, dtype=ttnn.bfloat16)
+    zref = _unpacked(yq, ofmt, orc).reshape(M, N) @ _unpacked(w2, oracle.BFP8_B, orc).reshape(N, 128)
+    assert oracle.comp_pcc(zref.numpy(), ttnn.to_torch(z).float().reshape(M, 128).numpy()) >= 0.9999

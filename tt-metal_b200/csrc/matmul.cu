@@ -6,6 +6,8 @@
 namespace ttb {
 int32_t launch_matmul_generic(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                               int64_t rows, int64_t K, int64_t N, int act, int flags, cudaStream_t stream);
+int32_t launch_bmm_generic(const void *a, const void *w, int w_dtype, void *out, int out_dtype, int64_t batch, int64_t M, int64_t K,
+                           int64_t N, cudaStream_t stream);
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N);
 int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N);
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
@@ -81,6 +83,12 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
         return launch_matmul_prefill(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes, status, s);
     }
     return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
+}
+
+int32_t ttb_bmm(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, void *out, int32_t out_dtype, int64_t batch, int64_t M,
+                int64_t K, int64_t N, void *stream) {
+    if (int32_t rc = validate(a, a_dtype, w, w_dtype, out, out_dtype, batch, M, K, N, TTB_ACT_NONE)) return rc;
+    return launch_bmm_generic(a, w, w_dtype, out, out_dtype, batch, M, K, N, (cudaStream_t)stream);
 }
 
 int32_t ttb_check_status(void *stream) { return read_and_clear_status((cudaStream_t)stream); }

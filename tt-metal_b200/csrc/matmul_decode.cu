@@ -21,7 +21,7 @@ static constexpr int64_t kCounterBytes = 65536;
 // partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
 static constexpr int64_t kAccumBytes = 16 << 20;
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, bool overlap, cudaStream_t stream);
+int32_t launch_decode_tmem(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream);
 
 // Device address of the status word on the current device (looked up once per device).
 int32_t status_word_address(int **out) {
@@ -214,9 +214,9 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
             overlap = false;   // only kernels may separate a launch from the one it overlaps with
         }
     }
-    // bfloat8_b weights of 32-row blocks reach the MMA through tensor memory; bfloat4_b, larger row blocks (and bfloat8_b
-    // on request) through shared memory
-    if (w_dtype == TTB_BFLOAT8_B && nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND)) return launch_decode_tmem(p, nb, overlap, stream);
+    // the weights of 32-row blocks reach the MMA through tensor memory; those of larger row blocks (and of any on request)
+    // through shared memory
+    if (nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND)) return launch_decode_tmem(p, w_dtype, nb, overlap, stream);
     return launch_decode_stream(p, w_dtype, nb, overlap, stream);
 }
 

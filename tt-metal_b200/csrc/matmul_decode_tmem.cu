@@ -52,13 +52,14 @@ constexpr int kEpiWarp0 = kExpandWarps;        // warps 12..15
 constexpr int kEpiThreads = 128;
 constexpr int kProducerWarp = kEpiWarp0 + 4, kMmaWarp = kProducerWarp + 1, kLoaderWarp = kProducerWarp + 3;   // two MMA issuers
 constexpr int kThreads = 32 * (kLoaderWarp + 1);
-constexpr int kTile = kBfp8TileBytes;
-constexpr int kStageBytes = 4 * kTile;         // 4352
+constexpr int NB = 32;   // activation rows per block (MMA N): one tile row
 constexpr int kAColsPerStage = BK / 2;         // TMEM columns of one expanded stage (two bf16 per column)
 constexpr uint32_t kB_SBO = 256;               // activations: 32-byte rows, eight rows per swizzle atom
 
-template <int NB>
+template <int FMT>
 struct Layout {
+    static constexpr int kTile = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
+    static constexpr int kStageBytes = 4 * kTile;                  // 4352 / 2304
     static constexpr int kRing = 8;                                // groups in flight
     static constexpr int kBStageBytes = NB * BK * 2;
     static constexpr int pk = 0;
@@ -77,7 +78,6 @@ struct Layout {
     static constexpr int kACol0 = kAccCols;                        // the A ring follows them
     static constexpr int kTmemColsUsed = kAccCols + kRing * kGroup * kAColsPerStage;
     static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;
-    static_assert(NB == 32, "one tile row of activations per block");
     static_assert(kTmemColsUsed <= 512, "tensor memory budget");
     static_assert(b % 256 == 0 && kBStageBytes % 1024 == 0, "alignment of the swizzled activation operand");
     // The teams wait on the ring barriers with different phase parities, which is only right while a waiter is at most
@@ -220,6 +220,50 @@ __device__ __noinline__ void expand_tile_big(uint32_t tile, uint32_t a_col, uint
     expand_tile<true>(tile, a_col, ld_off, eh, sh0);
 }
 
+// One packed bfloat4_b tile (576 bytes) -> the 32 TMEM lanes of this warp's quadrant. One transposing load covers the whole
+// tile: per 16-column half a lane receives two registers - four bytes of even K rows and four of odd K rows, each byte
+// the codes of columns 2p (low nibble) and 2p + 1 (high nibble), p = lane / 4. Column 2p goes to TMEM lane p, column 2p + 1
+// to TMEM lane p + 8 of the half (the epilogue reads its column index accordingly). (sign << 15) | (mantissa << 4) is the
+// weight divided by 2^(E + 4 - ...): the same subnormal trick and the same row scales as for bfloat8_b.
+__device__ __forceinline__ void ldmatrix_x2_trans_b8_2(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+template <bool BIG>
+__device__ __forceinline__ void expand_tile4(uint32_t tile, uint32_t a_col, uint32_t ld_off4, uint32_t eh, int sh0) {
+    const uint32_t my_scale = (__vminu2(eh, 0x007f007fu) + 0x007f007fu) << 7;   // 2^min(E, 127) per half
+    const uint32_t my_t = BIG ? (__vmaxu2(__vminu2(eh, 0x00fe00feu), 0x007f007fu) << 7) : 0u;
+    uint32_t m[2][2];   // [16-column half][even / odd K rows]
+    ldmatrix_x2_trans_b8_2(tile + ld_off4, m[0][0], m[0][1], m[1][0], m[1][1]);
+#pragma unroll
+    for (int nh = 0; nh < 2; ++nh) {
+        // [s m m m 0 0 0 0] per byte: columns 2p (from the low nibbles) and 2p + 1 (high nibbles), even and odd K rows
+        const uint32_t lo_e = (m[nh][0] << 4) & 0xf0f0f0f0u, lo_o = (m[nh][1] << 4) & 0xf0f0f0f0u;
+        const uint32_t hi_e = m[nh][0] & 0xf0f0f0f0u, hi_o = m[nh][1] & 0xf0f0f0f0u;
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+            // bytes 2*kh and 2*kh+1 of the registers: K rows 4q..4q+3 of the upper (kh = 0) or lower face
+            const int f = 2 * kh + nh;
+            const uint32_t s01 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0);
+            const uint32_t s23 = __shfl_sync(0xffffffffu, my_scale, 8 * f + sh0 + 1);
+            const uint32_t sel0 = kh ? 0x6622u : 0x4400u, sel1 = kh ? 0x7733u : 0x5511u;
+            uint32_t o[4];
+            o[0] = mul2(__byte_perm(lo_e, lo_o, sel0) & 0x80708070u, s01);   // column 2p: K rows (4q, 4q+1)
+            o[1] = mul2(__byte_perm(lo_e, lo_o, sel1) & 0x80708070u, s23);   //            K rows (4q+2, 4q+3)
+            o[2] = mul2(__byte_perm(hi_e, hi_o, sel0) & 0x80708070u, s01);   // column 2p + 1
+            o[3] = mul2(__byte_perm(hi_e, hi_o, sel1) & 0x80708070u, s23);
+            if (BIG) {
+                const uint32_t t01 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0);
+                const uint32_t t23 = __shfl_sync(0xffffffffu, my_t, 8 * f + sh0 + 1);
+                o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
+            }
+            tmem_st_16x256b(a_col + ((uint32_t)(nh * 16) << 16) + (uint32_t)(kh * 8), o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+__device__ __noinline__ void expand_tile4_big(uint32_t tile, uint32_t a_col, uint32_t ld_off4, uint32_t eh, int sh0) {
+    expand_tile4<true>(tile, a_col, ld_off4, eh, sh0);
+}
+
 struct EpiCtx {
     uint8_t *smem;
     uint32_t tmem_base, acc_full0, acc_empty0;
@@ -232,9 +276,9 @@ constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks e
 
 // Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
 // that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
-template <int NB>
+template <int FMT>
 __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, const int g0, bool ok) {
-    using L = Layout<NB>;
+    using L = Layout<FMT>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tid = threadIdx.x - 32 * kEpiWarp0;
     const int quad = warp & 3;
@@ -248,7 +292,11 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     tc_fence_after_sync();
     const TileRef tr = tile_ref(p, s.tile);
     const int64_t row0 = (int64_t)tr.rchunk * NB;
-    const int64_t n = (int64_t)tr.nt * BN + quad * 32 + lane;
+    // Which weight column this thread's TMEM lane holds. bfloat8_b: the lane's own. bfloat4_b: a code byte carries two
+    // neighbouring columns, and the transposing load hands the even one to lanes 0..7 and the odd one to lanes 8..15 of
+    // every 16-lane half (expand_tile4).
+    const int col_in_quad = FMT == TTB_BFLOAT8_B ? lane : (lane & 16) + ((lane & 7) << 1) + ((lane >> 3) & 1);
+    const int64_t n = (int64_t)tr.nt * BN + quad * 32 + col_in_quad;
     const bool gathered = p.ranks > 1 && tr.prob == 0;
     OutView ov;
     ov.out = p.outv[tr.prob];
@@ -382,9 +430,9 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     return eok;
 }
 
-template <int NB>
+template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const __grid_constant__ DecodeArgs p, const __grid_constant__ WeightMaps maps, const __grid_constant__ ActMap amap) {
-    using L = Layout<NB>;
+    using L = Layout<FMT>;
     constexpr int kRing = L::kRing;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -447,8 +495,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                     TL(0, tlg); ++tlg;
                     // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
                     // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
-                    mbar_arrive_expect_tx(full_pk(gs), kGroup * kStageBytes);
-                    tma_load_3d(sbase + L::pk + gs * kGroup * kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
+                    mbar_arrive_expect_tx(full_pk(gs), kGroup * L::kStageBytes);
+                    tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
             }
@@ -543,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         it.start(p, block);
         Seg s;
         for (; it.next(p, block, s); ++seg_idx) {
-            ok = epilogue<NB>(p, ectx, s, seg_idx, g0, ok);
+            ok = epilogue<FMT>(p, ectx, s, seg_idx, g0, ok);
             g0 += (s.nit + kGroup - 1) / kGroup;
         }
     } else {
@@ -551,9 +599,17 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         const int team = warp >> 2, quad = warp & 3;
         // ldmatrix row addresses: lanes 0-15 give the rows of the left face, 16-31 of the right face
         const uint32_t ld_off = 64u + (uint32_t)(lane >> 4) * 256u + (uint32_t)(lane & 15) * 16u;
+        // bfloat4_b: a 16-byte row of the transposing load is a pair of K rows of one face (8 bytes = 16 nibbles each). Lanes
+        // 0-15 give the rows of the left faces (0 and 2), lanes 16-31 of the right faces; row r of the 16 is K row pair
+        // sigma(r) of the upper (sigma < 8) or lower face, with sigma chosen such that the four rows a lane receives
+        // (4q .. 4q+3, q = lane % 4) are K rows 4q..4q+3 of the upper and of the lower face - the same K rows a lane holds
+        // for bfloat8_b, so the scale table and the TMEM columns are the same.
+        const int r16 = lane & 15;
+        const int sigma = ((r16 >> 1) & 1) * 8 + (r16 >> 2) * 2 + (r16 & 1);   // 0,1,8,9, 2,3,10,11, 4,5,12,13, 6,7,14,15
+        const uint32_t ld_off4 = 64u + (uint32_t)(lane >> 4) * 128u + (uint32_t)(sigma >> 3) * 256u + (uint32_t)(sigma & 7) * 16u;
         const int sh0 = 2 * (lane & 3);  // within a face's 8 scale pairs: this lane's K rows are 4*(lane%4) .. +3
         const uint32_t st_lane = (uint32_t)(quad * 32) << 16;
-        const uint32_t pk_quad = sbase + L::pk + quad * kTile;
+        const uint32_t pk_quad = sbase + L::pk + quad * L::kTile;
         const uint32_t a_col_q = tmem_base + st_lane + (uint32_t)L::kACol0;
         // the block's groups are numbered across segments; team t takes groups t, t + 3, ...
         SegIter it;
@@ -583,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
             if (lane == 0 && quad == 0) { TL(9, G); }
             tc_fence_after_sync();
-            uint32_t tile = pk_quad + (uint32_t)(gs * kGroup * kStageBytes);
+            uint32_t tile = pk_quad + (uint32_t)(gs * kGroup * L::kStageBytes);
             uint32_t a_col = a_col_q + (uint32_t)(gs * kGroup * kAColsPerStage);
 #pragma unroll 1
             for (int j = 0; j < r; ++j) {
@@ -591,11 +647,19 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 uint32_t e2;
                 asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e2) : "r"(tile + 2u * lane));
                 const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
-                if (__any_sync(0xffffffffu, (eh & 0x00800080u) != 0u))
-                    expand_tile_big(tile, a_col, ld_off, eh, sh0);
-                else
-                    expand_tile<false>(tile, a_col, ld_off, eh, sh0);
-                tile += kStageBytes;
+                const bool big = __any_sync(0xffffffffu, (eh & 0x00800080u) != 0u);
+                if (FMT == TTB_BFLOAT8_B) {
+                    if (big)
+                        expand_tile_big(tile, a_col, ld_off, eh, sh0);
+                    else
+                        expand_tile<false>(tile, a_col, ld_off, eh, sh0);
+                } else {
+                    if (big)
+                        expand_tile4_big(tile, a_col, ld_off4, eh, sh0);
+                    else
+                        expand_tile4<false>(tile, a_col, ld_off4, eh, sh0);
+                }
+                tile += L::kStageBytes;
                 a_col += kAColsPerStage;
             }
             if (lane == 0 && quad == 0) { TL(10, G); }
@@ -626,15 +690,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     }
 }
 
-template <int NB>
+template <int FMT>
 int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, const ActMap &amap, bool overlap, cudaStream_t stream) {
-    constexpr int smem_bytes = Layout<NB>::total + 1024;
+    constexpr int smem_bytes = Layout<FMT>::total + 1024;
     static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -647,7 +711,7 @@ int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, const ActMap &am
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<NB>, p, maps, amap));
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<FMT>, p, maps, amap));
     TTB_LAUNCH_CHECK("matmul_decode_tmem");
     return TTB_OK;
 }
@@ -661,13 +725,14 @@ extern "C" int32_t ttb_debug_timeline(void *host) {
 }
 #endif
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int nb, bool overlap, cudaStream_t stream) {
+int32_t launch_decode_tmem(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream) {
     WeightMaps maps;
-    if (int32_t rc = make_weight_maps(p, TTB_BFLOAT8_B, maps)) return rc;
+    if (int32_t rc = make_weight_maps(p, fmt, maps)) return rc;
     if (nb != 32) return fail(TTB_E_UNSUPPORTED, "the tensor-memory-operand decode kernel serves 32-row blocks");
     ActMap amap;
     if (int32_t rc = make_act_map(p, (int64_t)(p.sk_tiles / p.tstart[p.nprob]) * 32, amap)) return rc;
-    return launch_one<32>(p, maps, amap, overlap, stream);
+    if (fmt == TTB_BFLOAT8_B) return launch_one<TTB_BFLOAT8_B>(p, maps, amap, overlap, stream);
+    return launch_one<TTB_BFLOAT4_B>(p, maps, amap, overlap, stream);
 }
 
 }  // namespace ttb

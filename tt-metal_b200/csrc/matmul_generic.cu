@@ -13,8 +13,11 @@ struct GenericArgs {
     const uint8_t *w;
     const uint16_t *bias;
     void *out;
-    int64_t M, K, N;  // M already includes the batch: rows = batch * M
+    int64_t M, K, N;  // M already includes the batch when the weight is shared: rows = batch * M
     int w_dtype, out_dtype, act, a_row_major, out_row_major;
+    // batched second operand (blockIdx.z = batch entry): distances between consecutive entries, in elements of a / out
+    // and in bytes of w; all zero for a shared weight
+    int64_t a_bstride, w_bstride, out_bstride;
 };
 
 // (row, col) of face-order index k inside a tile.
@@ -31,6 +34,9 @@ __global__ void __launch_bounds__(256) matmul_generic_kernel(GenericArgs p) {
     const int64_t nt = blockIdx.x, mt = blockIdx.y;
     const int64_t Kt = p.K / 32, Nt = p.N / 32;
     const int ty = t >> 4, tx = t & 15;
+    const int64_t bz = blockIdx.z;
+    const uint16_t *const a_base = p.a + bz * p.a_bstride;
+    const uint8_t *const w_base = p.w + bz * p.w_bstride;
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     for (int64_t kt = 0; kt < Kt; ++kt) {
         // activations: four consecutive face-order elements per thread
@@ -39,9 +45,9 @@ __global__ void __launch_bounds__(256) matmul_generic_kernel(GenericArgs p) {
             face_rc(4 * t, r, c);
             uint2 v;
             if (p.a_row_major)
-                v = __ldg(reinterpret_cast<const uint2 *>(p.a + (mt * 32 + r) * p.K + kt * 32 + c));
+                v = __ldg(reinterpret_cast<const uint2 *>(a_base + (mt * 32 + r) * p.K + kt * 32 + c));
             else
-                v = __ldg(reinterpret_cast<const uint2 *>(p.a + (mt * Kt + kt) * 1024 + 4 * t));
+                v = __ldg(reinterpret_cast<const uint2 *>(a_base + (mt * Kt + kt) * 1024 + 4 * t));
             As[r][c + 0] = __uint_as_float(v.x << 16);
             As[r][c + 1] = __uint_as_float(v.x & 0xffff0000u);
             As[r][c + 2] = __uint_as_float(v.y << 16);
@@ -53,16 +59,16 @@ __global__ void __launch_bounds__(256) matmul_generic_kernel(GenericArgs p) {
             const int64_t tile = kt * Nt + nt;
             uint32_t u[4];
             if (p.w_dtype == TTB_BFLOAT16) {
-                uint2 v = __ldg(reinterpret_cast<const uint2 *>(p.w + (tile * 1024 + 4 * t) * 2));
+                uint2 v = __ldg(reinterpret_cast<const uint2 *>(w_base + (tile * 1024 + 4 * t) * 2));
                 u[0] = v.x << 16; u[1] = v.x & 0xffff0000u; u[2] = v.y << 16; u[3] = v.y & 0xffff0000u;
             } else if (p.w_dtype == TTB_BFLOAT8_B) {
-                const uint8_t *tb = p.w + tile * kBfp8TileBytes;
+                const uint8_t *tb = w_base + tile * kBfp8TileBytes;
                 const uint32_t E = __ldg(tb + (t >> 2));
                 const uint32_t cw = __ldg(reinterpret_cast<const uint32_t *>(tb + 64 + 4 * t));
 #pragma unroll
                 for (int i = 0; i < 4; ++i) u[i] = bfp_from_code<7>((cw >> (8 * i)) & 0xff, E);
             } else {
-                const uint8_t *tb = p.w + tile * kBfp4TileBytes;
+                const uint8_t *tb = w_base + tile * kBfp4TileBytes;
                 const uint32_t E = __ldg(tb + (t >> 2));
                 const uint32_t cw = __ldg(reinterpret_cast<const uint16_t *>(tb + 64 + 2 * t));
 #pragma unroll
@@ -91,7 +97,7 @@ __global__ void __launch_bounds__(256) matmul_generic_kernel(GenericArgs p) {
             float v = acc[i][j];
             if (p.bias) v += bias_at(p.bias, c);
             v = apply_activation(v, p.act);
-            const int64_t off = p.out_row_major ? r * p.N + c : tiled_offset(r, c, Nt);
+            const int64_t off = bz * p.out_bstride + (p.out_row_major ? r * p.N + c : tiled_offset(r, c, Nt));
             if (p.out_dtype == TTB_FLOAT32)
                 reinterpret_cast<float *>(p.out)[off] = v;
             else
@@ -109,10 +115,30 @@ int32_t launch_matmul_generic(const void *a, const void *w, int w_dtype, const v
     p.w_dtype = w_dtype; p.out_dtype = out_dtype; p.act = act;
     p.a_row_major = (flags & TTB_MM_A_ROW_MAJOR) != 0;
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
+    p.a_bstride = p.w_bstride = p.out_bstride = 0;
     if (rows / 32 > 65535) return fail(TTB_E_UNSUPPORTED, "ttb_matmul (generic kernel): more than 65535 row tiles");
     dim3 grid((unsigned)(N / 32), (unsigned)(rows / 32));
     matmul_generic_kernel<<<grid, 256, 0, stream>>>(p);
     TTB_LAUNCH_CHECK("matmul_generic");
+    return TTB_OK;
+}
+
+// out[b] = a[b] x w[b] for `batch` independent [M, K] x [K, N] products (tiled operands).
+int32_t launch_bmm_generic(const void *a, const void *w, int w_dtype, void *out, int out_dtype, int64_t batch, int64_t M, int64_t K,
+                           int64_t N, cudaStream_t stream) {
+    GenericArgs p;
+    p.a = (const uint16_t *)a; p.w = (const uint8_t *)w; p.bias = nullptr; p.out = out;
+    p.M = M; p.K = K; p.N = N;
+    p.w_dtype = w_dtype; p.out_dtype = out_dtype; p.act = TTB_ACT_NONE;
+    p.a_row_major = 0;
+    p.out_row_major = 0;
+    p.a_bstride = M * K;
+    p.out_bstride = M * N;
+    p.w_bstride = w_dtype == TTB_BFLOAT16 ? K * N * 2 : K * N / 1024 * bfp_tile_bytes(w_dtype);
+    if (M / 32 > 65535 || batch > 65535) return fail(TTB_E_UNSUPPORTED, "ttb_bmm: more than 65535 row tiles or batch entries");
+    dim3 grid((unsigned)(N / 32), (unsigned)(M / 32), (unsigned)batch);
+    matmul_generic_kernel<<<grid, 256, 0, stream>>>(p);
+    TTB_LAUNCH_CHECK("bmm_generic");
     return TTB_OK;
 }
 

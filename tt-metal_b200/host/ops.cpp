@@ -382,8 +382,7 @@ void validate_operand(const char *op, const char *name, const Tensor &t, bool we
     if (t.layout() != Layout::TILE) throw_error(who + " must be of layout Layout.TILE, but got " + to_string(t.layout()));
     if (t.storage_type() != StorageType::DEVICE) throw_error(who + " must be on device!");
     if (!t.is_allocated()) throw_error(who + " must be allocated!");
-    if (!weight && d != DataType::BFLOAT16)
-        throw_error(who + ": block-float activations are not supported on this device; use bfloat16 activations");
+    (void)weight;
 }
 
 int activation_code(const std::optional<std::string> &act) {
@@ -394,24 +393,44 @@ int activation_code(const std::optional<std::string> &act) {
     throw_error("ttnn.linear: Unsupported activation function " + *act);
 }
 
-Tensor run_matmul(const char *op, const Tensor &a, const Tensor &b, const std::optional<Tensor> &bias, std::optional<DataType> dtype,
+Tensor run_matmul(const char *op, const Tensor &a_in, const Tensor &b, const std::optional<Tensor> &bias, std::optional<DataType> dtype,
                   const std::optional<std::string> &activation) {
-    validate_operand(op, "input_tensor_a", a, false);
+    validate_operand(op, "input_tensor_a", a_in, false);
     validate_operand(op, "input_tensor_b", b, true);
-    if (a.device() != b.device()) throw_error(std::string(op) + ": operands must be on the same device");
-    const Shape &sa = a.shape(), &sb = b.shape();
+    if (a_in.device() != b.device()) throw_error(std::string(op) + ": operands must be on the same device");
+    const Shape &sa = a_in.shape(), &sb = b.shape();
     const int64_t width_a = sa[-1], height_b = sb[-2];
     if (width_a != height_b) throw_error(std::string(op) + ": The width of the first tensor must be equal to the height of the second tensor");
-    for (size_t i = 0; i + 2 < sb.rank(); ++i)
-        if (sb.dims()[i] != 1) throw_error(std::string(op) + ": a batched second operand is not supported on this path; the weight must be [.., 1, K, N]");
     const auto &pa = sa.padded(), &pb = sb.padded();
     const int64_t Mp = pa[pa.size() - 2], Kp = pa[pa.size() - 1], Np = pb[pb.size() - 1];
     if (pb[pb.size() - 2] != Kp) throw_error(std::string(op) + ": padded inner dimensions disagree");
-    int64_t batch = 1;
+    int64_t batch = 1, batch_b = 1;
     for (size_t i = 0; i + 2 < pa.size(); ++i) batch *= pa[i];
-    const DataType out_dtype = dtype.value_or(a.dtype());
-    if (out_dtype != DataType::BFLOAT16 && out_dtype != DataType::FLOAT32)
-        throw_error(std::string(op) + ": output dtype must be bfloat16 or float32 on this device");
+    for (size_t i = 0; i + 2 < pb.size(); ++i) batch_b *= pb[i];
+    // The second operand is either one [K, N] matrix shared by every batch entry of the first, or carries the first
+    // operand's batch (tt::tt_metal::bmm, tt_eager/tt_dnn/op_library/bmm/bmm_op.cpp:518-626).
+    const bool batched_b = batch_b != 1;
+    if (batched_b) {
+        if (batch_b != batch) throw_error(std::string(op) + ": a batched second operand must have the batch dimensions of the first");
+        if (bias) throw_error(std::string(op) + ": bias is not supported with a batched second operand");
+        if (activation) throw_error(std::string(op) + ": a fused activation is not supported with a batched second operand");
+    }
+    // output dtype = dtype or the first operand's (bmm_op.cpp:1148-1161); block-float outputs are the host packer's
+    // arithmetic applied to the fp32 result
+    const DataType out_dtype = dtype.value_or(a_in.dtype());
+    if (out_dtype != DataType::BFLOAT16 && out_dtype != DataType::FLOAT32 && !is_block_float(out_dtype))
+        throw_error(std::string(op) + ": output dtype must be bfloat16, float32, bfloat8_b or bfloat4_b");
+    Device *dev = a_in.device();
+    dev->make_current();
+    // block-float activations (bmm_op.cpp:839 admits them) are expanded to bfloat16 first: exact
+    Tensor a = a_in;
+    if (is_block_float(a_in.dtype())) {
+        int64_t outer, H, W;
+        sa.as_outer_hw(outer, H, W, /*padded=*/true);
+        auto ab = allocate_device_buffer(dev, sa.padded_volume() * 2);
+        check(ttb_unpack_bfp(a_in.data(), ttb_dtype(a_in.dtype()), ab->ptr, TTB_BFLOAT16, outer, H, W, /*dst_row_major=*/0, 0, nullptr), op);
+        a = Tensor(ab, sa, DataType::BFLOAT16, Layout::TILE);
+    }
     const void *bias_ptr = nullptr;
     if (bias) {
         // TILE layout, [.., N] padded to one tile row: [1,1,32,N] in the reference (bmm_op.cpp:859-863).
@@ -428,19 +447,29 @@ Tensor run_matmul(const char *op, const Tensor &a, const Tensor &b, const std::o
     od.back() = sb[-1];
     op_.back() = Np;
     Shape out_shape(od, op_);
-    Device *dev = a.device();
-    dev->make_current();
-    auto outb = allocate_device_buffer(dev, physical_bytes(out_shape, out_dtype, Layout::TILE));
-    const int64_t ws_bytes = ttb_matmul_workspace_bytes(ttb_dtype(b.dtype()), batch, Mp, Kp, Np, 0);
-    void *ws = ws_bytes > 0 ? dev->workspace(ws_bytes) : nullptr;
-    // Every producer of a block-float tensor on this API (from_torch, to_layout, load_tensor, to_device) has finished on the
-    // device before it returns, so a block-float weight is complete long before this launch is enqueued and the kernel may
-    // stream it while the previous kernel drains.
-    const int flags = TTB_MM_WORKSPACE_ZEROED | (is_block_float(b.dtype()) ? TTB_MM_WEIGHTS_RESIDENT : 0);
-    check(ttb_matmul(a.data(), ttb_dtype(a.dtype()), b.data(), ttb_dtype(b.dtype()), bias_ptr, outb->ptr, ttb_dtype(out_dtype), batch, Mp,
-                     Kp, Np, activation_code(activation), flags, ws, ws_bytes, nullptr),
-          op);
-    return Tensor(outb, out_shape, out_dtype, Layout::TILE);
+    const DataType kernel_out = is_block_float(out_dtype) ? DataType::FLOAT32 : out_dtype;
+    auto outb = allocate_device_buffer(dev, physical_bytes(out_shape, kernel_out, Layout::TILE));
+    if (batched_b) {
+        check(ttb_bmm(a.data(), ttb_dtype(a.dtype()), b.data(), ttb_dtype(b.dtype()), outb->ptr, ttb_dtype(kernel_out), batch, Mp, Kp, Np, nullptr), op);
+    } else {
+        const int64_t ws_bytes = ttb_matmul_workspace_bytes(ttb_dtype(b.dtype()), batch, Mp, Kp, Np, 0);
+        void *ws = ws_bytes > 0 ? dev->workspace(ws_bytes) : nullptr;
+        // Every producer of a block-float tensor on this API (from_torch, to_layout, load_tensor, to_device) has finished on the
+        // device before it returns, so a block-float weight is complete long before this launch is enqueued and the kernel may
+        // stream it while the previous kernel drains.
+        const int flags = TTB_MM_WORKSPACE_ZEROED | (is_block_float(b.dtype()) ? TTB_MM_WEIGHTS_RESIDENT : 0);
+        check(ttb_matmul(a.data(), ttb_dtype(a.dtype()), b.data(), ttb_dtype(b.dtype()), bias_ptr, outb->ptr, ttb_dtype(kernel_out), batch, Mp,
+                         Kp, Np, activation_code(activation), flags, ws, ws_bytes, nullptr),
+              op);
+    }
+    if (!is_block_float(out_dtype)) return Tensor(outb, out_shape, out_dtype, Layout::TILE);
+    // pack the fp32 tiles (already in tile order) with the device packer: bit-exact with packing the fp32 result on the host
+    auto packed = allocate_device_buffer(dev, physical_bytes(out_shape, out_dtype, Layout::TILE));
+    int64_t outer, H, W;
+    out_shape.as_outer_hw(outer, H, W, /*padded=*/true);
+    check(ttb_pack_bfp(outb->ptr, TTB_FLOAT32, packed->ptr, ttb_dtype(out_dtype), outer, H, W, /*src_row_major=*/0, /*two_pass=*/0, nullptr), op);
+    check(ttb_stream_synchronize(nullptr), op);   // block-float tensors are complete when they are returned
+    return Tensor(packed, out_shape, out_dtype, Layout::TILE);
 }
 
 }  // namespace
