@@ -70,6 +70,11 @@ extern "C" {
                                       drains and wait for it before touching activations, bias, workspace or output.
                                       Takes effect together with TTB_MM_WORKSPACE_ZEROED (no memset between the kernels). */
 
+#define TTB_MM_GATED 256 /* ttb_matmul_multi with two weights of one shape: out[0] = act(a w[0] + bias[0]) * (a w[1] + bias[1]),
+                            the gated MLP's silu(x w1) * (x w3) (models/demos/mistral7b/tt/mistral_mlp.py:51-73,
+                            llama2_70b/tt/llama_mlp_optimized.py:165-197) formed inside the launch; out[1] is not written.
+                            Workspace: ttb_matmul_gated_workspace_bytes. Row counts of 32, 96, 160 or 224. */
+
 const char *ttb_last_error(void);
 int32_t ttb_version(void);
 
@@ -297,6 +302,7 @@ int32_t ttb_matmul_peer(const void *a_dev, int32_t a_dtype, const void *w_dev, i
  * applies to weight 0 only: its result goes to gather->out[...] on every rank and out[0] is ignored; `wait` as in
  * ttb_matmul_peer. Results are identical to `count` calls of ttb_matmul. */
 int64_t ttb_matmul_multi_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N);
+int64_t ttb_matmul_gated_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N);
 int32_t ttb_matmul_multi(const void *a_dev, int32_t a_dtype, int32_t count, const void *const *w_dev, int32_t w_dtype,
                          const void *const *bias_dev, void *const *out_dev, int32_t out_dtype, int64_t batch, int64_t M,
                          int64_t K, const int64_t *N, int32_t activation, int32_t flags, void *workspace_dev,

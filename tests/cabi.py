@@ -15,6 +15,7 @@ ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 MM_A_ROW_MAJOR, MM_OUT_ROW_MAJOR, MM_FORCE_GENERIC, MM_WORKSPACE_ZEROED, MM_DECODE_TMEM_OPERAND, MM_DETERMINISTIC = 1, 2, 4, 8, 16, 32
 MM_WEIGHTS_RESIDENT = 64
 MM_DECODE_SMEM_OPERAND = 128
+MM_GATED = 256
 TILE_BYTES = {BFLOAT8_B: 1088, BFLOAT4_B: 576}
 
 _vp, _i32, _i64, _sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
@@ -56,6 +57,7 @@ _SIGS = {
     "ttb_matmul_peer": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_peer_wait": (_i32, [_vp, _vp]),
     "ttb_matmul_decode_plan": (_i32, [_i32, _i64, _i64, _i64, _i32, _vp, _vp, _i32]),
+    "ttb_matmul_gated_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_matmul_multi_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i32, _vp]),
     "ttb_matmul_multi": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "ttb_comm_unique_id": (_i32, [_vp]),

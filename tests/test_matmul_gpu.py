@@ -402,3 +402,47 @@ def test_multi_arguments_are_validated(ttb):
     assert rc == -1 and b"count" in ttb.cdll.ttb_last_error()
     torch.cuda.synchronize()
     assert int(buf.count_nonzero().item()) == 0
+
+
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
+@pytest.mark.parametrize("M,K,N", [(32, 512, 256), (32, 4096, 1024), (96, 1024, 384), (32, 4096, 14336), (32, 256, 18944)])
+def test_gated_pair_in_one_launch(ttb, orc, w_dtype, M, K, N):
+    """MM_GATED: out = silu(a w0 + b0) * (a w1): the gate multiply of the gated MLP formed inside the launch, with and
+    without K split over blocks, against fp32 torch on the oracle-unpacked weights; the scratch is clean afterwards and a
+    second launch gives the same bytes under a fixed reduction order."""
+    import ctypes
+    import torch
+    x = vectors.randn(71, (M, K), 1.0).bfloat16()
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    if K * N > 8 << 20:
+        (w0, r0), (w1, r1) = (make_big_case(ttb, orc, 72 + j, K, N, w_dtype) for j in range(2))
+    else:
+        (_, w0, r0), (_, w1, r1) = (make_case(ttb, orc, 72 + j, M, K, N, w_dtype, w_std=0.05) for j in range(2))
+    bias = vectors.randn(75, (1, N), 0.5).bfloat16()
+    b0 = ttb.tilize(torch.cat([bias, torch.zeros(31, N, dtype=torch.bfloat16)]).cuda(), 1, 32, N)
+    out = torch.empty(M * N, dtype=torch.bfloat16, device="cuda")
+    arr_w = (ctypes.c_void_p * 2)(w0.data_ptr(), w1.data_ptr())
+    arr_b = (ctypes.c_void_p * 2)(b0.data_ptr(), None)
+    arr_o = (ctypes.c_void_p * 2)(out.data_ptr(), None)
+    arr_n = (ctypes.c_int64 * 2)(N, N)
+    nbytes = ttb.matmul_gated_workspace_bytes(w_dtype, 1, M, K, N)
+    assert nbytes > 0
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    results = []
+    for rep in range(2):
+        out.zero_()
+        ttb.check(ttb.cdll.ttb_matmul_multi(a.data_ptr(), cabi.BFLOAT16, 2, arr_w, w_dtype, arr_b, arr_o, cabi.BFLOAT16, 1, M, K, arr_n,
+                                            cabi.ACT_SILU, cabi.MM_GATED | cabi.MM_WORKSPACE_ZEROED | cabi.MM_DETERMINISTIC, ws.data_ptr(), nbytes,
+                                            None, None, None))
+        ttb.check(ttb.check_status(None))
+        results.append(out.clone())
+        assert int(ws[: 65536 + (16 << 20)].count_nonzero().item()) == 0
+    assert torch.equal(results[0], results[1])
+    xf = x.float().cuda()
+    ref = torch.nn.functional.silu(xf @ r0.cuda() + bias.float().cuda()) * (xf @ r1.cuda())
+    check(ttb.untilize(results[0], 1, M, N).reshape(M, N), ref)
+    # refused where it cannot run: three weights, unequal shapes
+    arr_n2 = (ctypes.c_int64 * 2)(N, 128)
+    rc = ttb.cdll.ttb_matmul_multi(a.data_ptr(), cabi.BFLOAT16, 2, arr_w, w_dtype, None, arr_o, cabi.BFLOAT16, 1, M, K, arr_n2,
+                                   cabi.ACT_SILU, cabi.MM_GATED | cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None, None, None)
+    assert rc == -1

@@ -252,3 +252,23 @@ def test_linear_with_block_float_activation_and_output(device, orc, out_dtype, o
     z = ttnn.linear(yq, w2, dtype=ttnn.bfloat16)
     zref = _unpacked(yq, ofmt, orc).reshape(M, N) @ _unpacked(w2, oracle.BFP8_B, orc).reshape(N, 128)
     assert oracle.comp_pcc(zref.numpy(), ttnn.to_torch(z).float().reshape(M, 128).numpy()) >= 0.9999
+
+
+@pytest.mark.parametrize("rows", [32, 64])
+def test_linear_gated_equals_the_three_op_sequence(device, orc, rows):
+    """ttnn.linear_gated against ttnn.linear(silu) x ttnn.linear -> ttnn.mul (mistral_mlp.py:51-73): one launch for 32 rows,
+    the fallback sequence for 64; both within bf16 rounding of the unfused result (which rounds the two factors first)."""
+    H, F = 1024, 2048
+    x = vectors.randn(51, (1, 1, rows, H), 1.0).bfloat16()
+    w1 = ttnn.from_torch(vectors.randn(52, (H, F), 0.05), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    w3 = ttnn.from_torch(vectors.randn(53, (H, F), 0.05), dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    xt = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    fused = ttnn.linear_gated(xt, w1, w3)
+    assert list(fused.shape) == [1, 1, rows, F] and fused.dtype == ttnn.bfloat16
+    unfused = ttnn.mul(ttnn.linear(xt, w1, activation="silu"), ttnn.linear(xt, w3))
+    xf = x.float().reshape(rows, H)
+    ref = torch.nn.functional.silu(xf @ _unpacked(w1, oracle.BFP8_B, orc).reshape(H, F)) * (xf @ _unpacked(w3, oracle.BFP8_B, orc).reshape(H, F))
+    for got in (fused, unfused):
+        y = ttnn.to_torch(got).float().reshape(rows, F)
+        assert oracle.comp_pcc(ref.numpy(), y.numpy()) >= 0.9999
+        assert float((y - ref).abs().max() / ref.abs().max()) <= 1e-2

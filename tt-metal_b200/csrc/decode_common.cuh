@@ -63,6 +63,11 @@ struct DecodeArgs {
     int sk_waves, sk_rem_tile0;      // rounds of whole tiles (tile = round * sk_grid + block), first tile of the split remainder
     int sk_tiles;                    // tiles in the list (all row chunks)
     int sk_units, sk_q, sk_r;        // units of the streamed remainder; units / blocks and units % blocks
+    // ---- gated pair (two weights, out = act(a w0 + b0) * (a w1 + b1)): whoever finishes a tile of either weight leaves its
+    // fp32 values in `gate` and takes a ticket on the pair's counter; the second one forms the product and stores it ----
+    int gated;
+    float *gate;
+    int *gate_counters;
     // ---- limit of the bounded waits in SM clocks (0 = the built-in defaults), set by ttb_set_wait_limit_cycles ----
     long long wait_limit;
 };

@@ -140,8 +140,12 @@ static bool stream_accumulate_ok(int64_t rows, int nprob, const int64_t *N) {
 }
 static int64_t stream_partial_bytes(const StreamPlan &sp) { return (int64_t)sp.slots * BN * sp.nb * 4; }
 
-int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const int64_t *N, bool compact) {
+// Gated pair: one fp32 tile per tile of either weight, where the first finisher of a pair leaves its values.
+static int64_t stream_gate_bytes(const StreamPlan &sp) { return (int64_t)sp.tiles_total * BN * sp.nb * 4; }
+
+int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const int64_t *N, bool compact, bool gated = false) {
     const StreamPlan sp = stream_plan(rows, K, nprob, N);
+    if (gated) return kCounterBytes + kAccumBytes + stream_partial_bytes(sp) + stream_gate_bytes(sp);
     if (!sp.shared_tiles) return 0;
     return kCounterBytes + (compact ? 0 : kAccumBytes) + stream_partial_bytes(sp);
 }
@@ -187,6 +191,14 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
     p.sk_waves = sp.waves; p.sk_rem_tile0 = sp.rem_tile0; p.sk_tiles = sp.tiles_total;
     p.splits = sp.pieces; p.kb_per_split = sp.kbps;
     p.ordered = compact || (flags & TTB_MM_DETERMINISTIC) != 0 || !stream_accumulate_ok(rows, nprob, N);
+    const bool gated = (flags & TTB_MM_GATED) != 0;
+    if (gated) {
+        if (nprob != 2 || N[0] != N[1]) return fail(TTB_E_INVALID, "ttb_matmul_multi: a gated launch takes two weights of one shape");
+        if (nb != 32 || compact || (flags & TTB_MM_DECODE_SMEM_OPERAND))
+            return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: the gated form serves row counts that are odd multiples of 32 (32, 96, 160, 224)");
+        if ((int64_t)(sp.tiles_total + sp.tiles_total / 2) * 4 > kCounterBytes) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: too many tiles for a gated launch");
+        p.gated = 1;
+    }
     if (gather) {
         p.ranks = gather->ranks; p.rank = gather->rank;
         p.outv[0] = gather->out[gather->rank];
@@ -198,8 +210,8 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
         p.expected = gather->expected;
         p.launch_arrivals = (unsigned)(gather->ranks * (int)(N[0] / BN) * sp.rchunks);
     }
-    if (sp.shared_tiles) {
-        const int64_t need = decode_workspace_bytes_multi(rows, K, nprob, N, compact);
+    if (sp.shared_tiles || gated) {
+        const int64_t need = decode_workspace_bytes_multi(rows, K, nprob, N, compact, gated);
         if (!workspace || workspace_bytes < need)
             return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
                         (long long)workspace_bytes);
@@ -207,6 +219,10 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
         p.counters = (int *)workspace;
         p.accum = (float *)((uint8_t *)workspace + kCounterBytes);
         p.partial = (float *)((uint8_t *)workspace + kCounterBytes + (compact ? 0 : kAccumBytes));
+        if (gated) {
+            p.gate = (float *)((uint8_t *)workspace + kCounterBytes + kAccumBytes + stream_partial_bytes(sp));
+            p.gate_counters = p.counters + sp.tiles_total;
+        }
         if (!counters_are_zero) {
             // counters always; in accumulate mode also the tiles this launch adds into
             const int64_t zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * nsum * 4);
@@ -362,6 +378,13 @@ extern "C" int64_t ttb_matmul_multi_workspace_bytes(int32_t w_dtype, int64_t bat
     return decode_workspace_bytes_multi(batch * M, K, count, N, false);
 }
 
+extern "C" int64_t ttb_matmul_gated_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N) {
+    using namespace ttb;
+    const int64_t Ns[2] = {N, N};
+    if (batch <= 0 || M <= 0 || !decode_supported_multi(w_dtype, batch * M, K, 2, Ns)) return 0;
+    return decode_workspace_bytes_multi(batch * M, K, 2, Ns, false, true);
+}
+
 extern "C" int32_t ttb_matmul_multi(const void *a, int32_t a_dtype, int32_t count, const void *const *w, int32_t w_dtype,
                                     const void *const *bias, void *const *out, int32_t out_dtype, int64_t batch, int64_t M, int64_t K,
                                     const int64_t *N, int32_t act, int32_t flags, void *workspace, int64_t workspace_bytes,
@@ -374,7 +397,8 @@ extern "C" int32_t ttb_matmul_multi(const void *a, int32_t a_dtype, int32_t coun
     if (batch <= 0 || M <= 0 || K <= 0 || M % 32 || K % 32) return fail(TTB_E_INVALID, "ttb_matmul_multi: batch, M, K must be positive and M, K multiples of 32");
     if (act < TTB_ACT_NONE || act > TTB_ACT_SILU) return fail(TTB_E_INVALID, "ttb_matmul_multi: unknown activation %d", act);
     for (int j = 0; j < count; ++j) {
-        if (!w[j] || (!out[j] && !(gather && j == 0))) return fail(TTB_E_INVALID, "ttb_matmul_multi: null tensor pointer for weight %d", j);
+        if (!w[j] || (!out[j] && !(gather && j == 0) && !((flags & TTB_MM_GATED) && j == 1)))
+            return fail(TTB_E_INVALID, "ttb_matmul_multi: null tensor pointer for weight %d", j);
         if (N[j] <= 0 || N[j] % 32) return fail(TTB_E_INVALID, "ttb_matmul_multi: N[%d] must be a positive multiple of 32", j);
         if ((reinterpret_cast<uintptr_t>(w[j]) | reinterpret_cast<uintptr_t>(out[j])) & 15)
             return fail(TTB_E_INVALID, "ttb_matmul_multi: tensors must be 16-byte aligned");
@@ -395,7 +419,7 @@ extern "C" int32_t ttb_matmul_multi(const void *a, int32_t a_dtype, int32_t coun
     }
     if (wait && (!wait->arrived || !wait->expected)) return fail(TTB_E_INVALID, "ttb_matmul_multi: incomplete wait description");
     return launch_matmul_decode_multi(a, count, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
-                                      flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT | TTB_MM_DECODE_SMEM_OPERAND),
+                                      flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT | TTB_MM_DECODE_SMEM_OPERAND | TTB_MM_GATED),
                                       workspace, workspace_bytes, (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false,
                                       (cudaStream_t)stream, gather, wait);
 }

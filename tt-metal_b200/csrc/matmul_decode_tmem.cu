@@ -297,7 +297,9 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     // every 16-lane half (expand_tile4).
     const int col_in_quad = FMT == TTB_BFLOAT8_B ? lane : (lane & 16) + ((lane & 7) << 1) + ((lane >> 3) & 1);
     const int64_t n = (int64_t)tr.nt * BN + quad * 32 + col_in_quad;
-    const bool gathered = p.ranks > 1 && tr.prob == 0;
+    // (gated pair: both weights' tiles lead to the one product tensor, which takes the first weight's place)
+    const bool gathered = p.ranks > 1 && (tr.prob == 0 || p.gated);
+    const int gate_pair = tr.rchunk * p.tstart[1] + tr.nt;
     OutView ov;
     ov.out = p.outv[tr.prob];
     ov.bias = p.biasv[tr.prob];
@@ -415,15 +417,60 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                     acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);   // leave zeros for the next launch
                 }
             }
-            finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+            if (!p.gated) {
+                finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+            } else {
+                // gated pair: bias (and, for the first weight, the activation) in fp32, left for whoever finishes the pair
+                const float bias = ov.bias ? bias_at(ov.bias, n) : 0.0f;
+                float4 *dst = reinterpret_cast<float4 *>(p.gate + ((int64_t)(gate_pair * 2 + tr.prob) * BN + quad * 32 + lane) * NB + col0);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = tr.prob == 0 ? apply_activation(v[j] + bias, p.act) : v[j] + bias;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+            }
         }
         if (contributors > 1 && tid == 0) p.counters[s.tile] = 0;
     }
     if (contributors == 1) release_accumulator();
+    bool send = finished;
+    if (p.gated) {
+        // the second of the pair's two tiles to be finished forms the product (the same four warps run through the same
+        // barriers whether or not this block finished anything)
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0) {
+            int second = 0;
+            if (finished && (eok || contributors > 1)) second = atomicAdd(p.gate_counters + gate_pair, 1) == 1 ? 1 : 0;
+            __threadfence();
+            *c.last_flag = second;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        send = *c.last_flag != 0;
+        if (send) {
+            OutView og = ov;
+            og.out = p.outv[0];
+            og.bias = nullptr;
+#pragma unroll
+            for (int cc = 0; cc < NB / 16; ++cc) {
+                const int col0 = cc * 16;
+                const float4 *g0 = reinterpret_cast<const float4 *>(p.gate + ((int64_t)(gate_pair * 2) * BN + quad * 32 + lane) * NB + col0);
+                const float4 *g1 = g0 + (int64_t)BN * NB / 4;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 x = __ldcg(g0 + j), y = __ldcg(g1 + j);
+                    v[4 * j] = x.x * y.x; v[4 * j + 1] = x.y * y.y; v[4 * j + 2] = x.z * y.z; v[4 * j + 3] = x.w * y.w;
+                }
+                finish_and_store_t<TTB_ACT_NONE>(p, og, v, row0, col0, n, stage);
+            }
+            if (tid == 0) p.gate_counters[gate_pair] = 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");   // (last_flag is reused below)
+    }
     if (gathered) {
         // one decision for the four warps, so that all of them take part in gather_send's barriers
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        if (tid == 0) *c.last_flag = (finished && *c.abort_flag == 0) ? 1 : 0;
+        if (tid == 0) *c.last_flag = (send && *c.abort_flag == 0) ? 1 : 0;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (*c.last_flag) gather_send<NB>(p, stage, row0, tr.nt, tid, kEpiThreads);   // ends with a barrier: the slab is free again
     }

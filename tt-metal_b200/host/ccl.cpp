@@ -136,8 +136,9 @@ int activation_code_of(const std::optional<std::string> &act) {
 
 std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
                                  const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot,
-                                 int *gather_slot) {
-    const char *op = "ttnn.linear_multi";
+                                 int *gather_slot, bool gated) {
+    const char *op = gated ? "ttnn.linear_gated" : "ttnn.linear_multi";
+    if (gated && weights.size() != 2) throw_error(std::string(op) + ": takes the two weights of the gate and up projections");
     const int n = (int)weights.size();
     if (n < 1 || n > TTB_MAX_GROUP) throw_error(std::string(op) + ": between one and four weights per launch");
     if (!biases.empty() && (int)biases.size() != n) throw_error(std::string(op) + ": one bias (or None) per weight");
@@ -175,30 +176,41 @@ std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &wei
     }
     Device *dev = x.device();
     dev->make_current();
+    if (gated && N[0] != N[1]) throw_error(std::string(op) + ": both weights must have the same shape");
+    if (gated && rows % 64 == 0) {
+        // the fused form serves 32-row blocks; otherwise two linears and their product (same values, three launches)
+        if (gather_first || wait_slot >= 0) throw_error(std::string(op) + ": the gathered form needs a row count of 32, 96, 160 or 224");
+        Tensor g = linear(x, weights[0], biases.empty() ? std::nullopt : biases[0], std::nullopt, activation, std::nullopt);
+        Tensor u = linear(x, weights[1], biases.empty() ? std::nullopt : biases[1], std::nullopt, std::nullopt, std::nullopt);
+        if (gather_slot) *gather_slot = -1;
+        return {multiply(g, u)};
+    }
     if ((gather_first || wait_slot >= 0) && !ring) throw_error(std::string(op) + ": gathering or waiting needs the mesh's ring of gather points");
     const int G = gather_first ? ring->ranks() : 1;
     int slot = -1;
     if (gather_first) slot = ring->take((int64_t)G * rows * N[0] * 2);
     // one allocation for all local outputs of the launch
     const int first_local = gather_first ? 1 : 0;
+    const int n_out = gated ? 1 : n;
     int64_t total = 0;
-    for (int j = first_local; j < n; ++j) total += rows * N[j];
+    for (int j = first_local; j < n_out; ++j) total += rows * N[j];
     std::shared_ptr<DeviceBuffer> block = total ? allocate_device_buffer(dev, total * 2) : nullptr;
     int64_t off = 0;
-    for (int j = first_local; j < n; ++j) {
+    for (int j = first_local; j < n_out; ++j) {
         o_ptr[j] = static_cast<uint8_t *>(block->ptr) + off * 2;
         off += rows * N[j];
     }
-    const int64_t need = ttb_matmul_multi_workspace_bytes(static_cast<int>(fmt), 1, rows, K, n, N);
+    const int64_t need = gated ? ttb_matmul_gated_workspace_bytes(static_cast<int>(fmt), 1, rows, K, N[0])
+                               : ttb_matmul_multi_workspace_bytes(static_cast<int>(fmt), 1, rows, K, n, N);
     void *ws = need > 0 ? dev->workspace(need) : nullptr;
     check(ttb_matmul_multi(x.data(), TTB_BFLOAT16, n, w_ptr, static_cast<int>(fmt), any_bias ? b_ptr : nullptr, o_ptr, TTB_BFLOAT16, 1, rows, K, N,
-                           activation_code_of(activation), TTB_MM_WORKSPACE_ZEROED | TTB_MM_WEIGHTS_RESIDENT, ws, need,
+                           activation_code_of(activation), TTB_MM_WORKSPACE_ZEROED | TTB_MM_WEIGHTS_RESIDENT | (gated ? TTB_MM_GATED : 0), ws, need,
                            gather_first ? ring->gather(slot) : nullptr, wait_slot >= 0 ? ring->wait(wait_slot) : nullptr, nullptr),
           op);
     if (gather_slot) *gather_slot = slot;
     std::vector<int64_t> lead(x.shape().dims().begin(), x.shape().dims().end() - 1), lead_p(xp.begin(), xp.end() - 1);
     std::vector<Tensor> results;
-    for (int j = 0; j < n; ++j) {
+    for (int j = 0; j < n_out; ++j) {
         std::vector<int64_t> d = lead, dp = lead_p;
         if (j < first_local) {
             d.push_back(G * Nl[j]);

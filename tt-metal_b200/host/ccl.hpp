@@ -71,8 +71,11 @@ class GatherRing {
 // `gather_first` the first result is gathered over the ranks by the kernel's epilogue into the ring's next point, whose index
 // is returned in *gather_slot; `wait_slot` >= 0 names the point of `ring` the activation came from (the kernel waits for it
 // itself).
+// `gated`: exactly two weights of one shape; the single result is activation(x w0 + b0) * (x w1 + b1), the gate multiply of
+// the gated MLP formed inside the launch (row counts that are multiples of 64 run the two linears and the product as
+// separate launches).
 std::vector<Tensor> linear_multi(const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
                                  const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot,
-                                 int *gather_slot);
+                                 int *gather_slot, bool gated = false);
 
 }  // namespace ttnn_b200

@@ -194,13 +194,13 @@ PYBIND11_MODULE(_ttnn, m) {
         .def("out_ptr", [](const GatherRing &r, int slot) { return reinterpret_cast<uint64_t>(r.out_ptr(slot)); });
     m.def("linear_multi",
           [](const Tensor &x, const std::vector<Tensor> &weights, const std::vector<std::optional<Tensor>> &biases,
-             const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot) {
+             const std::optional<std::string> &activation, GatherRing *ring, bool gather_first, int wait_slot, bool gated) {
               int slot = -1;
-              std::vector<Tensor> out = linear_multi(x, weights, biases, activation, ring, gather_first, wait_slot, &slot);
+              std::vector<Tensor> out = linear_multi(x, weights, biases, activation, ring, gather_first, wait_slot, &slot, gated);
               return py::make_tuple(out, slot);
           },
           py::arg("input_tensor"), py::arg("weights"), py::arg("biases"), py::arg("activation").none(true), py::arg("ring").none(true),
-          py::arg("gather_first") = false, py::arg("wait_slot") = -1);
+          py::arg("gather_first") = false, py::arg("wait_slot") = -1, py::arg("gated") = false);
     m.def("mul", &multiply, py::arg("input_tensor_a"), py::arg("input_tensor_b"));
     m.def("matmul", &matmul, py::arg("input_tensor_a"), py::arg("input_tensor_b"), py::kw_only(), py::arg("dtype") = std::nullopt,
           py::arg("program_config") = std::nullopt);

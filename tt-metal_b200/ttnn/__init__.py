@@ -22,7 +22,7 @@ from .operations.core import (from_torch, to_torch, to_layout, to_device, from_d
                               load_tensor, as_tensor, is_tensor_storage_on_device)
 from .operations.matmul import (matmul, linear, mul, MatmulProgramConfig, MatmulDefaultProgramConfig, MatmulMultiCoreReuseProgramConfig,
                                 MatmulMultiCoreReuseMultiCastProgramConfig, MatmulMultiCoreReuseMultiCast1DProgramConfig)
-from .operations.ccl import all_gather, linear_all_gather, linear_multi, wait_for_gather
+from .operations.ccl import all_gather, linear_all_gather, linear_gated, linear_multi, wait_for_gather
 
 Tensor.__matmul__ = lambda self, other: matmul(self, other)
 MultiDeviceTensor.__matmul__ = lambda self, other: matmul(self, other)

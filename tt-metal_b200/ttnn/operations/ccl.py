@@ -35,7 +35,7 @@ def _local(t):
     return t.local if isinstance(t, MultiDeviceTensor) else t
 
 
-def _fused_linear(input_tensor, weights, biases, activation, gather_first, ring_slots=8):
+def _fused_linear(input_tensor, weights, biases, activation, gather_first, ring_slots=8, gated=False):
     """One launch of ttb_matmul_multi through the host layer: up to four weights on one activation; optionally the first
     result is gathered over the mesh by the kernel's epilogue. Returns the list of results (MultiDeviceTensor when the
     input is one)."""
@@ -66,7 +66,7 @@ def _fused_linear(input_tensor, weights, biases, activation, gather_first, ring_
     native = ring.native if (ring is not None and (gather_first or wait_slot >= 0)) else None
     outs, slot = _ttnn.linear_multi(x, [_local(w) for w in weights],
                                     [(_local(b) if b is not None else None) for b in biases] if biases is not None else [],
-                                    activation, native, bool(gather_first and G > 1), wait_slot)
+                                    activation, native, bool(gather_first and G > 1), wait_slot, gated)
     results = []
     for j, t in enumerate(outs):
         if multi:
@@ -85,6 +85,16 @@ def linear_multi(input_tensor, weights, *, biases=None, activation=None, all_gat
     all_gather_first the first result is gathered along its last dimension over the mesh by the kernel's own epilogue
     (see linear_all_gather)."""
     return _fused_linear(input_tensor, weights, biases, activation, all_gather_first)
+
+
+def linear_gated(input_tensor, gate_weight, up_weight, *, gate_bias=None, up_bias=None, activation="silu", all_gather=False):
+    """activation(x @ gate_weight + gate_bias) * (x @ up_weight + up_bias) as ONE launch: both weights stream through one
+    persistent kernel and the product is formed where the second of a column tile's two halves is finished - the gated MLP's
+    silu(x w1) * (x w3) (models/demos/mistral7b/tt/mistral_mlp.py:51-73, models/demos/llama2_70b/tt/llama_mlp_optimized.py:165-197)
+    without the two intermediate tensors and the separate multiply. With `all_gather` the product is gathered over the mesh
+    by the same kernel (as linear_all_gather)."""
+    biases = [gate_bias, up_bias] if (gate_bias is not None or up_bias is not None) else None
+    return _fused_linear(input_tensor, [gate_weight, up_weight], biases, activation, all_gather, gated=True)[0]
 
 
 def linear_all_gather(input_tensor, weight, *, bias=None, activation=None, dim=-1, num_links=1, ring_slots=8):
