@@ -97,6 +97,11 @@ int32_t ttb_memset(void *dst_dev, int32_t value, size_t bytes, void *stream);
 int32_t ttb_stream_synchronize(void *stream);
 int32_t ttb_device_synchronize(void);
 
+/* NVTX range around whatever the caller brackets with the pair (the reference marks the same spots with Tracy zones,
+ * tt_metal/common/bfloat8.hpp:103,176; tt_metal/tools/profiler/op_profiler.hpp:290-312). No cost without a profiler attached. */
+int32_t ttb_nvtx_push(const char *name);
+int32_t ttb_nvtx_pop(void);
+
 /* Bytes of a buffer holding outer*Hp*Wp elements of `dtype` (Hp, Wp multiples of 32 for the
  * block-float types). Mirrors compute_buffer_size (tt_eager/tensor/tensor_utils.hpp:34-47). */
 int64_t ttb_buffer_bytes(int32_t dtype, int64_t outer, int64_t Hp, int64_t Wp);

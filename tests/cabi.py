@@ -36,6 +36,8 @@ _SIGS = {
     "ttb_memset": (_i32, [_vp, _i32, _sz, _vp]),
     "ttb_stream_synchronize": (_i32, [_vp]),
     "ttb_device_synchronize": (_i32, []),
+    "ttb_nvtx_push": (_i32, [ctypes.c_char_p]),
+    "ttb_nvtx_pop": (_i32, []),
     "ttb_buffer_bytes": (_i64, [_i32, _i64, _i64, _i64]),
     "ttb_tilize": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp]),
     "ttb_untilize": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp]),

@@ -1,6 +1,8 @@
 // C ABI: error reporting and the thin CUDA-runtime wrappers (device memory, copies, sync).
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges cost nothing unless a profiler injects its library
+
 #include "common.cuh"
 
 namespace ttb {
@@ -121,6 +123,16 @@ int32_t ttb_stream_synchronize(void *stream) {
 }
 int32_t ttb_device_synchronize(void) {
     TTB_CUDA_TRY(cudaDeviceSynchronize());
+    return TTB_OK;
+}
+
+// ---- NVTX ranges (timeline tools show them around the calls they bracket) ---------------------------------------
+int32_t ttb_nvtx_push(const char *name) {
+    nvtxRangePushA(name ? name : "ttb");
+    return TTB_OK;
+}
+int32_t ttb_nvtx_pop(void) {
+    nvtxRangePop();
     return TTB_OK;
 }
 

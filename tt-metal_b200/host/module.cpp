@@ -201,6 +201,8 @@ PYBIND11_MODULE(_ttnn, m) {
           },
           py::arg("input_tensor"), py::arg("weights"), py::arg("biases"), py::arg("activation").none(true), py::arg("ring").none(true),
           py::arg("gather_first") = false, py::arg("wait_slot") = -1, py::arg("gated") = false);
+    m.def("nvtx_push", [](const std::string &name) { ttb_nvtx_push(name.c_str()); });
+    m.def("nvtx_pop", []() { ttb_nvtx_pop(); });
     m.def("mul", &multiply, py::arg("input_tensor_a"), py::arg("input_tensor_b"));
     m.def("matmul", &matmul, py::arg("input_tensor_a"), py::arg("input_tensor_b"), py::kw_only(), py::arg("dtype") = std::nullopt,
           py::arg("program_config") = std::nullopt);
