@@ -305,13 +305,41 @@ int32_t ttb_matmul_peer(const void *a_dev, int32_t a_dtype, const void *w_dev, i
  * llama2_70b/tt/llama_mlp_optimized.py:165-193) - becomes one pass of one persistent kernel over all their tiles; the
  * weights stay separate tensors. Decode shapes only. `bias` may be NULL or hold NULL entries. `gather` (may be NULL)
  * applies to weight 0 only: its result goes to gather->out[...] on every rank and out[0] is ignored; `wait` as in
- * ttb_matmul_peer. Results are identical to `count` calls of ttb_matmul. */
+ * ttb_matmul_peer. Results agree with `count` calls of ttb_matmul up to the order in which fp32 partial sums are added. */
 int64_t ttb_matmul_multi_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int32_t count, const int64_t *N);
 int64_t ttb_matmul_gated_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N);
 int32_t ttb_matmul_multi(const void *a_dev, int32_t a_dtype, int32_t count, const void *const *w_dev, int32_t w_dtype,
                          const void *const *bias_dev, void *const *out_dev, int32_t out_dtype, int64_t batch, int64_t M,
                          int64_t K, const int64_t *N, int32_t activation, int32_t flags, void *workspace_dev,
                          int64_t workspace_bytes, const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream);
+/* Several ttb_matmul_multi calls as the stages of ONE launch. The persistent blocks walk the stages in order without
+ * meeting in between: the weight stream of stage s + 1 starts while stage s drains, and a stage whose activation is an
+ * earlier stage's output (`input_from`) or a gathered tensor (`wait`) holds back only its activation copies until that
+ * is complete. What the reference's decode MLP issues as matmul, matmul, multiply, matmul on one device
+ * (models/demos/llama2_70b/tt/llama_mlp_optimized.py:165-218, models/demos/mistral7b/tt/mistral_mlp.py:51-73) becomes
+ * two stages: the gated pair, then the down projection. Row counts that are odd multiples of 32 (one tile row per
+ * block); all weights of the launch in one block-float format. Results agree with the separate calls up to the order in
+ * which fp32 partial sums over K are added (and repeat exactly from launch to launch under TTB_MM_DETERMINISTIC). */
+typedef struct ttb_matmul_stage {
+    const void *a;                     /* activation [batch * M, K], bf16 (for input_from >= 0: that stage's out[0]) */
+    int32_t count;                     /* weights of the stage, 1..TTB_MAX_GROUP */
+    const void *w[TTB_MAX_GROUP];
+    const void *bias[TTB_MAX_GROUP];   /* entries may be NULL */
+    void *out[TTB_MAX_GROUP];
+    int32_t out_dtype;
+    int64_t K;
+    int64_t N[TTB_MAX_GROUP];
+    int32_t activation;
+    int32_t flags;                     /* TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_GATED */
+    const ttb_peer_gather *gather;     /* as in ttb_matmul_multi; may be NULL */
+    const ttb_peer_wait_t *wait;       /* as in ttb_matmul_multi; may be NULL */
+    int32_t input_from;                /* index of the earlier stage that writes `a`, or -1 */
+} ttb_matmul_stage;
+#define TTB_MAX_STAGES 4
+int64_t ttb_matmul_sequence_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, const ttb_matmul_stage *stages, int32_t count);
+/* `flags`: TTB_MM_WORKSPACE_ZEROED | TTB_MM_WEIGHTS_RESIDENT for the launch as a whole. */
+int32_t ttb_matmul_sequence(const ttb_matmul_stage *stages, int32_t count, int32_t a_dtype, int32_t w_dtype, int64_t batch, int64_t M,
+                            int32_t flags, void *workspace_dev, int64_t workspace_bytes, void *stream);
 /* The work decomposition ttb_matmul / ttb_matmul_multi use for a decode shape (no GPU needed). out[0..9] = rows per block,
  * tiles (128 columns x rows per block) in the launch, persistent blocks, K pieces per tile (1 = whole tiles round by round
  * plus a streamed remainder), K blocks (of 32) per piece, rounds of whole tiles / pieces, first tile of the streamed

@@ -62,6 +62,8 @@ _SIGS = {
     "ttb_matmul_gated_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64]),
     "ttb_matmul_multi_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i32, _vp]),
     "ttb_matmul_multi": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    "ttb_matmul_sequence_workspace_bytes": (_i64, [_i32, _i64, _i64, _vp, _i32]),
+    "ttb_matmul_sequence": (_i32, [_vp, _i32, _i32, _i32, _i64, _i64, _i32, _vp, _i64, _vp]),
     "ttb_comm_unique_id": (_i32, [_vp]),
     "ttb_comm_init": (_i32, [ctypes.POINTER(_vp), _i32, _i32, _vp, _i64]),
     "ttb_comm_check": (_i32, [_vp, _i64]),
@@ -85,6 +87,30 @@ class PeerGather(ctypes.Structure):
 class PeerWait(ctypes.Structure):
     """ttb_peer_wait_t of include/ttb.h."""
     _fields_ = [("arrived", _vp), ("expected", _vp)]
+
+
+MAX_GROUP, MAX_STAGES = 4, 4
+
+
+class MatmulStage(ctypes.Structure):
+    """ttb_matmul_stage of include/ttb.h."""
+    _fields_ = [("a", _vp), ("count", _i32), ("w", _vp * MAX_GROUP), ("bias", _vp * MAX_GROUP), ("out", _vp * MAX_GROUP),
+                ("out_dtype", _i32), ("K", _i64), ("N", _i64 * MAX_GROUP), ("activation", _i32), ("flags", _i32),
+                ("gather", ctypes.POINTER(PeerGather)), ("wait", ctypes.POINTER(PeerWait)), ("input_from", _i32)]
+
+
+def matmul_stage(a, ws, outs, K, Ns, biases=None, out_dtype=BFLOAT16, act=ACT_NONE, flags=0, gather=None, wait=None, input_from=-1):
+    """One stage from device addresses (ints); `gather` / `wait` are PeerGather / PeerWait objects the caller keeps alive."""
+    st = MatmulStage()
+    st.a, st.count, st.out_dtype, st.K, st.activation, st.flags, st.input_from = a, len(ws), out_dtype, K, act, flags, input_from
+    for j, w in enumerate(ws):
+        st.w[j], st.out[j], st.N[j] = w, outs[j], Ns[j]
+        st.bias[j] = biases[j] if biases else None
+    if gather is not None:
+        st.gather = ctypes.pointer(gather)
+    if wait is not None:
+        st.wait = ctypes.pointer(wait)
+    return st
 
 
 def peer_gather(rank, outs, arrived, uses):

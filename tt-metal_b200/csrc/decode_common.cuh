@@ -9,6 +9,7 @@
 namespace ttb {
 
 struct DecodeArgs;
+constexpr int kMaxSequenceStages = 4;   // stages (ttb_matmul_multi calls) one launch can hold
 // One tiled tensor map per weight of a launch: the packed weight seen as [K blocks][tiles per row][tile as 8-byte words], so
 // that a producer thread fetches the three stages of a group (three K blocks x four tiles) with ONE copy instruction.
 struct alignas(64) WeightMaps {
@@ -68,6 +69,9 @@ struct DecodeArgs {
     int gated;
     float *gate;
     int *gate_counters;
+    // ---- stages of one launch (matmul_decode_tmem.cu): the earlier stage whose output is this stage's activation (-1: none),
+    // and whether this stage counts its stored tiles for a later one ----
+    int depends_on, count_done;
     // ---- limit of the bounded waits in SM clocks (0 = the built-in defaults), set by ttb_set_wait_limit_cycles ----
     long long wait_limit;
 };
@@ -108,6 +112,44 @@ __device__ __forceinline__ bool peer_wait(const DecodeArgs &p, volatile int *abo
     const long long t0 = clock64();
     for (unsigned spin = 1;; ++spin) {
         if ((int)(ld_acquire_sys(p.wait_arrived) - expected) >= 0) return true;
+        if ((spin & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > limit_cycles) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, code);
+                return false;
+            }
+        }
+        __nanosleep(64);
+    }
+}
+
+// The same against a total the caller computed (stages of one launch: what the gather point had been told to expect before
+// the launch plus the shares of the launch's own earlier stages).
+__device__ __forceinline__ bool peer_wait_for(const DecodeArgs &p, unsigned expected, volatile int *abort_flag, int code) {
+    const long long limit_cycles = peer_wait_limit(p);
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+        if ((int)(ld_acquire_sys(p.wait_arrived) - expected) >= 0) return true;
+        if ((spin & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > limit_cycles) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, code);
+                return false;
+            }
+        }
+        __nanosleep(64);
+    }
+}
+// Bounded wait until a counter of this GPU (tiles an earlier stage of the launch has stored) reaches `target`.
+__device__ __forceinline__ bool count_wait(const int *counter, int target, const DecodeArgs &p, volatile int *abort_flag, int code) {
+    const long long limit_cycles = peer_wait_limit(p);
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) return true;
         if ((spin & 15u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > limit_cycles) {

@@ -21,7 +21,11 @@ static constexpr int64_t kCounterBytes = 65536;
 // partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
 static constexpr int64_t kAccumBytes = 16 << 20;
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream);
+int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream);
+// The tail of the counter region belongs to the launch as a whole (matmul_decode_tmem.cu: blocks that have finished, tiles
+// each stage has stored); the per-tile counters stay below it.
+static constexpr int kSyncInts = 16;
+static constexpr int kSyncInt0 = (int)(65536 / 4) - kSyncInts;
 
 // Device address of the status word on the current device (looked up once per device).
 int32_t status_word_address(int **out) {
@@ -43,7 +47,7 @@ static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : 
 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) * 4 <= kCounterBytes;
+           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) <= kSyncInt0;
 }
 
 // ---- streamed decomposition (matmul_decode_stream.cu) ----------------------------------------------------------------
@@ -129,7 +133,7 @@ bool decode_supported_multi(int w_dtype, int64_t rows, int64_t K, int nprob, con
         if (N[j] <= 0 || N[j] % BN) return false;
         tiles += N[j] / BN;
     }
-    return tiles * (rows / 32) * 4 <= kCounterBytes;
+    return tiles * (rows / 32) <= kSyncInt0;
 }
 
 // Accumulate mode needs rows * (sum of N) fp32 inside the fixed 16 MiB region; larger outputs use ordered mode.
@@ -154,11 +158,16 @@ int64_t decode_workspace_bytes_compact(int64_t rows, int64_t K, int64_t N) { ret
 
 int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes_multi(rows, K, 1, &N, false); }
 
-int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *w, int w_dtype, const void *const *bias, void *const *out,
-                                   int out_dtype, int64_t rows, int64_t K, const int64_t *N, int act, int flags, void *workspace,
-                                   int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream,
-                                   const ttb_peer_gather *gather, const ttb_peer_wait_t *wait) {
-    DecodeArgs p = {};
+// Fills the launch arguments of one ttb_matmul_multi-shaped piece of work. `zero_bytes`: how much of the head of the
+// workspace must be zero before the launch (the caller clears it unless it is known to be).
+static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_bytes, const void *a, int nprob, const void *const *w, int w_dtype,
+                                   const void *const *bias, void *const *out, int out_dtype, int64_t rows, int64_t K, const int64_t *N, int act,
+                                   int flags, void *workspace, int64_t workspace_bytes, bool compact, const ttb_peer_gather *gather,
+                                   const ttb_peer_wait_t *wait) {
+    (void)w_dtype;
+    p = DecodeArgs{};
+    p.depends_on = -1;
+    zero_bytes = 0;
     p.a = (const uint16_t *)a;
     p.K = K; p.Kt = (int)(K / 32); p.nkb = (int)(K / BK);
     p.act = act; p.out_dtype = out_dtype;
@@ -166,7 +175,6 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
     p.out_row_major = (flags & TTB_MM_OUT_ROW_MAJOR) != 0;
     if (int32_t rc = status_word_address(&p.status)) return rc;
     p.wait_limit = g_wait_limit_cycles;
-    bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
     if (wait) {
         p.wait_arrived = wait->arrived; p.wait_expected = wait->expected;
     }
@@ -196,7 +204,7 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
         if (nprob != 2 || N[0] != N[1]) return fail(TTB_E_INVALID, "ttb_matmul_multi: a gated launch takes two weights of one shape");
         if (nb != 32 || compact || (flags & TTB_MM_DECODE_SMEM_OPERAND))
             return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: the gated form serves row counts that are odd multiples of 32 (32, 96, 160, 224)");
-        if ((int64_t)(sp.tiles_total + sp.tiles_total / 2) * 4 > kCounterBytes) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: too many tiles for a gated launch");
+        if (sp.tiles_total + sp.tiles_total / 2 > kSyncInt0) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: too many tiles for a gated launch");
         p.gated = 1;
     }
     if (gather) {
@@ -223,17 +231,86 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
             p.gate = (float *)((uint8_t *)workspace + kCounterBytes + kAccumBytes + stream_partial_bytes(sp));
             p.gate_counters = p.counters + sp.tiles_total;
         }
-        if (!counters_are_zero) {
-            // counters always; in accumulate mode also the tiles this launch adds into
-            const int64_t zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * nsum * 4);
-            TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
-            overlap = false;   // only kernels may separate a launch from the one it overlaps with
-        }
+        // counters always; in accumulate mode also the tiles this launch adds into
+        zero_bytes = kCounterBytes + (p.ordered ? 0 : rows * nsum * 4);
+    }
+    nb_out = nb;
+    return TTB_OK;
+}
+
+int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *w, int w_dtype, const void *const *bias, void *const *out,
+                                   int out_dtype, int64_t rows, int64_t K, const int64_t *N, int act, int flags, void *workspace,
+                                   int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream,
+                                   const ttb_peer_gather *gather, const ttb_peer_wait_t *wait) {
+    DecodeArgs p;
+    int nb = 0;
+    int64_t zero_bytes = 0;
+    if (int32_t rc = prepare_decode_args(p, nb, zero_bytes, a, nprob, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace,
+                                         workspace_bytes, compact, gather, wait))
+        return rc;
+    bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
+    if (zero_bytes > 0 && !counters_are_zero) {
+        TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
+        overlap = false;   // only kernels may separate a launch from the one it overlaps with
     }
     // the weights of 32-row blocks reach the MMA through tensor memory; those of larger row blocks (and of any on request)
     // through shared memory
-    if (nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND)) return launch_decode_tmem(p, w_dtype, nb, overlap, stream);
+    if (nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND))
+        return launch_decode_tmem(&p, 1, w_dtype, p.counters ? p.counters + kSyncInt0 : nullptr, overlap, stream);
     return launch_decode_stream(p, w_dtype, nb, overlap, stream);
+}
+
+// Several ttb_matmul_multi-shaped stages in one launch of the tensor-memory kernel. The workspace is cut into one slice per
+// stage (blocks can be in different stages at the same time); the first slice's counter region also carries the launch's
+// own counters.
+int64_t decode_sequence_workspace_bytes(int64_t rows, int count, const ttb_matmul_stage *st) {
+    int64_t total = kCounterBytes;   // the launch's counters (and nothing else, so that a stage without scratch needs none)
+    for (int s = 0; s < count; ++s) {
+        const bool gated = (st[s].flags & TTB_MM_GATED) != 0;
+        total += (decode_workspace_bytes_multi(rows, st[s].K, st[s].count, st[s].N, false, gated) + 255) & ~int64_t(255);
+    }
+    return total;
+}
+
+int32_t launch_matmul_decode_sequence(const ttb_matmul_stage *st, int count, int w_dtype, int64_t rows, int flags, void *workspace,
+                                      int64_t workspace_bytes, cudaStream_t stream) {
+    if (count < 1 || count > kMaxSequenceStages) return fail(TTB_E_INVALID, "ttb_matmul_sequence: 1..%d stages, got %d", kMaxSequenceStages, count);
+    if (decode_rows_per_block(rows) != 32)
+        return fail(TTB_E_UNSUPPORTED, "ttb_matmul_sequence: serves row counts that are odd multiples of 32 (32, 96, 160, 224)");
+    const int64_t need = decode_sequence_workspace_bytes(rows, count, st);
+    if (!workspace || workspace_bytes < need)
+        return fail(TTB_E_WORKSPACE, "ttb_matmul_sequence: needs %lld bytes of workspace, got %lld", (long long)need, (long long)workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return fail(TTB_E_INVALID, "ttb_matmul_sequence: workspace must be 256-byte aligned");
+    // Blocks of a later stage wait for blocks of an earlier one: every block of the launch must get an SM of its own.
+    int dev = 0, sms = 0;
+    TTB_CUDA_TRY(cudaGetDevice(&dev));
+    TTB_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    static DecodeArgs args[kMaxSequenceStages];
+    const bool zeroed = (flags & TTB_MM_WORKSPACE_ZEROED) != 0;
+    bool overlap = (flags & TTB_MM_WEIGHTS_RESIDENT) != 0;
+    if (!zeroed) {
+        TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)kCounterBytes, stream));
+        overlap = false;
+    }
+    uint8_t *ws = (uint8_t *)workspace + kCounterBytes;
+    for (int s = 0; s < count; ++s) {
+        const ttb_matmul_stage &g = st[s];
+        const int sflags = g.flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_GATED);
+        const int64_t slice = (decode_workspace_bytes_multi(rows, g.K, g.count, g.N, false, (sflags & TTB_MM_GATED) != 0) + 255) & ~int64_t(255);
+        int nb = 0;
+        int64_t zero_bytes = 0;
+        if (int32_t rc = prepare_decode_args(args[s], nb, zero_bytes, g.a, g.count, g.w, w_dtype, g.bias, g.out, g.out_dtype, rows, g.K, g.N,
+                                             g.activation, sflags, slice ? ws : nullptr, slice, /*compact=*/false, g.gather, g.wait))
+            return rc;
+        if (args[s].sk_grid > sms)
+            return fail(TTB_E_UNSUPPORTED, "ttb_matmul_sequence: the plan uses %d blocks, the device has %d multiprocessors", args[s].sk_grid, sms);
+        if (g.input_from >= s || g.input_from < -1) return fail(TTB_E_INVALID, "ttb_matmul_sequence: stage %d: input_from must name an earlier stage or be -1", s);
+        args[s].depends_on = g.input_from;
+        if (g.input_from >= 0) args[g.input_from].count_done = 1;
+        if (zero_bytes > 0 && !zeroed) TTB_CUDA_TRY(cudaMemsetAsync(ws, 0, (size_t)zero_bytes, stream));
+        ws += slice;
+    }
+    return launch_decode_tmem(args, count, w_dtype, (int *)workspace, overlap, stream);
 }
 
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
@@ -385,43 +462,85 @@ extern "C" int64_t ttb_matmul_gated_workspace_bytes(int32_t w_dtype, int64_t bat
     return decode_workspace_bytes_multi(batch * M, K, 2, Ns, false, true);
 }
 
+namespace ttb {
+// Argument checks shared by ttb_matmul_multi and the stages of ttb_matmul_sequence.
+static int32_t validate_multi(const char *who, const void *a, int32_t a_dtype, int32_t count, const void *const *w, int32_t w_dtype,
+                              void *const *out, int32_t out_dtype, int64_t rows, int64_t K, const int64_t *N, int32_t act, int32_t flags,
+                              const ttb_peer_gather *gather, const ttb_peer_wait_t *wait) {
+    if (!a || !w || !out || !N) return fail(TTB_E_INVALID, "%s: null pointer", who);
+    if (count < 1 || count > TTB_MAX_GROUP) return fail(TTB_E_INVALID, "%s: count must be 1..%d", who, TTB_MAX_GROUP);
+    if (a_dtype != TTB_BFLOAT16) return fail(TTB_E_UNSUPPORTED, "%s: activations must be bfloat16", who);
+    if (out_dtype != TTB_BFLOAT16 && out_dtype != TTB_FLOAT32) return fail(TTB_E_UNSUPPORTED, "%s: output must be bfloat16 or float32", who);
+    if (rows <= 0 || K <= 0 || rows % 32 || K % 32) return fail(TTB_E_INVALID, "%s: batch, M, K must be positive and M, K multiples of 32", who);
+    if (act < TTB_ACT_NONE || act > TTB_ACT_SILU) return fail(TTB_E_INVALID, "%s: unknown activation %d", who, act);
+    for (int j = 0; j < count; ++j) {
+        if (!w[j] || (!out[j] && !(gather && j == 0) && !((flags & TTB_MM_GATED) && j == 1)))
+            return fail(TTB_E_INVALID, "%s: null tensor pointer for weight %d", who, j);
+        if (N[j] <= 0 || N[j] % 32) return fail(TTB_E_INVALID, "%s: N[%d] must be a positive multiple of 32", who, j);
+        if ((reinterpret_cast<uintptr_t>(w[j]) | reinterpret_cast<uintptr_t>(out[j])) & 15)
+            return fail(TTB_E_INVALID, "%s: tensors must be 16-byte aligned", who);
+    }
+    if (!decode_supported_multi(w_dtype, rows, K, count, N))
+        return fail(TTB_E_UNSUPPORTED, "%s: decode shapes only (bfloat8_b / bfloat4_b weights, at most 256 rows, every N a multiple of 128)", who);
+    if (gather) {
+        if (gather->ranks < 2 || gather->ranks > TTB_MAX_RANKS || gather->rank < 0 || gather->rank >= gather->ranks)
+            return fail(TTB_E_INVALID, "%s: ranks must be 2..%d and rank inside it", who, TTB_MAX_RANKS);
+        if (out_dtype != TTB_BFLOAT16 || (flags & TTB_MM_OUT_ROW_MAJOR)) return fail(TTB_E_UNSUPPORTED, "%s: the gathered output is bfloat16 in tile layout", who);
+        if (!gather->expected) return fail(TTB_E_INVALID, "%s: null expected-arrivals counter", who);
+        for (int r = 0; r < gather->ranks; ++r)
+            if (!gather->out[r] || !gather->arrived[r] || (reinterpret_cast<uintptr_t>(gather->out[r]) & 15))
+                return fail(TTB_E_INVALID, "%s: null or misaligned peer pointer for rank %d", who, r);
+    }
+    if (wait && (!wait->arrived || !wait->expected)) return fail(TTB_E_INVALID, "%s: incomplete wait description", who);
+    return TTB_OK;
+}
+}  // namespace ttb
+
 extern "C" int32_t ttb_matmul_multi(const void *a, int32_t a_dtype, int32_t count, const void *const *w, int32_t w_dtype,
                                     const void *const *bias, void *const *out, int32_t out_dtype, int64_t batch, int64_t M, int64_t K,
                                     const int64_t *N, int32_t act, int32_t flags, void *workspace, int64_t workspace_bytes,
                                     const ttb_peer_gather *gather, const ttb_peer_wait_t *wait, void *stream) {
     using namespace ttb;
-    if (!a || !w || !out || !N) return fail(TTB_E_INVALID, "ttb_matmul_multi: null pointer");
-    if (count < 1 || count > TTB_MAX_GROUP) return fail(TTB_E_INVALID, "ttb_matmul_multi: count must be 1..%d", TTB_MAX_GROUP);
-    if (a_dtype != TTB_BFLOAT16) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: activations must be bfloat16");
-    if (out_dtype != TTB_BFLOAT16 && out_dtype != TTB_FLOAT32) return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: output must be bfloat16 or float32");
-    if (batch <= 0 || M <= 0 || K <= 0 || M % 32 || K % 32) return fail(TTB_E_INVALID, "ttb_matmul_multi: batch, M, K must be positive and M, K multiples of 32");
-    if (act < TTB_ACT_NONE || act > TTB_ACT_SILU) return fail(TTB_E_INVALID, "ttb_matmul_multi: unknown activation %d", act);
-    for (int j = 0; j < count; ++j) {
-        if (!w[j] || (!out[j] && !(gather && j == 0) && !((flags & TTB_MM_GATED) && j == 1)))
-            return fail(TTB_E_INVALID, "ttb_matmul_multi: null tensor pointer for weight %d", j);
-        if (N[j] <= 0 || N[j] % 32) return fail(TTB_E_INVALID, "ttb_matmul_multi: N[%d] must be a positive multiple of 32", j);
-        if ((reinterpret_cast<uintptr_t>(w[j]) | reinterpret_cast<uintptr_t>(out[j])) & 15)
-            return fail(TTB_E_INVALID, "ttb_matmul_multi: tensors must be 16-byte aligned");
-    }
+    if (batch <= 0 || M <= 0 || M % 32) return fail(TTB_E_INVALID, "ttb_matmul_multi: batch, M, K must be positive and M, K multiples of 32");
     const int64_t rows = batch * M;
-    if (!decode_supported_multi(w_dtype, rows, K, count, N))
-        return fail(TTB_E_UNSUPPORTED,
-                    "ttb_matmul_multi: decode shapes only (bfloat8_b / bfloat4_b weights, at most 256 rows, every N a multiple of 128)");
-    if (gather) {
-        if (gather->ranks < 2 || gather->ranks > TTB_MAX_RANKS || gather->rank < 0 || gather->rank >= gather->ranks)
-            return fail(TTB_E_INVALID, "ttb_matmul_multi: ranks must be 2..%d and rank inside it", TTB_MAX_RANKS);
-        if (out_dtype != TTB_BFLOAT16 || (flags & TTB_MM_OUT_ROW_MAJOR))
-            return fail(TTB_E_UNSUPPORTED, "ttb_matmul_multi: the gathered output is bfloat16 in tile layout");
-        if (!gather->expected) return fail(TTB_E_INVALID, "ttb_matmul_multi: null expected-arrivals counter");
-        for (int r = 0; r < gather->ranks; ++r)
-            if (!gather->out[r] || !gather->arrived[r] || (reinterpret_cast<uintptr_t>(gather->out[r]) & 15))
-                return fail(TTB_E_INVALID, "ttb_matmul_multi: null or misaligned peer pointer for rank %d", r);
-    }
-    if (wait && (!wait->arrived || !wait->expected)) return fail(TTB_E_INVALID, "ttb_matmul_multi: incomplete wait description");
+    if (int32_t rc = validate_multi("ttb_matmul_multi", a, a_dtype, count, w, w_dtype, out, out_dtype, rows, K, N, act, flags, gather, wait)) return rc;
     return launch_matmul_decode_multi(a, count, w, w_dtype, bias, out, out_dtype, rows, K, N, act,
                                       flags & (TTB_MM_A_ROW_MAJOR | TTB_MM_OUT_ROW_MAJOR | TTB_MM_DETERMINISTIC | TTB_MM_WEIGHTS_RESIDENT | TTB_MM_DECODE_SMEM_OPERAND | TTB_MM_GATED),
                                       workspace, workspace_bytes, (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false,
                                       (cudaStream_t)stream, gather, wait);
+}
+
+// ---- several such launches as the stages of one --------------------------------------------------------------------------
+extern "C" int64_t ttb_matmul_sequence_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, const ttb_matmul_stage *stages, int32_t count) {
+    using namespace ttb;
+    if (!stages || count < 1 || count > kMaxSequenceStages || batch <= 0 || M <= 0) return 0;
+    for (int s = 0; s < count; ++s)
+        if (!decode_supported_multi(w_dtype, batch * M, stages[s].K, stages[s].count, stages[s].N)) return 0;
+    return decode_sequence_workspace_bytes(batch * M, count, stages);
+}
+
+extern "C" int32_t ttb_matmul_sequence(const ttb_matmul_stage *stages, int32_t count, int32_t a_dtype, int32_t w_dtype, int64_t batch, int64_t M,
+                                       int32_t flags, void *workspace, int64_t workspace_bytes, void *stream) {
+    using namespace ttb;
+    if (!stages) return fail(TTB_E_INVALID, "ttb_matmul_sequence: null stage list");
+    if (count < 1 || count > kMaxSequenceStages) return fail(TTB_E_INVALID, "ttb_matmul_sequence: 1..%d stages, got %d", kMaxSequenceStages, count);
+    if (batch <= 0 || M <= 0 || M % 32) return fail(TTB_E_INVALID, "ttb_matmul_sequence: batch and M must be positive and M a multiple of 32");
+    const int64_t rows = batch * M;
+    for (int s = 0; s < count; ++s) {
+        const ttb_matmul_stage &g = stages[s];
+        if (int32_t rc = validate_multi("ttb_matmul_sequence", g.a, a_dtype, g.count, g.w, w_dtype, g.out, g.out_dtype, rows, g.K, g.N, g.activation,
+                                        g.flags, g.gather, g.wait))
+            return rc;
+        if (g.input_from >= 0) {
+            if (g.input_from >= s) return fail(TTB_E_INVALID, "ttb_matmul_sequence: stage %d: input_from must name an earlier stage", s);
+            const ttb_matmul_stage &f = stages[g.input_from];
+            if (f.out_dtype != TTB_BFLOAT16 || ((f.flags & TTB_MM_OUT_ROW_MAJOR) != 0) != ((g.flags & TTB_MM_A_ROW_MAJOR) != 0))
+                return fail(TTB_E_INVALID, "ttb_matmul_sequence: stage %d reads stage %d's output, which must be bfloat16 in the layout stage %d expects", s,
+                            g.input_from, s);
+        }
+    }
+    return launch_matmul_decode_sequence(stages, count, w_dtype, rows, flags & (TTB_MM_WORKSPACE_ZEROED | TTB_MM_WEIGHTS_RESIDENT), workspace,
+                                         workspace_bytes, (cudaStream_t)stream);
 }
 
 namespace {

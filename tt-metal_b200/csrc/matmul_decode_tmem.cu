@@ -66,8 +66,8 @@ struct Layout {
     static constexpr int b = pk + kRing * kGroup * kStageBytes;    // (a multiple of 256: the swizzled operand needs it)
     static constexpr int stage = b + kRing * kGroup * kBStageBytes;   // [NB x 128] bf16 tiled slab for the gather epilogue
     static constexpr int bars = stage + NB * BN * 2;
-    // full_pk[kRing], full_a[kRing], empty[kRing / 2] (per pair of groups), acc_full[2], acc_empty[2]
-    static constexpr int nbars = 3 * kRing + 4;
+    // full_w[kRing], full_b[kRing], full_a[kRing], empty[kRing / 2] (per pair of groups), acc_full[2], acc_empty[2]
+    static constexpr int nbars = 4 * kRing + 4;
     static constexpr int misc = bars + 8 * nbars;                  // tmem base, abort flag, last-block flag, two accumulator-ready flags
     static constexpr int total = misc + 32;
     // Issuing costs a thread ~46 cycles per MMA and ~300 per commit, whatever the MMA's size. Two issuing threads take
@@ -100,9 +100,14 @@ __device__ __forceinline__ int block_of_unit(const DecodeArgs &p, int u) {
 struct SegIter {
     int w, u, u_end;
     __device__ __forceinline__ void start(const DecodeArgs &p, int block) {
-        w = 0;
-        u = unit_begin(p, block);
-        u_end = unit_begin(p, block + 1);
+        if (block < p.sk_grid) {
+            w = 0;
+            u = unit_begin(p, block);
+            u_end = unit_begin(p, block + 1);
+        } else {   // a stage planned for fewer blocks than the launch has
+            w = p.sk_waves;
+            u = u_end = 0;
+        }
     }
     __device__ __forceinline__ bool next(const DecodeArgs &p, int block, Seg &s) {
         while (w < p.sk_waves) {
@@ -137,6 +142,38 @@ struct SegIter {
         s.slot = rt + block;
         u = e;
         return true;
+    }
+};
+
+// A launch runs a sequence of stages, each what one ttb_matmul_multi call describes. The persistent blocks walk the stages
+// one after the other without meeting in between: the weight stream, the expansion and the MMAs continue across stage
+// borders, and a stage that consumes what an earlier one produced (or what the ranks gathered) holds only its activation
+// copies until that is complete.
+template <int S>
+struct alignas(64) Sequence {
+    int n, grid;
+    int *sync;    // zero between launches: [0] blocks that have finished the launch, [1 + s] tiles of stage s stored (if counted)
+    DecodeArgs st[S];
+    WeightMaps maps[S];
+    ActMap amap[S];
+};
+
+// A block's segments over all stages, in order.
+template <int S>
+struct WorkIter {
+    int si;
+    SegIter it;
+    __device__ __forceinline__ void start(const Sequence<S> &q, int block) {
+        si = 0;
+        it.start(q.st[0], block);
+    }
+    __device__ __forceinline__ bool next(const Sequence<S> &q, int block, Seg &s) {
+        while (true) {
+            if (it.next(q.st[S == 1 ? 0 : si], block, s)) return true;
+            if (S == 1 || si + 1 >= q.n) return false;
+            ++si;
+            it.start(q.st[si], block);
+        }
     }
 };
 
@@ -277,7 +314,7 @@ constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks e
 // Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
 // that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
 template <int FMT>
-__device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, const int g0, bool ok) {
+__device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, const int g0, bool ok, int *done_counter) {
     using L = Layout<FMT>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tid = threadIdx.x - 32 * kEpiWarp0;
@@ -467,6 +504,12 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");   // (last_flag is reused below)
     }
+    if (done_counter) {
+        // a later stage of this launch reads this stage's output: count the tile once it is stored
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0 && send && (eok || contributors > 1)) atomicAdd(done_counter, 1);
+    }
     if (gathered) {
         // one decision for the four warps, so that all of them take part in gather_send's barriers
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -477,29 +520,37 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     return eok;
 }
 
-template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const __grid_constant__ DecodeArgs p, const __grid_constant__ WeightMaps maps, const __grid_constant__ ActMap amap) {
+template <int FMT, int S>
+__global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const __grid_constant__ Sequence<S> q) {
     using L = Layout<FMT>;
     constexpr int kRing = L::kRing;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::bars;
-    auto full_pk = [&](int s) { return bar0 + 8u * s; };                 // packed tiles and activations of the group have landed
-    auto full_a = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's weights are expanded in tensor memory
-    auto empty = [&](int s) { return bar0 + 8u * (2 * kRing + (s >> 1)); };   // the MMAs of the pair of groups {s & ~1, s | 1} are complete: both slots are free
-    const uint32_t acc_full0 = bar0 + 8u * (3 * kRing), acc_empty0 = acc_full0 + 16u;
+    auto full_w = [&](int s) { return bar0 + 8u * s; };                   // the group's packed tiles have landed
+    auto full_b = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's activations have landed
+    auto full_a = [&](int s) { return bar0 + 8u * (2 * kRing + s); };     // the group's weights are expanded in tensor memory
+    auto empty = [&](int s) { return bar0 + 8u * (3 * kRing + (s >> 1)); };   // the MMAs of the pair of groups {s & ~1, s | 1} are complete: both slots are free
+    const uint32_t acc_full0 = bar0 + 8u * (4 * kRing), acc_empty0 = acc_full0 + 16u;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
     volatile int *last_flag = reinterpret_cast<volatile int *>(smem + L::misc + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = (int)blockIdx.x;
-    const long long lim = barrier_wait_limit(p);
+    const DecodeArgs &p0 = q.st[0];
+    // (the waits inside the block outlast the wait for other GPUs that some stage of the launch may sit in)
+    bool waits_for_peers = false;
+#pragma unroll
+    for (int s = 0; s < S; ++s) waits_for_peers = waits_for_peers || (s < q.n && q.st[s].wait_arrived != nullptr);
+    const long long lim = p0.wait_limit > 0 ? 2 * p0.wait_limit + 1000000LL : waits_for_peers ? 25000000000LL : 2000000000LL;
+    int *const status = p0.status;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kRing; ++s) {
-            mbar_init(full_pk(s), 2);     // the two producer threads, each with its byte count
+            mbar_init(full_w(s), 1);      // the weight producer, with its byte count
+            mbar_init(full_b(s), 1);      // the activation producer, with its byte count
             mbar_init(full_a(s), 4);      // the four expand warps of the group's team
             if ((s & 1) == 0) mbar_init(empty(s), 1);   // the commit of the issuer that owns the pair
         }
@@ -525,25 +576,26 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     grid_dep_launch();
 
     if (warp == kProducerWarp) {
-        // ---------------- packed weight tiles -> shared-memory ring, across segment borders ----------------
+        // ---------------- packed weight tiles -> shared-memory ring, across segment and stage borders ----------------
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
             int gs = 0, tlg = 0;
             (void)tlg;
             uint32_t ph = 0;
-            SegIter it;
-            it.start(p, block);
+            WorkIter<S> it;
+            it.start(q, block);
             Seg s;
-            while (ok && it.next(p, block, s)) {
+            while (ok && it.next(q, block, s)) {
+                const DecodeArgs &p = q.st[S == 1 ? 0 : it.si];
                 const TileRef tr = tile_ref(p, s.tile);
-                const void *map = &maps.m[tr.prob];
+                const void *map = &q.maps[S == 1 ? 0 : it.si].m[tr.prob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 11, lim)) { ok = false; break; }
+                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, status, 11, lim)) { ok = false; break; }
                     TL(0, tlg); ++tlg;
                     // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
                     // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
-                    mbar_arrive_expect_tx(full_pk(gs), kGroup * L::kStageBytes);
-                    tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
+                    mbar_arrive_expect_tx(full_w(gs), kGroup * L::kStageBytes);
+                    tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_w(gs), policy);
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
             }
@@ -551,28 +603,51 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     } else if (warp == kLoaderWarp) {
         // ---------------- activations -> shared memory, one tensor-map copy per group ----------------
         if (lane == 0) {
-            grid_dep_wait();   // the activations are the previous kernel's output
-            if (p.wait_arrived) {
-                if (!peer_wait(p, abort_flag, 6)) ok = false;
-                fence_proxy_async_global();   // what the peers stored, seen by the acquire above, is read by the copy unit next
-            }
-            int gs = 0, tlg = 0;
+            grid_dep_wait();   // the activations are earlier kernels' output
+            // What the gather points this launch waits for had been told to expect before the launch (the totals are only
+            // brought up to date by the last block to finish); stages of this launch that gather into a point add their share.
+            unsigned e0[S];
+#pragma unroll
+            for (int s = 0; s < S; ++s) e0[s] = (s < q.n && q.st[s].wait_arrived) ? *reinterpret_cast<const volatile unsigned *>(q.st[s].wait_expected) : 0u;
+            int gs = 0, tlg = 0, ready_stage = -1;
             (void)tlg;
             uint32_t ph = 0;
-            SegIter it;
-            it.start(p, block);
+            WorkIter<S> it;
+            it.start(q, block);
             Seg s;
-            while (ok && it.next(p, block, s)) {
+            while (ok && it.next(q, block, s)) {
+                const DecodeArgs &p = q.st[S == 1 ? 0 : it.si];
+                if (it.si != ready_stage) {
+                    // first segment of a stage: hold the copies until the stage's activation is complete
+                    ready_stage = it.si;
+                    bool waited = false;
+                    if (p.wait_arrived) {
+                        unsigned target = 0;
+#pragma unroll
+                        for (int j = 0; j < S; ++j) {
+                            if (j == it.si) target += e0[j];
+                            if (j < it.si && q.st[j].ranks > 1 && q.st[j].expected == p.wait_expected) target += q.st[j].launch_arrivals;
+                        }
+                        if (!peer_wait_for(p, target, abort_flag, 6)) { ok = false; break; }
+                        waited = true;
+                    }
+                    if (S > 1 && p.depends_on >= 0) {
+                        if (!count_wait(q.sync + 1 + p.depends_on, q.st[p.depends_on].sk_tiles / (q.st[p.depends_on].gated ? 2 : 1), p, abort_flag, 8)) { ok = false; break; }
+                        waited = true;
+                    }
+                    if (waited) fence_proxy_async_global();   // what was stored before the signal is read by the copy unit next
+                }
                 const int rchunk = s.tile / p.tstart[p.nprob];
+                const void *amap = &q.amap[S == 1 ? 0 : it.si].m;
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, p.status, 17, lim)) { ok = false; break; }
+                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, status, 17, lim)) { ok = false; break; }
                     TL(4, tlg); ++tlg;
-                    mbar_arrive_expect_tx(full_pk(gs), kGroup * L::kBStageBytes);
+                    mbar_arrive_expect_tx(full_b(gs), kGroup * L::kBStageBytes);
                     const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
                     if (p.a_row_major)
-                        tma_load_3d_plain(dst, &amap.m, 0, rchunk * NB, (s.kb0 + i0) * 2, full_pk(gs));
+                        tma_load_3d_plain(dst, amap, 0, rchunk * NB, (s.kb0 + i0) * 2, full_b(gs));
                     else
-                        tma_load_5d(dst, &amap.m, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_pk(gs));
+                        tma_load_5d(dst, amap, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_b(gs));
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
             }
@@ -590,12 +665,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             int gs = 0, seg_idx = 0, tlg = 0;
             (void)tlg;
             uint32_t ph = 0;
-            SegIter it;
-            it.start(p, block);
+            WorkIter<S> it;
+            it.start(q, block);
             Seg s;
-            for (; ok && it.next(p, block, s); ++seg_idx) {
+            for (; ok && it.next(q, block, s); ++seg_idx) {
                 const int buf = seg_idx & 1;
-                if (!mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, p.status, 16, lim)) { ok = false; break; }
+                if (!mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, status, 16, lim)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + h) * NB);
                 bool fresh = true;   // this issuer's accumulator holds nothing of this segment yet
@@ -603,9 +678,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                     if (((gs >> 1) & 1) == h) {
                         const int r = min(kGroup, s.nit - i0);
                         if (h == 0) { TL(1, tlg); }
-                        // expanded weights; the activations of the group landed before its expansion could start, and waiting
-                        // on their barrier here (complete by now) makes them visible to this thread's MMAs
-                        if (!mbar_wait(full_a(gs), ph, abort_flag, p.status, 12, lim) || !mbar_wait(full_pk(gs), ph, abort_flag, p.status, 18, lim)) { ok = false; break; }
+                        if (!mbar_wait(full_a(gs), ph, abort_flag, status, 12, lim) || !mbar_wait(full_b(gs), ph, abort_flag, status, 18, lim)) { ok = false; break; }
                         if (h == 0) { TL(2, tlg); }
                         tc_fence_after_sync();
                         const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
@@ -627,18 +700,19 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 // (an issuer that had no group in this segment still commits: its arrival is part of the barrier's count)
                 if (ok) mma_commit(acc_full0 + 8u * buf);
             }
+            // An odd number of groups leaves the last pair's commit unsent: nothing waits for it any more.
         }
     } else if (warp >= kEpiWarp0) {
         // ---------------- epilogue warps ----------------
         grid_dep_wait();   // the epilogues touch scratch and outputs
-        if (p.ranks > 1 && blockIdx.x == 0 && warp == kEpiWarp0 && lane == 0) *p.expected = *p.expected + p.launch_arrivals;
         const EpiCtx ectx = {smem, tmem_base, acc_full0, acc_empty0, abort_flag, last_flag, lim};
         int seg_idx = 0, g0 = 0;
-        SegIter it;
-        it.start(p, block);
+        WorkIter<S> it;
+        it.start(q, block);
         Seg s;
-        for (; it.next(p, block, s); ++seg_idx) {
-            ok = epilogue<FMT>(p, ectx, s, seg_idx, g0, ok);
+        for (; it.next(q, block, s); ++seg_idx) {
+            const DecodeArgs &p = q.st[S == 1 ? 0 : it.si];
+            ok = epilogue<FMT>(p, ectx, s, seg_idx, g0, ok, (S > 1 && p.count_done) ? q.sync + 1 + it.si : nullptr);
             g0 += (s.nit + kGroup - 1) / kGroup;
         }
     } else {
@@ -658,15 +732,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         const uint32_t st_lane = (uint32_t)(quad * 32) << 16;
         const uint32_t pk_quad = sbase + L::pk + quad * L::kTile;
         const uint32_t a_col_q = tmem_base + st_lane + (uint32_t)L::kACol0;
-        // the block's groups are numbered across segments; team t takes groups t, t + 3, ...
-        SegIter it;
-        it.start(p, block);
+        // the block's groups are numbered across segments and stages; team t takes groups t, t + 3, ...
+        WorkIter<S> it;
+        it.start(q, block);
         Seg cur = {0, 0, 0, 1, 0, 0};
         int cur_g0 = 0, cur_ng = 0;
         auto locate = [&](int G) {   // advances `cur` to the segment that holds group G; false once the block's work ends
             while (G >= cur_g0 + cur_ng) {
                 cur_g0 += cur_ng;
-                if (!it.next(p, block, cur)) {
+                if (!it.next(q, block, cur)) {
                     cur_ng = 0;
                     return false;
                 }
@@ -682,7 +756,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             int good = 1;
             if (lane == 0 && quad == 0) { TL(7, G); }
             // (the producers waited for the slot to be free before they filled it: the group's place in tensor memory is free too)
-            if (lane == 0) good = mbar_wait(full_pk(gs), phs, abort_flag, p.status, 14, lim);
+            if (lane == 0) good = mbar_wait(full_w(gs), phs, abort_flag, status, 14, lim);
             if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
             if (lane == 0 && quad == 0) { TL(9, G); }
             tc_fence_after_sync();
@@ -735,21 +809,40 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, L::kTmemCols);
     }
+    // The last block to finish brings the gather points' expected totals up to date (nothing in this launch reads them
+    // after its start) and leaves the launch's bookkeeping counters zero.
+    if (threadIdx.x == 0) {
+        grid_dep_wait();   // (a block without work gets here early: the counters may still be the previous launch's)
+        bool last = gridDim.x == 1;
+        if (q.sync && gridDim.x > 1) {
+            __threadfence();
+            last = atomicAdd(q.sync, 1) == (int)gridDim.x - 1;
+        } else if (!q.sync) {
+            last = block == 0;   // a single stage without scratch: no stage of this launch waits on a point it fills
+        }
+        if (last) {
+            for (int s = 0; s < q.n; ++s) {
+                if (q.st[s].ranks > 1) *q.st[s].expected = *q.st[s].expected + q.st[s].launch_arrivals;
+                if (q.sync) q.sync[1 + s] = 0;
+            }
+            if (q.sync) q.sync[0] = 0;
+        }
+    }
 }
 
-template <int FMT>
-int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, const ActMap &amap, bool overlap, cudaStream_t stream) {
+template <int FMT, int S>
+int32_t launch_seq(const Sequence<S> &q, bool overlap, cudaStream_t stream) {
     constexpr int smem_bytes = Layout<FMT>::total + 1024;
     static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<FMT, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)p.sk_grid);
+    cfg.gridDim = dim3((unsigned)q.grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -758,9 +851,25 @@ int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, const ActMap &am
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<FMT>, p, maps, amap));
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<FMT, S>, q));
     TTB_LAUNCH_CHECK("matmul_decode_tmem");
     return TTB_OK;
+}
+
+template <int S>
+int32_t build_and_launch(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream) {
+    static Sequence<S> q;   // (large: kept out of the stack; one host thread per process drives the library)
+    q.n = n;
+    q.sync = sync;
+    q.grid = 1;
+    for (int s = 0; s < n; ++s) {
+        q.st[s] = stages[s];
+        if (stages[s].sk_grid > q.grid) q.grid = stages[s].sk_grid;
+        if (int32_t rc = make_weight_maps(stages[s], fmt, q.maps[s])) return rc;
+        if (int32_t rc = make_act_map(stages[s], (int64_t)(stages[s].sk_tiles / stages[s].tstart[stages[s].nprob]) * 32, q.amap[s])) return rc;
+    }
+    if (fmt == TTB_BFLOAT8_B) return launch_seq<TTB_BFLOAT8_B, S>(q, overlap, stream);
+    return launch_seq<TTB_BFLOAT4_B, S>(q, overlap, stream);
 }
 
 }  // namespace
@@ -772,14 +881,12 @@ extern "C" int32_t ttb_debug_timeline(void *host) {
 }
 #endif
 
-int32_t launch_decode_tmem(const DecodeArgs &p, int fmt, int nb, bool overlap, cudaStream_t stream) {
-    WeightMaps maps;
-    if (int32_t rc = make_weight_maps(p, fmt, maps)) return rc;
-    if (nb != 32) return fail(TTB_E_UNSUPPORTED, "the tensor-memory-operand decode kernel serves 32-row blocks");
-    ActMap amap;
-    if (int32_t rc = make_act_map(p, (int64_t)(p.sk_tiles / p.tstart[p.nprob]) * 32, amap)) return rc;
-    if (fmt == TTB_BFLOAT8_B) return launch_one<TTB_BFLOAT8_B>(p, maps, amap, overlap, stream);
-    return launch_one<TTB_BFLOAT4_B>(p, maps, amap, overlap, stream);
+// `stages`: what launch_matmul_decode_multi prepared for each stage (32-row blocks, one weight format for the launch);
+// `sync`: the launch's bookkeeping counters in the zeroed head of the workspace, or null for a single stage without scratch.
+int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream) {
+    if (n < 1 || n > kMaxSequenceStages) return fail(TTB_E_INVALID, "a launch holds 1..%d stages", kMaxSequenceStages);
+    if (n == 1) return build_and_launch<1>(stages, n, fmt, sync, overlap, stream);
+    return build_and_launch<kMaxSequenceStages>(stages, n, fmt, sync, overlap, stream);
 }
 
 }  // namespace ttb
