@@ -25,7 +25,8 @@
 // tensor-map copy that delivers them in the MMA's swizzled K-major operand layout; warps 17 and 18 (one thread each)
 // issue the MMAs of the first and second K step of every stage into their own accumulators.
 // One ring of eight groups carries everything a group needs - packed tiles and activations in shared memory, expanded
-// weights in tensor memory - and is released as a whole by the commit of the group's MMAs.
+// weights in tensor memory. A slot's packed tiles are released as soon as they are expanded (the next copy from HBM
+// starts then); its activations and its place in tensor memory by the commit of the group's MMAs.
 // Every wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include "decode_common.cuh"
 
@@ -60,14 +61,17 @@ template <int FMT>
 struct Layout {
     static constexpr int kTile = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
     static constexpr int kStageBytes = 4 * kTile;                  // 4352 / 2304
-    static constexpr int kRing = 8;                                // groups in flight
+    static constexpr int kRing = 8;                                // groups whose activations / expanded weights are in flight
+    // Packed tiles in flight: the copies from HBM need ~100 KB per SM under way to keep the memory system busy, on top of
+    // the groups that sit in shared memory while they are expanded, so this ring is deeper than the one above.
+    static constexpr int kWRing = FMT == TTB_BFLOAT8_B ? 12 : 20;
     static constexpr int kBStageBytes = NB * BK * 2;
     static constexpr int pk = 0;
-    static constexpr int b = pk + kRing * kGroup * kStageBytes;    // (a multiple of 256: the swizzled operand needs it)
+    static constexpr int b = pk + kWRing * kGroup * kStageBytes;   // (a multiple of 256: the swizzled operand needs it)
     static constexpr int stage = b + kRing * kGroup * kBStageBytes;   // [NB x 128] bf16 tiled slab for the gather epilogue
     static constexpr int bars = stage + NB * BN * 2;
-    // full_w[kRing], full_b[kRing], full_a[kRing], empty[kRing / 2] (per pair of groups), acc_full[2], acc_empty[2]
-    static constexpr int nbars = 4 * kRing + 4;
+    // full_b[kRing], full_a[kRing], empty[kRing] (one per pair of groups used), acc_full[2], acc_empty[2], full_w[kWRing], w_empty[kWRing]
+    static constexpr int nbars = 3 * kRing + 4 + 2 * kWRing;
     static constexpr int misc = bars + 8 * nbars;                  // tmem base, abort flag, last-block flag, two accumulator-ready flags
     static constexpr int total = misc + 32;
     // Issuing costs a thread ~46 cycles per MMA and ~300 per commit, whatever the MMA's size. Two issuing threads take
@@ -82,7 +86,7 @@ struct Layout {
     static_assert(b % 256 == 0 && kBStageBytes % 1024 == 0, "alignment of the swizzled activation operand");
     // The teams wait on the ring barriers with different phase parities, which is only right while a waiter is at most
     // one phase behind, i.e. while the ring has at least as many groups as there are teams.
-    static_assert(kTeams <= kRing && kRing % 2 == 0, "ring shorter than the number of teams");
+    static_assert(kTeams <= kRing && kRing % 2 == 0 && kTeams <= kWRing, "ring shorter than the number of teams");
 };
 
 struct Seg {
@@ -200,6 +204,17 @@ __device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t addr, uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_16x256b(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -326,6 +341,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     if (tid == 0) *ready = (ok && mbar_wait(acc_full, (uint32_t)((seg_idx >> 1) & 1), c.abort_flag, p.status, 15, c.lim)) ? 1 : 0;
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     const bool eok = *ready != 0;
+    if (tid == 0) { TL(5, seg_idx * 8); }
     tc_fence_after_sync();
     const TileRef tr = tile_ref(p, s.tile);
     const int64_t row0 = (int64_t)tr.rchunk * NB;
@@ -397,8 +413,10 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
             }
         }
         release_accumulator();
+        if (tid == 0) { TL(5, seg_idx * 8 + 1); }
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (tid == 0) { TL(5, seg_idx * 8 + 2); }
         if (tid == 0) {
             *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
             __threadfence();   // acquire side: the other blocks' partial sums, published before their tickets, are visible to
@@ -406,6 +424,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         finished = *c.last_flag != 0;
+        if (tid == 0) { TL(5, seg_idx * 8 + 3); }
     }
     // phase 2: whoever holds the complete sum - the only block of an unshared tile, or the last arriver - finishes the tile
     if (finished && (eok || contributors > 1)) {
@@ -469,6 +488,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
         if (contributors > 1 && tid == 0) p.counters[s.tile] = 0;
     }
     if (contributors == 1) release_accumulator();
+    if (tid == 0) { TL(5, seg_idx * 8 + 4); }
     bool send = finished;
     if (p.gated) {
         // the second of the pair's two tiles to be finished forms the product (the same four warps run through the same
@@ -504,6 +524,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");   // (last_flag is reused below)
     }
+    if (tid == 0) { TL(5, seg_idx * 8 + 5); }
     if (done_counter) {
         // a later stage of this launch reads this stage's output: count the tile once it is stored
         __threadfence();
@@ -517,6 +538,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (*c.last_flag) gather_send<NB>(p, stage, row0, tr.nt, tid, kEpiThreads);   // ends with a barrier: the slab is free again
     }
+    if (tid == 0) { TL(6, seg_idx); }
     return eok;
 }
 
@@ -528,11 +550,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::bars;
-    auto full_w = [&](int s) { return bar0 + 8u * s; };                   // the group's packed tiles have landed
-    auto full_b = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's activations have landed
-    auto full_a = [&](int s) { return bar0 + 8u * (2 * kRing + s); };     // the group's weights are expanded in tensor memory
-    auto empty = [&](int s) { return bar0 + 8u * (3 * kRing + (s >> 1)); };   // the MMAs of the pair of groups {s & ~1, s | 1} are complete: both slots are free
-    const uint32_t acc_full0 = bar0 + 8u * (4 * kRing), acc_empty0 = acc_full0 + 16u;
+    constexpr int kWRing = L::kWRing;
+    auto full_b = [&](int s) { return bar0 + 8u * s; };                   // the group's activations have landed
+    auto full_a = [&](int s) { return bar0 + 8u * (kRing + s); };         // the group's weights are expanded in tensor memory
+    auto empty = [&](int s) { return bar0 + 8u * (2 * kRing + (s >> 1)); };   // the MMAs of the pair of groups {s & ~1, s | 1} are complete: both slots are free
+    const uint32_t acc_full0 = bar0 + 8u * (3 * kRing), acc_empty0 = acc_full0 + 16u;
+    // the ring of packed tiles (slot = group number modulo kWRing): landed / read out of shared memory (the slot can take
+    // the next copy while the expanded weights still wait in tensor memory for their MMAs)
+    auto full_w = [&](int s) { return acc_empty0 + 16u + 8u * s; };
+    auto w_empty = [&](int s) { return acc_empty0 + 16u + 8u * (kWRing + s); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::misc + 4);
     volatile int *last_flag = reinterpret_cast<volatile int *>(smem + L::misc + 8);
@@ -549,10 +575,13 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kRing; ++s) {
-            mbar_init(full_w(s), 1);      // the weight producer, with its byte count
             mbar_init(full_b(s), 1);      // the activation producer, with its byte count
             mbar_init(full_a(s), 4);      // the four expand warps of the group's team
             if ((s & 1) == 0) mbar_init(empty(s), 1);   // the commit of the issuer that owns the pair
+        }
+        for (int s = 0; s < kWRing; ++s) {
+            mbar_init(full_w(s), 1);      // the weight producer, with its byte count
+            mbar_init(w_empty(s), 4);     // the four expand warps of the group's team
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(acc_full0 + 8u * s, 2);
@@ -577,7 +606,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
 
     if (warp == kProducerWarp) {
         // ---------------- packed weight tiles -> shared-memory ring, across segment and stage borders ----------------
-        if (lane == 0) {
+        // (the whole warp walks the work list, one elected lane issues: see the MMA issuers)
+        {
+            const bool leader = elect_one();
             const uint64_t policy = l2_policy_evict_first();
             int gs = 0, tlg = 0;
             (void)tlg;
@@ -590,19 +621,23 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 const TileRef tr = tile_ref(p, s.tile);
                 const void *map = &q.maps[S == 1 ? 0 : it.si].m[tr.prob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, status, 11, lim)) { ok = false; break; }
-                    TL(0, tlg); ++tlg;
-                    // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
-                    // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
-                    mbar_arrive_expect_tx(full_w(gs), kGroup * L::kStageBytes);
-                    tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_w(gs), policy);
-                    if (++gs == kRing) { gs = 0; ph ^= 1; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(w_empty(gs), ph ^ 1, abort_flag, status, 11, lim))) { ok = false; break; }
+                    if (leader) {
+                        TL(0, tlg);
+                        // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
+                        // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
+                        mbar_arrive_expect_tx(full_w(gs), kGroup * L::kStageBytes);
+                        tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_w(gs), policy);
+                    }
+                    ++tlg;
+                    if (++gs == kWRing) { gs = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == kLoaderWarp) {
         // ---------------- activations -> shared memory, one tensor-map copy per group ----------------
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             grid_dep_wait();   // the activations are earlier kernels' output
             // What the gather points this launch waits for had been told to expect before the launch (the totals are only
             // brought up to date by the last block to finish); stages of this launch that gather into a point add their share.
@@ -620,7 +655,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 if (it.si != ready_stage) {
                     // first segment of a stage: hold the copies until the stage's activation is complete
                     ready_stage = it.si;
-                    bool waited = false;
+                    bool waited = false, good = true;
                     if (p.wait_arrived) {
                         unsigned target = 0;
 #pragma unroll
@@ -628,26 +663,33 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                             if (j == it.si) target += e0[j];
                             if (j < it.si && q.st[j].ranks > 1 && q.st[j].expected == p.wait_expected) target += q.st[j].launch_arrivals;
                         }
-                        if (!peer_wait_for(p, target, abort_flag, 6)) { ok = false; break; }
+                        if (leader) good = peer_wait_for(p, target, abort_flag, 6);   // (one lane polls)
                         waited = true;
                     }
                     if (S > 1 && p.depends_on >= 0) {
-                        if (!count_wait(q.sync + 1 + p.depends_on, q.st[p.depends_on].sk_tiles / (q.st[p.depends_on].gated ? 2 : 1), p, abort_flag, 8)) { ok = false; break; }
+                        if (leader && good) good = count_wait(q.sync + 1 + p.depends_on, q.st[p.depends_on].sk_tiles / (q.st[p.depends_on].gated ? 2 : 1), p, abort_flag, 8);
                         waited = true;
                     }
-                    if (waited) fence_proxy_async_global();   // what was stored before the signal is read by the copy unit next
+                    if (waited) {
+                        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+                        if (leader) fence_proxy_async_global();   // what was stored before the signal is read by the copy unit next
+                    }
+                    if (leader) { TL(8, it.si); }
                 }
                 const int rchunk = s.tile / p.tstart[p.nprob];
                 const void *amap = &q.amap[S == 1 ? 0 : it.si].m;
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if ((gs & 1) == 0 && !mbar_wait(empty(gs), ph ^ 1, abort_flag, status, 17, lim)) { ok = false; break; }
-                    TL(4, tlg); ++tlg;
-                    mbar_arrive_expect_tx(full_b(gs), kGroup * L::kBStageBytes);
-                    const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
-                    if (p.a_row_major)
-                        tma_load_3d_plain(dst, amap, 0, rchunk * NB, (s.kb0 + i0) * 2, full_b(gs));
-                    else
-                        tma_load_5d(dst, amap, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_b(gs));
+                    if ((gs & 1) == 0 && !__all_sync(0xffffffffu, mbar_wait(empty(gs), ph ^ 1, abort_flag, status, 17, lim))) { ok = false; break; }
+                    if (leader) {
+                        TL(4, tlg);
+                        mbar_arrive_expect_tx(full_b(gs), kGroup * L::kBStageBytes);
+                        const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
+                        if (p.a_row_major)
+                            tma_load_3d_plain(dst, amap, 0, rchunk * NB, (s.kb0 + i0) * 2, full_b(gs));
+                        else
+                            tma_load_5d(dst, amap, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_b(gs));
+                    }
+                    ++tlg;
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
             }
@@ -655,7 +697,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ---------------- MMA issuers: A from tensor memory, B (activations) from shared memory ----------------
         // Issuer h takes the pairs of groups whose pair number is h modulo 2 and accumulates them in accumulator h.
-        if (lane == 0) {
+        // The whole warp walks the work list (so that addresses and descriptors stay warp-uniform values); one elected lane
+        // issues.
+        {
+            const bool leader = elect_one();
             const int h = warp - kMmaWarp;
             constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/false, /*b_mn_major=*/false);
             const uint64_t b_desc0 = smem_desc_sw32(sbase + L::b, kB_SBO);
@@ -670,35 +715,42 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             Seg s;
             for (; ok && it.next(q, block, s); ++seg_idx) {
                 const int buf = seg_idx & 1;
-                if (!mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, status, 16, lim)) { ok = false; break; }
+                // (every decision the warp takes is taken by all its lanes together)
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, status, 16, lim))) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + h) * NB);
                 bool fresh = true;   // this issuer's accumulator holds nothing of this segment yet
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
                     if (((gs >> 1) & 1) == h) {
                         const int r = min(kGroup, s.nit - i0);
-                        if (h == 0) { TL(1, tlg); }
-                        if (!mbar_wait(full_a(gs), ph, abort_flag, status, 12, lim) || !mbar_wait(full_b(gs), ph, abort_flag, status, 18, lim)) { ok = false; break; }
-                        if (h == 0) { TL(2, tlg); }
+                        if (h == 0 && leader) { TL(1, tlg); }
+                        if (!__all_sync(0xffffffffu, mbar_wait(full_a(gs), ph, abort_flag, status, 12, lim) && mbar_wait(full_b(gs), ph, abort_flag, status, 18, lim))) { ok = false; break; }
+                        if (h == 0 && leader) { TL(2, tlg); }
                         tc_fence_after_sync();
                         const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
                         const uint32_t b_lo = b_lo0 + (uint32_t)gs * ((kGroup * L::kBStageBytes) >> 4);
 #pragma unroll
                         for (int j = 0; j < kGroup; ++j) {
+#ifdef TTB_KO_MMA
+                            if (false) {
+#else
                             if (j < r) {
-                                mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage), mk(b_lo + (uint32_t)((j * L::kBStageBytes) >> 4), b_hi), idesc, !(fresh && j == 0));
-                                mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage + 8), mk(b_lo + (uint32_t)((j * L::kBStageBytes + L::kBStageBytes / 2) >> 4), b_hi), idesc, true);
+#endif
+                                if (leader) {
+                                    mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage), mk(b_lo + (uint32_t)((j * L::kBStageBytes) >> 4), b_hi), idesc, !(fresh && j == 0));
+                                    mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage + 8), mk(b_lo + (uint32_t)((j * L::kBStageBytes + L::kBStageBytes / 2) >> 4), b_hi), idesc, true);
+                                }
                             }
                         }
                         fresh = false;
-                        if (gs & 1) mma_commit(empty(gs));   // second group of the pair: one commit frees both slots
-                        if (h == 0) { TL(3, tlg); }
+                        if ((gs & 1) && leader) mma_commit(empty(gs));   // second group of the pair: one commit frees both slots
+                        if (h == 0 && leader) { TL(3, tlg); }
                     }
                     ++tlg;
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
                 // (an issuer that had no group in this segment still commits: its arrival is part of the barrier's count)
-                if (ok) mma_commit(acc_full0 + 8u * buf);
+                if (ok && leader) mma_commit(acc_full0 + 8u * buf);
             }
             // An odd number of groups leaves the last pair's commit unsent: nothing waits for it any more.
         }
@@ -749,19 +801,22 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             return true;
         };
         int G = team;
-        int gs = G % kRing;
-        uint32_t phs = (uint32_t)(G / kRing) & 1u;
+        int gs = G % kRing, ws = G % kWRing;   // (ws: the slot in the ring of packed tiles)
+        uint32_t phs = (uint32_t)(G / kRing) & 1u, wphs = (uint32_t)(G / kWRing) & 1u;
         while (locate(G)) {
             const int r = min(kGroup, cur.nit - (G - cur_g0) * kGroup);
             int good = 1;
             if (lane == 0 && quad == 0) { TL(7, G); }
-            // (the producers waited for the slot to be free before they filled it: the group's place in tensor memory is free too)
-            if (lane == 0) good = mbar_wait(full_w(gs), phs, abort_flag, status, 14, lim);
-            if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
+            // the packed tiles have landed, and the MMAs that read this slot's place in tensor memory a ring pass ago are complete
+            good = mbar_wait(full_w(ws), wphs, abort_flag, status, 14, lim) && mbar_wait(empty(gs), phs ^ 1u, abort_flag, status, 19, lim);
+            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
             if (lane == 0 && quad == 0) { TL(9, G); }
             tc_fence_after_sync();
-            uint32_t tile = pk_quad + (uint32_t)(gs * kGroup * L::kStageBytes);
+            uint32_t tile = pk_quad + (uint32_t)(ws * kGroup * L::kStageBytes);
             uint32_t a_col = a_col_q + (uint32_t)(gs * kGroup * kAColsPerStage);
+#ifdef TTB_KO_EXPAND
+            if (false)
+#endif
 #pragma unroll 1
             for (int j = 0; j < r; ++j) {
                 // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
@@ -787,11 +842,16 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_a(gs));
+            if (lane == 0) {
+                mbar_arrive(full_a(gs));
+                mbar_arrive(w_empty(ws));
+            }
             if (lane == 0 && quad == 0) { TL(11, G); }
             G += kTeams;
             gs += kTeams;
             if (gs >= kRing) { gs -= kRing; phs ^= 1u; }
+            ws += kTeams;
+            if (ws >= kWRing) { ws -= kWRing; wphs ^= 1u; }
         }
     }
 
