@@ -11,17 +11,17 @@ namespace ttb {
 struct DecodeArgs;
 constexpr int kMaxSequenceStages = 4;   // stages (ttb_matmul_multi calls) one launch can hold
 // One tiled tensor map per weight of a launch: the packed weight seen as [K blocks][tiles per row][tile as 8-byte words], so
-// that a producer thread fetches the three stages of a group (three K blocks x four tiles) with ONE copy instruction.
+// that a producer thread fetches the stages of a group (`group` K blocks x four tiles) with ONE copy instruction.
 struct alignas(64) WeightMaps {
     CUtensorMap m[TTB_MAX_GROUP];
 };
-int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps);
+int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps, int group = 3);
 // The activation [rows, K] (tiled or row-major bf16) as a tensor map whose box is three K blocks of 32 rows, delivered in
-// the MMA's K-major operand layout with the 32-byte swizzle: [K block][16-column half][row][16 values].
+// the MMA's K-major operand layout (`group` K blocks of 32 rows) with the 32-byte swizzle: [K block][16-column half][row][16 values].
 struct alignas(64) ActMap {
     CUtensorMap m;
 };
-int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map);
+int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map, int group = 3);
 
 struct DecodeArgs {
     const uint8_t *w;

@@ -596,7 +596,7 @@ int32_t launch_one(const DecodeArgs &p, const WeightMaps &maps, bool overlap, cu
 
 // Tensor maps of the launch's weights. cuTensorMapEncodeTiled is reached through the runtime's driver entry point (no link
 // against the driver library).
-int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) {
+int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps, int group) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -613,7 +613,7 @@ int32_t make_weight_maps(const DecodeArgs &p, int fmt, WeightMaps &maps) {
         const cuuint64_t Nt = (cuuint64_t)(p.Nv[j] / 32), Kt = (cuuint64_t)p.Kt;
         const cuuint64_t dims[3] = {tile_bytes / 8, Nt, Kt};
         const cuuint64_t strides[2] = {tile_bytes, Nt * tile_bytes};
-        const cuuint32_t box[3] = {(cuuint32_t)(tile_bytes / 8), 4, 3};   // three K blocks = one group of stages in both kernels
+        const cuuint32_t box[3] = {(cuuint32_t)(tile_bytes / 8), 4, (cuuint32_t)group};   // `group` K blocks = one group of stages
         const cuuint32_t estr[3] = {1, 1, 1};
         const CUresult r = encode(&maps.m[j], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<uint8_t *>(p.wv[j]), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -637,7 +637,7 @@ static int32_t tensor_map_encoder(void **out) {
     return TTB_OK;
 }
 
-int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map) {
+int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map, int group) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -651,14 +651,14 @@ int32_t make_act_map(const DecodeArgs &p, int64_t rows, ActMap &map) {
         // [rows][K]: 16 values, rows, 16-column chunks
         const cuuint64_t dims[3] = {16, (cuuint64_t)rows, (cuuint64_t)(p.K / 16)};
         const cuuint64_t strides[2] = {(cuuint64_t)p.K * 2, 32};
-        const cuuint32_t box[3] = {16, 32, 6};
+        const cuuint32_t box[3] = {16, 32, (cuuint32_t)(2 * group)};
         r = encode(&map.m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         // tiles of 2048 bytes in (row tile, K tile) order; inside: 16 values, 16 face rows, upper / lower faces, left / right faces
         const cuuint64_t dims[5] = {16, 16, 2, 2, (cuuint64_t)((rows / 32) * p.Kt)};
         const cuuint64_t strides[4] = {32, 1024, 512, 2048};
-        const cuuint32_t box[5] = {16, 16, 2, 2, 3};
+        const cuuint32_t box[5] = {16, 16, 2, 2, (cuuint32_t)group};
         r = encode(&map.m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }

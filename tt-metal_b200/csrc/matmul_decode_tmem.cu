@@ -18,7 +18,7 @@
 //     the activations (B) from shared memory.
 //
 // Roles (20 warps). A warp can only touch the 32 TMEM lanes of its quadrant (warp % 4) = one of the four packed tiles of
-// a stage, so the expand warps 0..11 form three teams of four; team t expands every third group of three K blocks.
+// a stage, so the expand warps 0..11 form three teams of four; team t expands every third group of four K blocks.
 // They do nothing else: no global loads, no epilogue. Warps 12..15 run the epilogues (one per TMEM lane quadrant) on one
 // of two accumulator sets while the MMAs of the next segment fill the other. Warp 16 (one thread) streams the packed
 // tiles with one tensor-map copy per group; warp 19 (one thread) streams the activations of the same group with another
@@ -46,7 +46,7 @@ using namespace ptx;
 
 constexpr int BN = 128;  // weight columns per tile (MMA M, TMEM lanes)
 constexpr int BK = 32;   // K per stage: one row of four packed tiles
-constexpr int kGroup = 3;                      // stages per group (one barrier round trip per group)
+constexpr int kGroup = 4;                      // stages (K blocks) per group: one barrier round trip and one copy of each kind per group
 constexpr int kTeams = 3;                      // expand teams of four warps
 constexpr int kExpandWarps = 4 * kTeams;       // warps 0..11; quadrant = warp % 4, team = warp / 4
 constexpr int kEpiWarp0 = kExpandWarps;        // warps 12..15
@@ -61,10 +61,10 @@ template <int FMT>
 struct Layout {
     static constexpr int kTile = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
     static constexpr int kStageBytes = 4 * kTile;                  // 4352 / 2304
-    static constexpr int kRing = 8;                                // groups whose activations / expanded weights are in flight
+    static constexpr int kRing = 6;                                // groups whose activations / expanded weights are in flight
     // Packed tiles in flight: the copies from HBM need ~100 KB per SM under way to keep the memory system busy, on top of
     // the groups that sit in shared memory while they are expanded, so this ring is deeper than the one above.
-    static constexpr int kWRing = FMT == TTB_BFLOAT8_B ? 12 : 20;
+    static constexpr int kWRing = FMT == TTB_BFLOAT8_B ? 9 : 15;
     static constexpr int kBStageBytes = NB * BK * 2;
     static constexpr int pk = 0;
     static constexpr int b = pk + kWRing * kGroup * kStageBytes;   // (a multiple of 256: the swizzled operand needs it)
@@ -624,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                     if (!__all_sync(0xffffffffu, mbar_wait(w_empty(gs), ph ^ 1, abort_flag, status, 11, lim))) { ok = false; break; }
                     if (leader) {
                         TL(0, tlg);
-                        // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
+                        // always a whole box of four K blocks: in a short last group the surplus lands in the group's unused
                         // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
                         mbar_arrive_expect_tx(full_w(gs), kGroup * L::kStageBytes);
                         tma_load_3d(sbase + L::pk + gs * kGroup * L::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_w(gs), policy);
@@ -696,7 +696,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ---------------- MMA issuers: A from tensor memory, B (activations) from shared memory ----------------
-        // Issuer h takes the pairs of groups whose pair number is h modulo 2 and accumulates them in accumulator h.
+        // Issuer h takes the pairs of groups (numbered over the block's whole work) whose pair number is h modulo 2 and
+        // accumulates them in accumulator h.
         // The whole warp walks the work list (so that addresses and descriptors stay warp-uniform values); one elected lane
         // issues.
         {
@@ -707,8 +708,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             const uint32_t a_col0 = tmem_base + (uint32_t)L::kACol0;
             auto mk = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
-            int gs = 0, seg_idx = 0, tlg = 0;
-            (void)tlg;
+            int gs = 0, seg_idx = 0, G = 0;
             uint32_t ph = 0;
             WorkIter<S> it;
             it.start(q, block);
@@ -721,11 +721,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                 const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + h) * NB);
                 bool fresh = true;   // this issuer's accumulator holds nothing of this segment yet
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if (((gs >> 1) & 1) == h) {
+                    if (((G >> 1) & 1) == h) {   // (G: the group's number over the block's whole work)
                         const int r = min(kGroup, s.nit - i0);
-                        if (h == 0 && leader) { TL(1, tlg); }
+                        if (h == 0 && leader) { TL(1, G); }
                         if (!__all_sync(0xffffffffu, mbar_wait(full_a(gs), ph, abort_flag, status, 12, lim) && mbar_wait(full_b(gs), ph, abort_flag, status, 18, lim))) { ok = false; break; }
-                        if (h == 0 && leader) { TL(2, tlg); }
+                        if (h == 0 && leader) { TL(2, G); }
                         tc_fence_after_sync();
                         const uint32_t a_col = a_col0 + (uint32_t)(gs * kGroup * kAColsPerStage);
                         const uint32_t b_lo = b_lo0 + (uint32_t)gs * ((kGroup * L::kBStageBytes) >> 4);
@@ -744,9 +744,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                         }
                         fresh = false;
                         if ((gs & 1) && leader) mma_commit(empty(gs));   // second group of the pair: one commit frees both slots
-                        if (h == 0 && leader) { TL(3, tlg); }
+                        if (h == 0 && leader) { TL(3, G); }
                     }
-                    ++tlg;
+                    ++G;
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
                 }
                 // (an issuer that had no group in this segment still commits: its arrival is part of the barrier's count)
@@ -925,8 +925,8 @@ int32_t build_and_launch(const DecodeArgs *stages, int n, int fmt, int *sync, bo
     for (int s = 0; s < n; ++s) {
         q.st[s] = stages[s];
         if (stages[s].sk_grid > q.grid) q.grid = stages[s].sk_grid;
-        if (int32_t rc = make_weight_maps(stages[s], fmt, q.maps[s])) return rc;
-        if (int32_t rc = make_act_map(stages[s], (int64_t)(stages[s].sk_tiles / stages[s].tstart[stages[s].nprob]) * 32, q.amap[s])) return rc;
+        if (int32_t rc = make_weight_maps(stages[s], fmt, q.maps[s], kGroup)) return rc;
+        if (int32_t rc = make_act_map(stages[s], (int64_t)(stages[s].sk_tiles / stages[s].tstart[stages[s].nprob]) * 32, q.amap[s], kGroup)) return rc;
     }
     if (fmt == TTB_BFLOAT8_B) return launch_seq<TTB_BFLOAT8_B, S>(q, overlap, stream);
     return launch_seq<TTB_BFLOAT4_B, S>(q, overlap, stream);
