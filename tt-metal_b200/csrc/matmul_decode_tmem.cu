@@ -268,6 +268,32 @@ __device__ __forceinline__ void expand_tile(uint32_t tile, uint32_t a_col, uint3
         tmem_st_16x256b(a_col + ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8), o[0], o[1], o[2], o[3]);
     }
 }
+// Two tiles at once (the common case: no exponent above 127): the transposing loads of both go out first and the faces
+// are expanded alternately, so that one tile's shuffles and stores wait behind the other's arithmetic.
+__device__ __forceinline__ void expand_pair(uint32_t tile0, uint32_t tile1, uint32_t a_col0, uint32_t a_col1, uint32_t ld_off, uint32_t eh0,
+                                            uint32_t eh1, int sh0) {
+    const uint32_t scale0 = (__vminu2(eh0, 0x007f007fu) + 0x007f007fu) << 7, scale1 = (__vminu2(eh1, 0x007f007fu) + 0x007f007fu) << 7;
+    uint32_t top0[4], bot0[4], top1[4], bot1[4];
+    ldmatrix_x2_trans_b8(tile0 + ld_off, top0);
+    ldmatrix_x2_trans_b8(tile0 + ld_off + 512u, bot0);
+    ldmatrix_x2_trans_b8(tile1 + ld_off, top1);
+    ldmatrix_x2_trans_b8(tile1 + ld_off + 512u, bot1);
+#pragma unroll
+    for (int f = 0; f < 4; ++f) {
+        const uint32_t p01 = __shfl_sync(0xffffffffu, scale0, 8 * f + sh0), p23 = __shfl_sync(0xffffffffu, scale0, 8 * f + sh0 + 1);
+        const uint32_t q01 = __shfl_sync(0xffffffffu, scale1, 8 * f + sh0), q23 = __shfl_sync(0xffffffffu, scale1, 8 * f + sh0 + 1);
+        const uint32_t c0 = (f >> 1) ? bot0[2 * (f & 1)] : top0[2 * (f & 1)], c1 = (f >> 1) ? bot0[2 * (f & 1) + 1] : top0[2 * (f & 1) + 1];
+        const uint32_t d0 = (f >> 1) ? bot1[2 * (f & 1)] : top1[2 * (f & 1)], d1 = (f >> 1) ? bot1[2 * (f & 1) + 1] : top1[2 * (f & 1) + 1];
+        uint32_t o[4], w[4];
+        expand4(c0, p01, p23, o[0], o[1]);
+        expand4(d0, q01, q23, w[0], w[1]);
+        expand4(c1, p01, p23, o[2], o[3]);
+        expand4(d1, q01, q23, w[2], w[3]);
+        const uint32_t off = ((uint32_t)((f & 1) * 16) << 16) + (uint32_t)((f >> 1) * 8);
+        tmem_st_16x256b(a_col0 + off, o[0], o[1], o[2], o[3]);
+        tmem_st_16x256b(a_col1 + off, w[0], w[1], w[2], w[3]);
+    }
+}
 __device__ __noinline__ void expand_tile_big(uint32_t tile, uint32_t a_col, uint32_t ld_off, uint32_t eh, int sh0) {
     expand_tile<true>(tile, a_col, ld_off, eh, sh0);
 }
@@ -309,6 +335,40 @@ __device__ __forceinline__ void expand_tile4(uint32_t tile, uint32_t a_col, uint
                 o[0] = mul2(o[0], t01); o[1] = mul2(o[1], t23); o[2] = mul2(o[2], t01); o[3] = mul2(o[3], t23);
             }
             tmem_st_16x256b(a_col + ((uint32_t)(nh * 16) << 16) + (uint32_t)(kh * 8), o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+// Two bfloat4_b tiles at once, as expand_pair.
+__device__ __forceinline__ void expand_pair4(uint32_t tile0, uint32_t tile1, uint32_t a_col0, uint32_t a_col1, uint32_t ld_off4, uint32_t eh0,
+                                             uint32_t eh1, int sh0) {
+    const uint32_t scale0 = (__vminu2(eh0, 0x007f007fu) + 0x007f007fu) << 7, scale1 = (__vminu2(eh1, 0x007f007fu) + 0x007f007fu) << 7;
+    uint32_t m[2][2], k[2][2];
+    ldmatrix_x2_trans_b8_2(tile0 + ld_off4, m[0][0], m[0][1], m[1][0], m[1][1]);
+    ldmatrix_x2_trans_b8_2(tile1 + ld_off4, k[0][0], k[0][1], k[1][0], k[1][1]);
+#pragma unroll
+    for (int nh = 0; nh < 2; ++nh) {
+        const uint32_t lo_e = (m[nh][0] << 4) & 0xf0f0f0f0u, lo_o = (m[nh][1] << 4) & 0xf0f0f0f0u;
+        const uint32_t hi_e = m[nh][0] & 0xf0f0f0f0u, hi_o = m[nh][1] & 0xf0f0f0f0u;
+        const uint32_t ko_e = (k[nh][0] << 4) & 0xf0f0f0f0u, ko_o = (k[nh][1] << 4) & 0xf0f0f0f0u;
+        const uint32_t ki_e = k[nh][0] & 0xf0f0f0f0u, ki_o = k[nh][1] & 0xf0f0f0f0u;
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+            const int f = 2 * kh + nh;
+            const uint32_t p01 = __shfl_sync(0xffffffffu, scale0, 8 * f + sh0), p23 = __shfl_sync(0xffffffffu, scale0, 8 * f + sh0 + 1);
+            const uint32_t q01 = __shfl_sync(0xffffffffu, scale1, 8 * f + sh0), q23 = __shfl_sync(0xffffffffu, scale1, 8 * f + sh0 + 1);
+            const uint32_t sel0 = kh ? 0x6622u : 0x4400u, sel1 = kh ? 0x7733u : 0x5511u;
+            uint32_t o[4], w[4];
+            o[0] = mul2(__byte_perm(lo_e, lo_o, sel0) & 0x80708070u, p01);
+            w[0] = mul2(__byte_perm(ko_e, ko_o, sel0) & 0x80708070u, q01);
+            o[1] = mul2(__byte_perm(lo_e, lo_o, sel1) & 0x80708070u, p23);
+            w[1] = mul2(__byte_perm(ko_e, ko_o, sel1) & 0x80708070u, q23);
+            o[2] = mul2(__byte_perm(hi_e, hi_o, sel0) & 0x80708070u, p01);
+            w[2] = mul2(__byte_perm(ki_e, ki_o, sel0) & 0x80708070u, q01);
+            o[3] = mul2(__byte_perm(hi_e, hi_o, sel1) & 0x80708070u, p23);
+            w[3] = mul2(__byte_perm(ki_e, ki_o, sel1) & 0x80708070u, q23);
+            const uint32_t off = ((uint32_t)(nh * 16) << 16) + (uint32_t)(kh * 8);
+            tmem_st_16x256b(a_col0 + off, o[0], o[1], o[2], o[3]);
+            tmem_st_16x256b(a_col1 + off, w[0], w[1], w[2], w[3]);
         }
     }
 }
@@ -818,25 +878,39 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             if (false)
 #endif
 #pragma unroll 1
-            for (int j = 0; j < r; ++j) {
+            for (int j = 0; j < r; j += 2) {
                 // row scales: lane l holds the powers of two of exponent bytes 2l and 2l+1 of the tile's 64
-                uint32_t e2;
+                const bool two = j + 1 < r;
+                uint32_t e2, e3 = 0u;
                 asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e2) : "r"(tile + 2u * lane));
-                const uint32_t eh = __byte_perm(e2, 0u, 0x4140u);                 // [e0, 0, e1, 0]
-                const bool big = __any_sync(0xffffffffu, (eh & 0x00800080u) != 0u);
-                if (FMT == TTB_BFLOAT8_B) {
-                    if (big)
-                        expand_tile_big(tile, a_col, ld_off, eh, sh0);
+                if (two) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e3) : "r"(tile + (uint32_t)L::kStageBytes + 2u * lane));
+                const uint32_t eh = __byte_perm(e2, 0u, 0x4140u), eh1 = __byte_perm(e3, 0u, 0x4140u);   // [e0, 0, e1, 0]
+                const bool big = __any_sync(0xffffffffu, ((eh | eh1) & 0x00800080u) != 0u);
+                if (two && !big) {
+                    if (FMT == TTB_BFLOAT8_B)
+                        expand_pair(tile, tile + L::kStageBytes, a_col, a_col + kAColsPerStage, ld_off, eh, eh1, sh0);
                     else
-                        expand_tile<false>(tile, a_col, ld_off, eh, sh0);
+                        expand_pair4(tile, tile + L::kStageBytes, a_col, a_col + kAColsPerStage, ld_off4, eh, eh1, sh0);
                 } else {
-                    if (big)
-                        expand_tile4_big(tile, a_col, ld_off4, eh, sh0);
-                    else
-                        expand_tile4<false>(tile, a_col, ld_off4, eh, sh0);
+                    // a lone last tile, or an exponent above 127 somewhere (a row maximum of 2 or more): one tile at a time
+                    for (int t = 0; t < (two ? 2 : 1); ++t) {
+                        const uint32_t e = t ? eh1 : eh, tl = tile + (uint32_t)(t * L::kStageBytes), ac = a_col + (uint32_t)(t * kAColsPerStage);
+                        const bool b1 = __any_sync(0xffffffffu, (e & 0x00800080u) != 0u);
+                        if (FMT == TTB_BFLOAT8_B) {
+                            if (b1)
+                                expand_tile_big(tl, ac, ld_off, e, sh0);
+                            else
+                                expand_tile<false>(tl, ac, ld_off, e, sh0);
+                        } else {
+                            if (b1)
+                                expand_tile4_big(tl, ac, ld_off4, e, sh0);
+                            else
+                                expand_tile4<false>(tl, ac, ld_off4, e, sh0);
+                        }
+                    }
                 }
-                tile += L::kStageBytes;
-                a_col += kAColsPerStage;
+                tile += 2 * L::kStageBytes;
+                a_col += 2 * kAColsPerStage;
             }
             if (lane == 0 && quad == 0) { TL(10, G); }
             tmem_st_wait();
