@@ -47,6 +47,7 @@ _SIGS = {
     "ttb_pack_bfp": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_unpack_bfp": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp]),
     "ttb_matmul_workspace_bytes": (_i64, [_i32, _i64, _i64, _i64, _i64, _i32]),
+    "ttb_matmul_plan": (_i32, [_i32, _i64, _i64, _i64, _i64, _i32, _vp, _i32]),
     "ttb_matmul": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _i64, _vp]),
     "ttb_bmm": (_i32, [_vp, _i32, _vp, _i32, _vp, _i32, _i64, _i64, _i64, _i64, _vp]),
     "ttb_matmul_decode_static": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),

@@ -201,7 +201,8 @@ def test_decode_plan_covers_every_k_block_exactly_once():
     lib = cabi.load()
     shapes = [(32, 4544, [18176]), (32, 8192, [8192]), (32, 8192, [8192, 1024, 1024]), (32, 8192, [28672, 28672]), (32, 28672, [8192]),
               (32, 8192, [1024, 128, 128]), (32, 8192, [128]), (32, 4096, [4096, 1024, 1024]), (64, 4096, [14336, 14336]),
-              (128, 2048, [256]), (256, 16384, [7680]), (96, 1056, [384, 128]), (32, 32, [128]), (32, 8192, [3584, 3584])]
+              (128, 2048, [256]), (256, 16384, [7680]), (96, 1056, [384, 128]), (32, 32, [128]), (32, 8192, [3584, 3584]),
+              (32, 4544, [4672]), (32, 18176, [4544]), (96, 512, [160, 96])]
     for M, K, Ns in shapes:
         arr = (ctypes.c_int64 * len(Ns))(*Ns)
         out = (ctypes.c_int32 * 10)()
@@ -209,7 +210,7 @@ def test_decode_plan_covers_every_k_block_exactly_once():
         plan = list(out)
         nb, tiles, grid, pieces, kbps, waves, rem0, units, upt, slots = plan
         nkb = K // 32
-        assert nb in (32, 64, 128) and M % nb == 0 and tiles == sum(n // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148
+        assert nb in (32, 64, 128) and M % nb == 0 and tiles == sum((n + 127) // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148
         cover = _walk_plan(plan, nkb)
         assert sorted(cover) == list(range(tiles)), (M, K, Ns, plan)
         shared = 0
@@ -221,4 +222,5 @@ def test_decode_plan_covers_every_k_block_exactly_once():
         assert shared <= slots or shared == 0, (M, K, Ns, plan, shared)
     bad = (ctypes.c_int64 * 1)(96)
     out = (ctypes.c_int32 * 10)()
-    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == -3
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 64, 64, 1, bad, out, 10) == -3   # two tile rows per block: whole column tiles only
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == 0

@@ -393,8 +393,8 @@ def test_multi_arguments_are_validated(ttb):
     import torch
     buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     ptrs = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
-    ns = (ctypes.c_int64 * 2)(128, 96)                    # 96 is not a multiple of 128: not a decode shape
-    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 2, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 32, 64, ns, 0, 0,
+    ns = (ctypes.c_int64 * 2)(128, 96)                    # 96 is not a multiple of 128: with 64 rows not a decode shape
+    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 2, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 64, 64, ns, 0, 0,
                                    buf.data_ptr(), 1 << 20, None, None, None)
     assert rc == -3
     rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 5, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 32, 64, ns, 0, 0,
@@ -446,3 +446,64 @@ def test_gated_pair_in_one_launch(ttb, orc, w_dtype, M, K, N):
     rc = ttb.cdll.ttb_matmul_multi(a.data_ptr(), cabi.BFLOAT16, 2, arr_w, w_dtype, None, arr_o, cabi.BFLOAT16, 1, M, K, arr_n2,
                                    cabi.ACT_SILU, cabi.MM_GATED | cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None, None, None)
     assert rc == -1
+
+
+def _plan(ttb, w_dtype, M, K, N, flags=0):
+    import ctypes
+    out = (ctypes.c_int64 * 5)()
+    assert ttb.cdll.ttb_matmul_plan(w_dtype, 1, M, K, N, flags, out, 5) == 0
+    return list(out)
+
+
+@pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
+@pytest.mark.parametrize("M,K,N", [
+    (32, 4544, 4672),      # Falcon-7B fused QKV: the last column tile holds 64 columns
+    (32, 4544, 4544),      # Falcon-7B dense / selfout
+    (32, 18176, 4544),     # Falcon-7B 4h_to_h
+    (96, 512, 160),        # 32 columns in the last tile, three tile rows
+    (32, 256, 96),         # a single, partial column tile
+])
+def test_last_column_tile_of_fewer_than_128_columns(ttb, orc, w_dtype, M, K, N):
+    """N a multiple of 32 but not of 128 stays on the tensor-core decode kernel (one launch, decode kind): the missing packed
+    tiles of the last column tile read as zeros, no column beyond N is stored - the bytes after the output stay untouched."""
+    import torch
+    assert _plan(ttb, w_dtype, M, K, N)[:3] == [1, M, 0]
+    if K * N > 8 << 20:
+        w_dev, w_ref = make_big_case(ttb, orc, 11, K, N, w_dtype, slice_cols=N)
+        x = vectors.randn(12, (M, K), 1.0).bfloat16()
+    else:
+        x, w_dev, w_ref = make_case(ttb, orc, 11, M, K, N, w_dtype)
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    bias = vectors.randn(13, (1, N), 0.5).bfloat16()
+    b_dev = ttb.tilize(torch.cat([bias, torch.zeros(31, N, dtype=torch.bfloat16)]).cuda(), 1, 32, N)
+    guard = 4096
+    for flags in (0, cabi.MM_OUT_ROW_MAJOR):
+        out = torch.full((M * N + guard,), 7.0, dtype=torch.bfloat16, device="cuda")
+        nbytes = ttb.matmul_workspace_bytes(w_dtype, 1, M, K, N, flags)
+        ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        ttb.check(ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), w_dtype, b_dev.data_ptr(), out.data_ptr(), cabi.BFLOAT16, 1, M, K, N,
+                                      cabi.ACT_GELU, flags | cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None))
+        ttb.check(ttb.check_status(None))
+        assert bool((out[M * N:] == 7.0).all())
+        y = out[: M * N] if flags else ttb.untilize(out[: M * N].clone(), 1, M, N)
+        check(y.reshape(M, N), act_ref(x.float().cuda() @ w_ref.cuda() + bias.float().cuda(), cabi.ACT_GELU))
+        if nbytes:
+            assert int(ws[:65536].count_nonzero().item()) == 0
+
+
+@pytest.mark.parametrize("M,kinds", [(288, [(256, 0), (32, 0)]), (352, [(256, 0), (96, 0)]), (480, [(256, 0), (224, 0)]),
+                                     (544, [(512, 1), (32, 0)]), (736, [(640, 1), (96, 0)])])
+def test_row_counts_between_the_kernels_run_as_two_ranges(ttb, orc, M, kinds):
+    """Row counts no single tensor-core kernel takes (288-480; above 512 and not a multiple of 128) are served by two launches
+    over consecutive row ranges - none of them by the CUDA-core kernel - and match the fp32 reference."""
+    import torch
+    K, N, w_dtype = 1024, 512, cabi.BFLOAT8_B
+    plan = _plan(ttb, w_dtype, M, K, N)
+    assert plan[0] == 2 and [(plan[1], plan[2]), (plan[3], plan[4])] == kinds
+    assert _plan(ttb, w_dtype, M, K, N, cabi.MM_FORCE_GENERIC)[0] == 0
+    x, w_dev, w_ref = make_case(ttb, orc, 21, M, K, N, w_dtype)
+    for flags in (0, cabi.MM_A_ROW_MAJOR | cabi.MM_OUT_ROW_MAJOR):
+        a = x.cuda().reshape(-1) if flags else ttb.tilize(x.cuda(), 1, M, K)
+        y = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, act=cabi.ACT_RELU, flags=flags, out_fp32=True)
+        y = y if flags else ttb.untilize(y, 1, M, N)
+        check(y.reshape(M, N), torch.relu(x.float().cuda() @ w_ref.cuda()))

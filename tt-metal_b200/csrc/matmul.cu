@@ -53,6 +53,37 @@ int32_t validate(const void *a, int a_dtype, const void *w, int w_dtype, void *o
     return TTB_OK;
 }
 
+// Row ranges of one matmul and the tensor-core kernel that takes each: the decode kernels serve up to 256 rows, the prefill
+// kernel multiples of 128 from 512 up. Row counts in between run as two decode launches (256 rows + the rest); a ragged
+// count above 512 as the prefill kernel on the whole 128-row blocks plus a decode launch on the last 32 to 96 rows. (Rows are
+// contiguous in both layouts - a tile row of a tiled tensor is 32 whole rows - so a range is just an offset.)
+struct RowChunk {
+    int64_t row0, rows;
+    bool prefill;
+};
+int plan_rows(int w_dtype, int64_t rows, int64_t K, int64_t N, RowChunk (&out)[2]) {
+    if (decode_supported(w_dtype, rows, K, N)) {
+        out[0] = {0, rows, false};
+        return 1;
+    }
+    if (prefill_supported(w_dtype, rows, K, N)) {
+        out[0] = {0, rows, true};
+        return 1;
+    }
+    if (rows > 256 && rows < 512 && decode_supported(w_dtype, 256, K, N) && decode_supported(w_dtype, rows - 256, K, N)) {
+        out[0] = {0, 256, false};
+        out[1] = {256, rows - 256, false};
+        return 2;
+    }
+    const int64_t whole = rows / 128 * 128;
+    if (rows > 512 && rows != whole && prefill_supported(w_dtype, whole, K, N) && decode_supported(w_dtype, rows - whole, K, N)) {
+        out[0] = {0, whole, true};
+        out[1] = {whole, rows - whole, false};
+        return 2;
+    }
+    return 0;
+}
+
 }  // namespace
 }  // namespace ttb
 
@@ -63,9 +94,28 @@ extern "C" {
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags) {
     const int64_t rows = batch * M;
     if (flags & TTB_MM_FORCE_GENERIC) return 0;
-    if (decode_supported(w_dtype, rows, K, N)) return decode_workspace_bytes(rows, K, N);
-    if (prefill_supported(w_dtype, rows, K, N)) return prefill_workspace_bytes(rows, K);
-    return 0;
+    RowChunk chunks[2];
+    const int n = plan_rows(w_dtype, rows, K, N, chunks);
+    int64_t bytes = 0;
+    for (int i = 0; i < n; ++i) {
+        const int64_t b = chunks[i].prefill ? prefill_workspace_bytes(chunks[i].rows, K) : decode_workspace_bytes(chunks[i].rows, K, N);
+        bytes = b > bytes ? b : bytes;
+    }
+    return bytes;
+}
+
+/* Which kernels ttb_matmul would use: out[0] = launches (0: the shape-generic CUDA-core kernel), then per launch its rows
+ * and 1 for the prefill kernel, 0 for a decode kernel. */
+int32_t ttb_matmul_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags, int64_t *out, int32_t out_len) {
+    if (!out || out_len < 5) return fail(TTB_E_INVALID, "ttb_matmul_plan: needs room for 5 values");
+    RowChunk chunks[2];
+    const int n = (flags & TTB_MM_FORCE_GENERIC) ? 0 : plan_rows(w_dtype, batch * M, K, N, chunks);
+    out[0] = n;
+    for (int i = 0; i < 2; ++i) {
+        out[1 + 2 * i] = i < n ? chunks[i].rows : 0;
+        out[2 + 2 * i] = i < n && chunks[i].prefill ? 1 : 0;
+    }
+    return TTB_OK;
 }
 
 int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, const void *bias, void *out,
@@ -74,15 +124,25 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
     if (int32_t rc = validate(a, a_dtype, w, w_dtype, out, out_dtype, batch, M, K, N, act)) return rc;
     const int64_t rows = batch * M;  // tiled [batch, M, K] with M % 32 == 0 is the same buffer as tiled [batch*M, K]
     auto s = (cudaStream_t)stream;
-    if (!(flags & TTB_MM_FORCE_GENERIC) && decode_supported(w_dtype, rows, K, N))
-        return launch_matmul_decode(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes,
-                                    (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false, s, nullptr, nullptr);
-    if (!(flags & TTB_MM_FORCE_GENERIC) && prefill_supported(w_dtype, rows, K, N)) {
-        int *status = nullptr;
-        if (int32_t rc = status_word_address(&status)) return rc;
-        return launch_matmul_prefill(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, workspace, workspace_bytes, status, s);
+    RowChunk chunks[2];
+    const int n = (flags & TTB_MM_FORCE_GENERIC) ? 0 : plan_rows(w_dtype, rows, K, N, chunks);
+    if (n == 0) return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
+    const int64_t out_elem = out_dtype == TTB_FLOAT32 ? 4 : 2;
+    for (int i = 0; i < n; ++i) {
+        const void *ai = static_cast<const uint8_t *>(a) + chunks[i].row0 * K * 2;
+        void *oi = static_cast<uint8_t *>(out) + chunks[i].row0 * N * out_elem;
+        int32_t rc;
+        if (chunks[i].prefill) {
+            int *status = nullptr;
+            if ((rc = status_word_address(&status))) return rc;
+            rc = launch_matmul_prefill(ai, w, w_dtype, bias, oi, out_dtype, chunks[i].rows, K, N, act, flags, workspace, workspace_bytes, status, s);
+        } else {
+            rc = launch_matmul_decode(ai, w, w_dtype, bias, oi, out_dtype, chunks[i].rows, K, N, act, flags, workspace, workspace_bytes,
+                                      (flags & TTB_MM_WORKSPACE_ZEROED) != 0, /*compact=*/false, s, nullptr, nullptr);
+        }
+        if (rc) return rc;
     }
-    return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
+    return TTB_OK;
 }
 
 int32_t ttb_bmm(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, void *out, int32_t out_dtype, int64_t batch, int64_t M,

@@ -45,9 +45,14 @@ int32_t status_word_address(int **out) {
 // Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
 static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32; }
 
+// 128-column tiles of a weight of N columns. The last one may hold 32, 64 or 96 columns (one tile row per block only: its
+// missing packed tiles read as zeros and the epilogue stores no column beyond N).
+static int tiles128(int64_t N) { return (int)((N + BN - 1) / BN); }
+static bool columns_ok(int64_t rows, int64_t N) { return N > 0 && N % 32 == 0 && (N % BN == 0 || decode_rows_per_block(rows) == 32); }
+
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && N % BN == 0 && (N / BN) * (rows / 32) <= kSyncInt0;
+           K % BK == 0 && columns_ok(rows, N) && tiles128(N) * (rows / 32) <= kSyncInt0;
 }
 
 // ---- streamed decomposition (matmul_decode_stream.cu) ----------------------------------------------------------------
@@ -61,8 +66,20 @@ struct StreamPlan {
     int slots;              // partial-sum slots
     bool shared_tiles;      // some tile's K range is shared by several blocks: scratch needed
 };
-// One persistent block per SM of a B200. The sizes derived from it (scratch) do not depend on the device at hand.
-static constexpr int kStreamBlocks = 148;
+// One persistent block per multiprocessor of the current device (read once per process; 148, a B200's count, where no device
+// can be asked - the plan and workspace queries also work without a GPU).
+static int stream_blocks() {
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+            cached = sms;
+        else
+            cached = 148;
+        (void)cudaGetLastError();
+    }
+    return cached;
+}
 static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a piece of a tile shorter than this
 
 // Picks the cheaper of two decompositions by a small cost model in units of one K-block's streaming time (~0.155 us):
@@ -73,11 +90,12 @@ static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a pi
 //    then has up to two shared segments, ~35 each for the exchange and the pipeline bubble around it.
 // Both pay ~25 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama / Mistral / Falcon shapes.
 static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N) {
+    const int kStreamBlocks = stream_blocks();
     StreamPlan sp;
     sp.nb = decode_rows_per_block(rows);
     sp.rchunks = (int)(rows / sp.nb);
     sp.tiles_row = 0;
-    for (int j = 0; j < nprob; ++j) sp.tiles_row += (int)(N[j] / BN);
+    for (int j = 0; j < nprob; ++j) sp.tiles_row += tiles128(N[j]);
     sp.tiles_total = sp.tiles_row * sp.rchunks;
     const int nkb = (int)(K / BK);
     sp.gran = kStreamGran;
@@ -130,8 +148,8 @@ bool decode_supported_multi(int w_dtype, int64_t rows, int64_t K, int nprob, con
     if (nprob < 1 || nprob > TTB_MAX_GROUP) return false;
     int64_t tiles = 0;
     for (int j = 0; j < nprob; ++j) {
-        if (N[j] <= 0 || N[j] % BN) return false;
-        tiles += N[j] / BN;
+        if (!columns_ok(rows, N[j])) return false;
+        tiles += tiles128(N[j]);
     }
     return tiles * (rows / 32) <= kSyncInt0;
 }
@@ -139,7 +157,7 @@ bool decode_supported_multi(int w_dtype, int64_t rows, int64_t K, int nprob, con
 // Accumulate mode needs rows * (sum of N) fp32 inside the fixed 16 MiB region; larger outputs use ordered mode.
 static bool stream_accumulate_ok(int64_t rows, int nprob, const int64_t *N) {
     int64_t n = 0;
-    for (int j = 0; j < nprob; ++j) n += N[j];
+    for (int j = 0; j < nprob; ++j) n += (int64_t)tiles128(N[j]) * BN;
     return rows * n * 4 <= kAccumBytes;
 }
 static int64_t stream_partial_bytes(const StreamPlan &sp) { return (int64_t)sp.slots * BN * sp.nb * 4; }
@@ -190,8 +208,8 @@ static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_byt
         p.outv[j] = out[j];
         p.Nv[j] = N[j];
         p.tstart[j] = t0;
-        t0 += (int)(N[j] / BN);
-        nsum += N[j];
+        t0 += tiles128(N[j]);
+        nsum += (int64_t)tiles128(N[j]) * BN;
     }
     p.tstart[nprob] = t0;
     p.sk_grid = sp.grid; p.sk_gran = sp.gran; p.sk_upt = sp.upt;
@@ -208,6 +226,7 @@ static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_byt
         p.gated = 1;
     }
     if (gather) {
+        if (N[0] % BN) return fail(TTB_E_UNSUPPORTED, "ttb_matmul: a gathered output needs a column count that is a multiple of 128");
         p.ranks = gather->ranks; p.rank = gather->rank;
         p.outv[0] = gather->out[gather->rank];
         p.out_n0 = (int64_t)gather->rank * N[0]; p.out_N = (int64_t)gather->ranks * N[0]; p.out_Nt = (int)(p.out_N / 32);
@@ -255,6 +274,9 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
     }
     // the weights of 32-row blocks reach the MMA through tensor memory; those of larger row blocks (and of any on request)
     // through shared memory
+    for (int j = 0; j < nprob; ++j)
+        if (N[j] % BN && (flags & TTB_MM_DECODE_SMEM_OPERAND))
+            return fail(TTB_E_UNSUPPORTED, "ttb_matmul: the shared-memory-operand kernel needs column counts that are multiples of 128");
     if (nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND))
         return launch_decode_tmem(&p, 1, w_dtype, p.counters ? p.counters + kSyncInt0 : nullptr, overlap, stream);
     return launch_decode_stream(p, w_dtype, nb, overlap, stream);
@@ -481,7 +503,7 @@ static int32_t validate_multi(const char *who, const void *a, int32_t a_dtype, i
             return fail(TTB_E_INVALID, "%s: tensors must be 16-byte aligned", who);
     }
     if (!decode_supported_multi(w_dtype, rows, K, count, N))
-        return fail(TTB_E_UNSUPPORTED, "%s: decode shapes only (bfloat8_b / bfloat4_b weights, at most 256 rows, every N a multiple of 128)", who);
+        return fail(TTB_E_UNSUPPORTED, "%s: decode shapes only (bfloat8_b / bfloat4_b weights, at most 256 rows, every N a multiple of 128 - of 32 for row counts that are odd multiples of 32)", who);
     if (gather) {
         if (gather->ranks < 2 || gather->ranks > TTB_MAX_RANKS || gather->rank < 0 || gather->rank >= gather->ranks)
             return fail(TTB_E_INVALID, "%s: ranks must be 2..%d and rank inside it", who, TTB_MAX_RANKS);

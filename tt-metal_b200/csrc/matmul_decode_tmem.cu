@@ -410,6 +410,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     // every 16-lane half (expand_tile4).
     const int col_in_quad = FMT == TTB_BFLOAT8_B ? lane : (lane & 16) + ((lane & 7) << 1) + ((lane >> 3) & 1);
     const int64_t n = (int64_t)tr.nt * BN + quad * 32 + col_in_quad;
+    const bool col_ok = n < p.Nv[tr.prob];   // (the last tile of a weight may hold fewer than 128 columns)
     // (gated pair: both weights' tiles lead to the one product tensor, which takes the first weight's place)
     const bool gathered = p.ranks > 1 && (tr.prob == 0 || p.gated);
     const int gate_pair = tr.rchunk * p.tstart[1] + tr.nt;
@@ -534,10 +535,10 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                 }
             }
             if (!p.gated) {
-                finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+                if (col_ok) finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
             } else {
                 // gated pair: bias (and, for the first weight, the activation) in fp32, left for whoever finishes the pair
-                const float bias = ov.bias ? bias_at(ov.bias, n) : 0.0f;
+                const float bias = (ov.bias && col_ok) ? bias_at(ov.bias, n) : 0.0f;
                 float4 *dst = reinterpret_cast<float4 *>(p.gate + ((int64_t)(gate_pair * 2 + tr.prob) * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = tr.prob == 0 ? apply_activation(v[j] + bias, p.act) : v[j] + bias;
@@ -578,7 +579,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                     const float4 x = __ldcg(g0 + j), y = __ldcg(g1 + j);
                     v[4 * j] = x.x * y.x; v[4 * j + 1] = x.y * y.y; v[4 * j + 2] = x.z * y.z; v[4 * j + 3] = x.w * y.w;
                 }
-                finish_and_store_t<TTB_ACT_NONE>(p, og, v, row0, col0, n, stage);
+                if (col_ok) finish_and_store_t<TTB_ACT_NONE>(p, og, v, row0, col0, n, stage);
             }
             if (tid == 0) p.gate_counters[gate_pair] = 0;
         }

@@ -467,7 +467,8 @@ int32_t launch_matmul_prefill(const void *a, const void *w, int w_dtype, const v
     // Whole waves: one block per SM runs at a time, so a handful of blocks left over after the last full wave would cost a
     // whole block time (8 of 896 blocks on the Llama MLP shape: 14 %). The column blocks that do not fill a wave are
     // given to a second launch with quarter-size blocks (128 x 128), whose tail is a quarter as long.
-    constexpr int kSms = 148;
+    int dev = 0, kSms = 148;   // multiprocessors of the device at hand
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&kSms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || kSms <= 0) kSms = 148;
     const int64_t nblocks = (int64_t)grid.x * grid.y;
     if (H == 2 && nblocks > kSms && nblocks % kSms != 0 && (nblocks % kSms) * 4 < kSms) {
         const unsigned cols_main = (unsigned)((nblocks / kSms) * kSms / grid.x);   // column blocks of the main launch
