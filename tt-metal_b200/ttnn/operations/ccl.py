@@ -61,7 +61,12 @@ def _fused_linear(input_tensor, weights, biases, activation, gather_first, ring_
                 if mesh.pending == (in_ring, in_slot):
                     mesh.pending = None
         if gather_first and mesh.pending is not None:
-            mesh.pending[0].stream_wait(mesh.pending[1])   # keeps the ranks within one gather of each other
+            # keeps the ranks within one gather of each other: the launch itself waits for the previous gather where it has
+            # no gathered input of its own to wait for (its weights stream meanwhile), else the stream is held
+            if wait_slot < 0 and mesh.pending[0] is ring:
+                wait_slot = mesh.pending[1]
+            else:
+                mesh.pending[0].stream_wait(mesh.pending[1])
             mesh.pending = None
     native = ring.native if (ring is not None and (gather_first or wait_slot >= 0)) else None
     outs, slot = _ttnn.linear_multi(x, [_local(w) for w in weights],
