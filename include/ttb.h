@@ -6,6 +6,9 @@
  * description of the last failure on the calling thread is available from ttb_last_error().
  * Device pointers are caller-owned; every compute call is asynchronous on the given CUDA stream
  * (a cudaStream_t passed as void*; NULL = the default stream) unless stated otherwise.
+ * Threads: one host thread drives the library at a time. The kernels' one-time set-up (function attributes, driver entry
+ * points, the NCCL table, the multiprocessor count) and the launch descriptors are filled on first use without locks; callers
+ * that launch from several threads serialise the calls themselves.
  *
  * Data layouts (identical to the reference's buffers, so bytes can be exchanged with it):
  *   - "tiled" = TILE_LAYOUT: tiles of 32x32 elements ordered row-major over (outer*H/32, W/32);

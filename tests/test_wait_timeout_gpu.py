@@ -74,3 +74,25 @@ def test_matmul_waiting_for_peers_gives_up_and_the_next_one_is_right(ttb, orc, s
     assert ttb.check_status(None) == 0
     check(ttb.untilize(out2, 1, M, N).reshape(M, N), x.float() @ w_ref)
     assert int(ws[: 65536 + (16 << 20)].count_nonzero().item()) == 0
+
+
+def test_host_layer_raises_on_a_timeout_and_clears_its_scratch(ttb, short_waits):
+    """ttnn.synchronize_device / ttnn.to_torch read the status word: after a wait that ran out they raise (once), the device's
+    matmul scratch is zero again, and the next ttnn.linear is right. (libttb is loaded once per process: the status word the
+    C-ABI call below raises is the one the host layer reads.)"""
+    import torch
+    import ttnn
+    device = ttnn.open_device(device_id=0)
+    torch.manual_seed(3)
+    x = torch.randn(1, 1, 32, 2048).bfloat16()
+    w = torch.randn(2048, 512) * 0.03
+    tx = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
+    tw = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+    want = ttnn.to_torch(ttnn.linear(tx, tw)).float()          # (split over K: uses the device's scratch)
+    counters, wt = _dead_gather_point()
+    ttb.check(ttb.cdll.ttb_peer_wait(ctypes.byref(wt), None))
+    with pytest.raises(RuntimeError, match="ran out"):
+        ttnn.synchronize_device(device)
+    ttnn.synchronize_device(device)                              # reported once
+    got = ttnn.to_torch(ttnn.linear(tx, tw)).float()
+    assert torch.equal(got, want)

@@ -211,11 +211,13 @@ __device__ __forceinline__ bool stream_epilogue(const DecodeArgs &p, const EpiCt
         tc_fence_before_sync();
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        if (tid == 0) *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
+        if (tid == 0) {
+            *c.last_flag = (atomicAdd(p.counters + s.tile, 1) == contributors - 1) ? 1 : 0;
+            __threadfence();   // acquire side: what the other blocks published before their tickets is visible to every
+                               // thread that passes the next barrier
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         finished = *c.last_flag != 0;
-        // No fence on this side: the other blocks' partial sums were performed in L2 before their tickets (their fences),
-        // thread 0 has its ticket's value, the barrier orders this thread after it, and the loads below bypass L1 (.cg).
     }
     // phase 2: whoever holds the complete sum - the only block of an unshared tile, or the last arriver - finishes the tile
     if (finished && (eok || contributors > 1)) {

@@ -24,6 +24,8 @@ std::shared_ptr<DeviceBuffer> upload(Device *dev, const void *src, int64_t bytes
 void download(void *dst, const DeviceBuffer &b, int64_t bytes) {
     check(ttb_memcpy_d2h(dst, b.ptr, (size_t)bytes, nullptr), "ttnn: device to host copy");
     check(ttb_stream_synchronize(nullptr), "ttnn: device to host copy");
+    // what is handed to the host has been computed without a wait running out
+    if (b.device) b.device->check_device_status("ttnn: device to host copy");
 }
 
 Tensor to_host_storage(const Tensor &t) {

@@ -92,9 +92,23 @@ std::map<int, std::unique_ptr<Device>> g_pool;
 }  // namespace
 
 void Device::make_current() const { check(ttb_set_device(id_), "ttnn.open_device"); }
-void Device::synchronize() const {
+void Device::synchronize() {
     make_current();
     check(ttb_device_synchronize(), "ttnn.synchronize_device");
+    check_device_status("ttnn.synchronize_device");
+}
+void Device::check_device_status(const char *what) {
+    const int32_t rc = ttb_check_status(nullptr);
+    if (rc == TTB_OK) return;
+    const std::string message = ttb_last_error();
+    if (rc == TTB_E_TIMEOUT && workspace_) {
+        ttb_memset(workspace_, 0, (size_t)workspace_bytes_, nullptr);
+        ttb_stream_synchronize(nullptr);
+    }
+    throw_error(std::string(what) + ": " + message +
+                (rc == TTB_E_TIMEOUT ? " (the matmul scratch was cleared; results since the last check are invalid, and a mesh whose gather "
+                                       "timed out must be reopened)"
+                                     : ""));
 }
 void *Device::workspace(int64_t bytes) {
     if (bytes <= workspace_bytes_) return workspace_;

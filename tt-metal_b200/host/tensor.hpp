@@ -97,7 +97,11 @@ class Device {
     explicit Device(int id) : id_(id) {}
     int id() const { return id_; }
     void make_current() const;
-    void synchronize() const;
+    void synchronize();
+    // Reads (and clears) the device status word after the default stream has drained. A bounded device-side wait that ran
+    // out (a peer that never stored its slice, a lost barrier arrival) left counters and partial sums behind in the
+    // scratch: it is cleared here, so that later matmuls start from zeros, and the error is raised.
+    void check_device_status(const char *what);
     // Grow-only scratch used by matmul's split-K reduction, zeroed when (re)allocated.
     void *workspace(int64_t bytes);
     ~Device();
