@@ -617,6 +617,38 @@ def run_gpu_arm(args):
                 "avg_launch_us": R.ms_mm * 1e3 / R.launches_per_step, "clocks": window_clocks or R.clocks}
 
     # ============================================================================================================
+    if args.workload == "c1":
+        # C1 on its own: tensor conversion (ttnn.from_torch's pack, ttnn.to_torch's unpack) in both block-float formats;
+        # the headline is bfloat8_b packing, `e2e` the same through ttnn.from_torch with the host copy inside.
+        if G != 1:
+            raise SystemExit("workload c1 is a single-GPU configuration")
+        with ClockSampler(local_rank, enabled=True) as clocks:
+            conv = {f"{d}_{n}": time_conversion(f, d, clocks) for f, n in ((BFP8, "bfp8"), (BFP4, "bfp4")) for d in ("pack", "unpack")}
+            host = (torch.randn(4096, 4096, generator=torch.Generator().manual_seed(0)) * 0.02).pin_memory()
+            for _ in range(3):
+                t = ttnn.from_torch(host, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                t = ttnn.from_torch(host, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
+            torch.cuda.synchronize()
+            e2e_s = (time.perf_counter() - t0) / args.steps
+        head = conv["pack_bfp8"]
+        print(json.dumps({
+            "metric": "bfloat8_b pack GB/s (ttnn.from_torch of fp32 [1,1,4096,4096], TILE_LAYOUT)", "value": head["value"], "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["us_per_launch"] / 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "tensor conversion: fp32 [1,1,4096,4096] N(0, 0.02) -> bfloat8_b tiles, four source buffers in rotation (256 MB, larger than L2)",
+                       "timed": "CUDA-graph replay of 20 launches x 400"},
+            "clocks": head["clocks"],
+            "e2e": {"value": head["algorithmic_bytes"] / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4096 * 4096 * 4, "d2h_bytes_per_step": 0,
+                    "ms_per_step": e2e_s * 1e3, "api": "ttnn.from_torch(pinned fp32, dtype=bfloat8_b, layout=TILE_LAYOUT, device)"},
+            "gpu_launches": 20 * 400,
+            "roofline": {"bound": "hbm", "achieved": head["value"], "peak": head["value"] / head["frac"], "unit": "GB/s", "frac": head["frac"],
+                         "traffic": None, "peak_kind": head["peak_kind"], "kernel": "pack_rowmajor_kernel"},
+            "extra": conv}), flush=True)
+        return
+
     with ClockSampler(local_rank, enabled=(rank == 0)) as clocks:
         wl = Workload(args.workload, G)
         R = time_workload(wl, args.steps, args.warmup, clocks)
@@ -758,9 +790,9 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="one launch per weight instead of one per group of weights that share an activation")
     ap.add_argument("--no-extra", action="store_true", help="skip the C1-C4 measurements that follow the headline at 1 GPU")
     ap.add_argument("--no-overlap", action="store_true", help="launch every matmul after the previous one has fully completed")
-    ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2"],
+    ap.add_argument("--workload", default="c5", choices=["c5", "c4", "c3", "c2", "c1"],
                     help="c5 = Llama-2-70B TP decode sweep (default, the headline), c4 = Llama-2-70B MLP prefill matmul, "
-                         "c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear")
+                         "c3 = Mistral-7B sweep, c2 = Falcon-7B decode linear, c1 = tensor conversion")
     ap.add_argument("--max-seconds", type=int, default=1500, help="watchdog: the process exits with status 3 after this long")
     args = ap.parse_args()
 
