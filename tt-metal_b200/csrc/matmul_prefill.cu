@@ -209,7 +209,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
 
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles and activation blocks -> shared memory ----------------
-        if (lane == 0) {
+        // (the whole warp walks the loop, so that addresses stay warp-uniform values; one elected lane issues)
+        {
+            const bool leader = elect_one();
             const uint8_t *wsrc = p.w + ((p.col_base >> 5) + (int64_t)ntile * 4 * H) * TB;
             const int64_t w_step = (int64_t)p.Nt * TB;
             // this block's activation sub-blocks inside the re-laid buffer (laid out for row blocks of p.x_R sub-blocks)
@@ -221,30 +223,34 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
             uint32_t phs = 0, phx = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);  // stages in this group (the last one may be short)
-                if (!mbar_wait(empty_x(gx), phx ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
-                mbar_arrive_expect_tx(full_x(gx), r * L::kActStageBytes);
-                if (x_contiguous) {
-                    // the r activation blocks of the group are adjacent in the re-laid buffer
-                    bulk_g2s_plain(sbase + L::x + gx * kGroup * L::kActStageBytes, xsrc, r * L::kActStageBytes, full_x(gx));
-                } else {
-                    for (int j = 0; j < r; ++j)
-                        bulk_g2s_plain(sbase + L::x + (gx * kGroup + j) * L::kActStageBytes, xsrc + j * x_stage_step, L::kActStageBytes,
-                                       full_x(gx));
+                if (!__all_sync(0xffffffffu, mbar_wait(empty_x(gx), phx ^ 1, abort_flag, p.status, 21))) { ok = false; break; }
+                if (leader) {
+                    mbar_arrive_expect_tx(full_x(gx), r * L::kActStageBytes);
+                    if (x_contiguous) {
+                        // the r activation blocks of the group are adjacent in the re-laid buffer
+                        bulk_g2s_plain(sbase + L::x + gx * kGroup * L::kActStageBytes, xsrc, r * L::kActStageBytes, full_x(gx));
+                    } else {
+                        for (int j = 0; j < r; ++j)
+                            bulk_g2s_plain(sbase + L::x + (gx * kGroup + j) * L::kActStageBytes, xsrc + j * x_stage_step, L::kActStageBytes,
+                                           full_x(gx));
+                    }
                 }
                 xsrc += r * x_stage_step;
-                if (!mbar_wait(empty_pk(gs), phs ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
-                mbar_arrive_expect_tx(full_pk(gs), r * L::kPkStageBytes);
-                for (int j = 0; j < r; ++j) {
-                    bulk_g2s_plain(sbase + L::pk + (gs * kGroup + j) * L::kPkStageBytes, wsrc, L::kPkStageBytes, full_pk(gs));
-                    wsrc += w_step;
+                if (!__all_sync(0xffffffffu, mbar_wait(empty_pk(gs), phs ^ 1, abort_flag, p.status, 22))) { ok = false; break; }
+                if (leader) {
+                    mbar_arrive_expect_tx(full_pk(gs), r * L::kPkStageBytes);
+                    for (int j = 0; j < r; ++j)
+                        bulk_g2s_plain(sbase + L::pk + (gs * kGroup + j) * L::kPkStageBytes, wsrc + j * w_step, L::kPkStageBytes, full_pk(gs));
                 }
+                wsrc += r * w_step;
                 if (++gs == kPkGroups) { gs = 0; phs ^= 1; }
                 if (++gx == kActGroups) { gx = 0; phx ^= 1; }
             }
         }
     } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // ---------------- MMA issuer (warp-uniform, one elected lane issues) ----------------
+        {
+            const bool leader = elect_one();
             constexpr uint32_t idesc = instr_desc_bf16_f32(BMS, BNB, /*a_mn_major=*/false, /*b_mn_major=*/true);
             const uint64_t x_desc0 = smem_desc_noswizzle(sbase + L::x, kX_LBO, kX_SBO);
             const uint64_t w_desc0 = smem_desc_noswizzle(sbase + L::w, kW_LBO, kW_SBO);
@@ -255,9 +261,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
             uint32_t phw = 0, phx = 0;
             for (int g = 0; g < ngroups; ++g) {
                 const int r = min(kGroup, nit - g * kGroup);
-                for (int j = r * H; j < C::kMembers; ++j) mbar_arrive(full_w(gw));  // stand in for the stages a short last group lacks
-                if (!mbar_wait(full_x(gx), phx, abort_flag, p.status, 23)) { ok = false; break; }
-                if (!mbar_wait(full_w(gw), phw, abort_flag, p.status, 24)) { ok = false; break; }
+                if (leader)
+                    for (int j = r * H; j < C::kMembers; ++j) mbar_arrive(full_w(gw));  // stand in for the stages a short last group lacks
+                if (!__all_sync(0xffffffffu, mbar_wait(full_x(gx), phx, abort_flag, p.status, 23) && mbar_wait(full_w(gw), phw, abort_flag, p.status, 24))) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t x_lo = x_lo0 + (uint32_t)gx * ((kGroup * L::kActStageBytes) >> 4);
                 const uint32_t w_lo = w_lo0 + (uint32_t)gw * ((kGroup * kWStageBytes) >> 4);
@@ -268,19 +274,21 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_prefill_kernel(const Prefi
                         for (int k16 = 0; k16 < BK / 16; ++k16) {
 #pragma unroll
                             for (int rr = 0; rr < R; ++rr)
-                                mma_bf16_ss(tmem_base + (uint32_t)(rr * BNB),
+                                if (leader) mma_bf16_ss(tmem_base + (uint32_t)(rr * BNB),
                                             mk(x_lo + ((j * L::kActStageBytes + rr * kActSubBytes + k16 * 2 * kX_LBO) >> 4), x_hi),
                                             mk(w_lo + ((j * kWStageBytes + k16 * 2 * kW_LBO) >> 4), w_hi), idesc,
                                             j > 0 || k16 > 0 || g > 0);
                         }
                     }
                 }
-                mma_commit(empty_w(gw));
-                mma_commit(empty_x(gx));
+                if (leader) {
+                    mma_commit(empty_w(gw));
+                    mma_commit(empty_x(gx));
+                }
                 if (++gw == kWGroups) { gw = 0; phw ^= 1; }
                 if (++gx == kActGroups) { gx = 0; phx ^= 1; }
             }
-            if (ok) mma_commit(accum_bar);
+            if (ok && leader) mma_commit(accum_bar);
         }
     } else if ((warp & 3) != 0) {
         // ---------------- expand warps: packed codes -> bf16 weights in shared memory (B operand) ----------------

@@ -71,6 +71,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// One lane of a converged warp: the lane that issues for warp-uniform single-issuer roles (the others follow the same
+// control flow, so addresses and descriptors stay uniform-datapath values).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- proxies and fences ------------------------------------------------------------------------
 // Orders this thread's shared-memory writes (generic proxy) before later asynchronous-proxy reads
 // (tcgen05.mma operand fetches, bulk copies).
