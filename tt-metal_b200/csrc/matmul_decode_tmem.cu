@@ -399,7 +399,8 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     // every 16-lane half (expand_tile4).
     const int col_in_quad = FMT == TTB_BFLOAT8_B ? lane : (lane & 16) + ((lane & 7) << 1) + ((lane >> 3) & 1);
     const int64_t n = (int64_t)tr.nt * BN + quad * 32 + col_in_quad;
-    const bool col_ok = n < p.Nv[tr.prob];   // (the last tile of a weight may hold fewer than 128 columns)
+    // (the last tile of a weight may hold fewer than 128 columns: no column beyond N is stored)
+#define TTB_COL_OK (n < p.Nv[tr.prob])
     // (gated pair: both weights' tiles lead to the one product tensor, which takes the first weight's place)
     const bool gathered = p.ranks > 1 && (tr.prob == 0 || p.gated);
     const int gate_pair = tr.rchunk * p.tstart[1] + tr.nt;
@@ -487,21 +488,20 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
             } else if (partials) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                // up to four blocks' partials per round: all loads of a round are issued before the first add; the adds
+                // up to three blocks' partials per round: all loads of a round are issued before the first add; the adds
                 // stay in block order
 #pragma unroll 1
-                for (int c0 = 0; c0 < contributors; c0 += 4) {
+                for (int c0 = 0; c0 < contributors; c0 += 3) {
                     const float4 *src = reinterpret_cast<const float4 *>(
                         p.partial + ((int64_t)(s.slot0 + c0) * BN + quad * 32 + lane) * NB + col0);
                     constexpr int64_t kSlot = (int64_t)BN * NB / 4;   // float4 per slot
-                    const int cnt = min(4, contributors - c0);
-                    float4 x0[4], x1[4], x2[4], x3[4];
+                    const int cnt = min(3, contributors - c0);
+                    float4 x0[4], x1[4], x2[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         x0[j] = __ldcg(src + j);
                         x1[j] = cnt > 1 ? __ldcg(src + kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                         x2[j] = cnt > 2 ? __ldcg(src + 2 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        x3[j] = cnt > 3 ? __ldcg(src + 3 * kSlot + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                     auto add = [&](const float4 (&x)[4]) {
 #pragma unroll
@@ -512,7 +512,6 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                     add(x0);
                     if (cnt > 1) add(x1);
                     if (cnt > 2) add(x2);
-                    if (cnt > 3) add(x3);
                 }
             } else {
                 float4 *acc = reinterpret_cast<float4 *>(acc_tile + (quad * 32 + lane) * NB + col0);
@@ -524,10 +523,10 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                 }
             }
             if (!p.gated) {
-                if (col_ok) finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
+                if (TTB_COL_OK) finish_and_store<NB>(p, ov, v, row0, col0, n, stage);
             } else {
                 // gated pair: bias (and, for the first weight, the activation) in fp32, left for whoever finishes the pair
-                const float bias = (ov.bias && col_ok) ? bias_at(ov.bias, n) : 0.0f;
+                const float bias = (ov.bias && TTB_COL_OK) ? bias_at(ov.bias, n) : 0.0f;
                 float4 *dst = reinterpret_cast<float4 *>(p.gate + ((int64_t)(gate_pair * 2 + tr.prob) * BN + quad * 32 + lane) * NB + col0);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = tr.prob == 0 ? apply_activation(v[j] + bias, p.act) : v[j] + bias;
@@ -568,7 +567,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
                     const float4 x = __ldcg(g0 + j), y = __ldcg(g1 + j);
                     v[4 * j] = x.x * y.x; v[4 * j + 1] = x.y * y.y; v[4 * j + 2] = x.z * y.z; v[4 * j + 3] = x.w * y.w;
                 }
-                if (col_ok) finish_and_store_t<TTB_ACT_NONE>(p, og, v, row0, col0, n, stage);
+                if (TTB_COL_OK) finish_and_store_t<TTB_ACT_NONE>(p, og, v, row0, col0, n, stage);
             }
             if (tid == 0) p.gate_counters[gate_pair] = 0;
         }
@@ -590,6 +589,7 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
     }
     if (tid == 0) { TL(6, seg_idx); }
     return eok;
+#undef TTB_COL_OK
 }
 
 template <int FMT, int S>
