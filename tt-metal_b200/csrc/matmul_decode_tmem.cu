@@ -1,5 +1,7 @@
-// Streamed decode matmul for bfloat8_b weights, weight operand through tensor memory, persistent form:
-//   out_j[rows, N_j] = act(a[rows, K] x W_j[K, N_j] + bias_j)   for up to four weights W_j that share the activation.
+// Streamed decode matmul for bfloat8_b / bfloat4_b weights and 32 activation rows per block, weight operand through
+// tensor memory, persistent form:
+//   out_j[rows, N_j] = act(a[rows, K] x W_j[K, N_j] + bias_j)   for up to four weights W_j that share the activation,
+// optionally several such stages in one launch, the product of a gated pair, and the all-gather of the first result.
 //
 // Same work decomposition as matmul_decode_stream.cu (one list of 128-column tiles over all weights of the launch, at most
 // one persistent block per SM working through (tile, K range) segments, partial sums of shared tiles exchanged through
@@ -8,7 +10,7 @@
 //
 // Why tensor memory: expanded to bf16 a weight is two bytes; writing it to shared memory and letting the MMA fetch it
 // back costs four bytes of shared-memory traffic per packed byte that HBM delivers. Here a packed tile crosses shared
-// memory once (bulk copy in, ldmatrix out) and the bf16 values go registers -> tensor memory -> MMA:
+// memory once (tensor-map copy in, ldmatrix out) and the bf16 values go registers -> tensor memory -> MMA:
 //   * ldmatrix.m16n16.trans.b8 reads a 16x16 face of 8-bit codes transposed, so that a lane holds four consecutive K
 //     values of one weight column - the order the MMA's A operand wants (TMEM lane = column n, TMEM column = K pair);
 //   * the codes become bf16 with one byte-permute, one mask and one packed multiply per pair ((sign << 15) | mantissa is,
@@ -18,15 +20,16 @@
 //     the activations (B) from shared memory.
 //
 // Roles (20 warps). A warp can only touch the 32 TMEM lanes of its quadrant (warp % 4) = one of the four packed tiles of
-// a stage, so the expand warps 0..11 form three teams of four; team t expands every third group of four K blocks.
-// They do nothing else: no global loads, no epilogue. Warps 12..15 run the epilogues (one per TMEM lane quadrant) on one
-// of two accumulator sets while the MMAs of the next segment fill the other. Warp 16 (one thread) streams the packed
-// tiles with one tensor-map copy per group; warp 19 (one thread) streams the activations of the same group with another
-// tensor-map copy that delivers them in the MMA's swizzled K-major operand layout; warps 17 and 18 (one thread each)
-// issue the MMAs of the first and second K step of every stage into their own accumulators.
-// One ring of eight groups carries everything a group needs - packed tiles and activations in shared memory, expanded
-// weights in tensor memory. A slot's packed tiles are released as soon as they are expanded (the next copy from HBM
-// starts then); its activations and its place in tensor memory by the commit of the group's MMAs.
+// a K block, so the expand warps 0..11 form three teams of four; team t expands every third group of four K blocks, two
+// tiles at a time. They do nothing else: no global loads, no epilogue. Warps 12..15 run the epilogues (one per TMEM lane
+// quadrant) on one of two accumulator sets while the MMAs of the next segment fill the other. Warp 16 streams the packed
+// tiles with one tensor-map copy per group; warp 19 streams the activations of the same group with another tensor-map
+// copy that delivers them in the MMA's swizzled K-major operand layout; warps 17 and 18 issue the MMAs, taking alternate
+// pairs of groups, each into its own accumulator. These four warps run warp-uniform: all lanes walk the work list, one
+// elected lane issues, so that addresses and descriptors are uniform-datapath values (with a single active lane every
+// MMA and copy paid for moving its operands between register files: 17 % of the kernel's time).
+// Three rings: packed tiles in shared memory (released as soon as they are expanded: the next copy from HBM starts
+// then), expanded weights in tensor memory and activations in shared memory (released by the commit of the pair's MMAs).
 // Every wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include "decode_common.cuh"
 

@@ -1,18 +1,20 @@
 // Compute-bound matmul for large row counts (prefill): out[rows, N] = act(a[rows, K] x W[K, N] + bias) with W in
 // packed bfloat8_b / bfloat4_b tiles and rows a multiple of 128.
 //
-// One block owns a [128*R rows] x [128 columns] output tile (R = 2 when the row count allows), held as R fp32
-// accumulators of 128 lanes x 128 columns in tensor memory, and walks K in blocks of 32:
+// One block owns a [128*R rows] x [128*H columns] output tile (R = H = 2 when the shape allows: 256 x 256, all of tensor
+// memory as two fp32 accumulators of 128 lanes x 256 columns; else 256 x 128 or 128 x 128) and walks K in blocks of 32:
 //   * the activations are first re-laid once per call (relayout_activations below) into blocks that already have the
-//     tensor cores' canonical K-major operand layout, so that a producer thread can fetch the [128*R x 32] activation
-//     block of a K step with one bulk copy; the same thread streams the packed weight tiles of the K step;
-//   * nine expand warps turn packed codes into bf16 in shared memory in the canonical N-contiguous operand layout
-//     (the expansion of matmul_decode_stream.cu, here feeding the MMA's B operand);
-//   * one thread issues tcgen05.mma (M = 128 activation rows, N = 128 weight columns, K = 16 per instruction, 2*R per
-//     K block), accumulating in tensor memory; tcgen05.commit releases operand stages;
+//     tensor cores' canonical K-major operand layout, so that the producer can fetch the [128*R x 32] activation
+//     block of a K step with one bulk copy; the same warp streams the packed weight tiles of the K step;
+//   * the expand warps turn packed codes into bf16 in shared memory in the canonical N-contiguous operand layout
+//     (the expansion of matmul_decode_stream.cu, here feeding the MMA's B operand), in teams that take ring groups in turn;
+//   * one warp issues tcgen05.mma (M = 128 activation rows, N = 128*H weight columns, K = 16 per instruction, 2*R per
+//     K block), accumulating in tensor memory; tcgen05.commit releases operand stages. Producer and issuer run
+//     warp-uniform with one elected issuing lane;
 //   * eight warps read the accumulators back with tcgen05.ld and apply bias, activation and the bf16 / fp32 store.
 // Each expanded weight is reused for 128*R rows, so the expansion cost per flop falls with R; each weight tile is
-// expanded once per row block, the packed bytes coming from L2 after their first read.
+// expanded once per row block, the packed bytes coming from L2 after their first read. Row blocks vary fastest over the
+// grid, and column blocks that would not fill a whole wave of blocks go to a second launch with 128 x 128 blocks.
 // Every mbarrier wait is bounded; a wait that runs out raises a status word instead of hanging.
 #include <type_traits>
 
