@@ -346,9 +346,10 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
     // arrivals in the same order for every group.
     if (warp == kProducerWarp) {
         // ---------------- producer: packed weight tiles -> shared-memory ring, across segment borders ----------------
-        // One thread, one tensor-map copy per group. (Letting the whole warp take part costs the steady state ~5 %: warp 0
-        // shares its scheduler with the two MMA issuers, whose single-thread loops feel every instruction issued next to them.)
-        if (lane == 0) {
+        // One tensor-map copy per group. The whole warp walks the work list (addresses stay warp-uniform values), one elected
+        // lane issues.
+        {
+            const bool leader = elect_one();
             const uint64_t policy = l2_policy_evict_first();
             int gs = 0;
             uint32_t ph = 0;
@@ -359,17 +360,20 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
                 const TileRef tr = tile_ref(p, s.tile);
                 const void *map = &maps.m[tr.prob];
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
-                    if (!mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(empty_pk(gs), ph ^ 1, abort_flag, p.status, 1, lim))) { ok = false; break; }
                     // always a whole box of three K blocks: in a short last group the surplus lands in the group's unused
                     // stages (rows beyond the weight read as zeros), and the byte count the barrier expects stays the same
-                    mbar_arrive_expect_tx(full_pk(gs), kGroup * Pk<FMT>::kStageBytes);
-                    tma_load_3d(sbase + L::pk + gs * kGroup * Pk<FMT>::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
+                    if (leader) {
+                        mbar_arrive_expect_tx(full_pk(gs), kGroup * Pk<FMT>::kStageBytes);
+                        tma_load_3d(sbase + L::pk + gs * kGroup * Pk<FMT>::kStageBytes, map, 0, tr.nt * 4, s.kb0 + i0, full_pk(gs), policy);
+                    }
                     if (++gs == kPkG) { gs = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp2) {
-        // ---------------- MMA issuers (lane 0) + epilogue (whole warp) ----------------
+        // ---------------- MMA issuers (warp-uniform, one elected lane issues) + epilogue (whole warp) ----------------
+        const bool leader = elect_one();
         const int k16 = warp == kMmaWarp ? 0 : 1;
         constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/true, /*b_mn_major=*/false);
         const uint64_t a_desc0 = smem_desc_noswizzle(sbase + L::a, kA_LBO, kA_SBO);
@@ -386,23 +390,23 @@ __global__ void __launch_bounds__(kThreadsDecode, 1) matmul_decode_stream_kernel
         it.start(p, block);
         Seg s;
         for (; it.next(p, block, s); ++seg_idx) {
-            if (lane == 0 && ok) {
+            if (ok) {
                 for (int i0 = 0; i0 < s.nit; i0 += kGroup) {
                     const int r = min(kGroup, s.nit - i0);
-                    if (!mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2, lim)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_ab(gt), ph, abort_flag, p.status, 2, lim))) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_lo = a_lo0 + (uint32_t)gt * ((kGroup * kAStageBytes) >> 4);
                     const uint32_t b_lo = b_lo0 + (uint32_t)gt * ((kGroup * L::kBStageBytes) >> 4);
 #pragma unroll
                     for (int j = 0; j < kGroup; ++j) {
-                        if (j < r)
+                        if (j < r && leader)
                             mma_bf16_ss(d_tmem, mk(a_lo + (uint32_t)((j * kAStageBytes) >> 4), a_hi),
                                         mk(b_lo + (uint32_t)((j * L::kBStageBytes) >> 4), b_hi), idesc, i0 > 0 || j > 0);
                     }
-                    mma_commit(empty_ab(gt));
+                    if (leader) mma_commit(empty_ab(gt));
                     if (++gt == kAbGroups) { gt = 0; ph ^= 1; }
                 }
-                if (ok) mma_commit(accum_bar);
+                if (ok && leader) mma_commit(accum_bar);
             }
             __syncwarp();
             ok = stream_epilogue<FMT, NB>(p, ectx, s, seg_idx, ok);
