@@ -175,8 +175,8 @@ int32_t ttb_unpack_bfp(const void *src_dev, int32_t fmt, void *dst_dev, int32_t 
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags);
 /* Which kernels ttb_matmul uses for a shape (no GPU needed): out[0] = launches (0: the shape-generic CUDA-core kernel; 1 or
  * 2 tensor-core launches over consecutive row ranges), then per launch its row count and 1 for the prefill kernel, 0 for
- * a decode kernel. Decode kernels take up to 256 rows (any N that is a multiple of 32 when the row count is an odd
- * multiple of 32, else multiples of 128); the prefill kernel multiples of 128 rows from 512 up; other row counts are
+ * a decode kernel. Decode kernels take up to 256 rows, in blocks of one or two tile rows (any N that is a multiple of 32 when the
+ * row count is an odd multiple of 32, else multiples of 128); the prefill kernel multiples of 128 rows from 512 up; other row counts are
  * served as two ranges. */
 int32_t ttb_matmul_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags, int64_t *out, int32_t out_len);
 int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,

@@ -507,3 +507,28 @@ def test_row_counts_between_the_kernels_run_as_two_ranges(ttb, orc, M, kinds):
         y = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, act=cabi.ACT_RELU, flags=flags, out_fp32=True)
         y = y if flags else ttb.untilize(y, 1, M, N)
         check(y.reshape(M, N), torch.relu(x.float().cuda() @ w_ref.cuda()))
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 1024, 37888), (128, 2048, 18944), (256, 1024, 9472)])
+def test_many_overlapped_launches_with_two_tile_rows_per_block(ttb, orc, M, K, N):
+    """Row counts divisible by 64 run with two tile rows per block; here with several whole-tile rounds per block and dozens of
+    launches back to back, each allowed to start while its predecessor drains (the arrangement in which a ring whose
+    length was not a multiple of the number of expand teams once lost a barrier phase): no wait runs out, every launch
+    gives the first one's bytes, and the result matches the reference."""
+    import torch
+    assert _plan(ttb, cabi.BFLOAT8_B, M, K, N)[:3] == [1, M, 0]
+    w_dev, w_ref = make_big_case(ttb, orc, 31, K, N, cabi.BFLOAT8_B)
+    x = vectors.randn(32, (M, K), 1.0).bfloat16()
+    a = ttb.tilize(x.cuda(), 1, M, K)
+    nbytes = ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N, 0)
+    ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    outs = [torch.empty(M * N, dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    flags = cabi.MM_WORKSPACE_ZEROED | cabi.MM_WEIGHTS_RESIDENT | cabi.MM_DETERMINISTIC
+    for rep in range(3):
+        for i in range(16):
+            ttb.check(ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), cabi.BFLOAT8_B, None, outs[i % 4].data_ptr(), cabi.BFLOAT16,
+                                          1, M, K, N, 0, flags, ws.data_ptr(), nbytes, None))
+        ttb.check(ttb.check_status(None))
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+    check(ttb.untilize(outs[0], 1, M, N).reshape(M, N), x.float().cuda() @ w_ref.cuda())

@@ -9,7 +9,7 @@ int32_t launch_matmul_generic(const void *a, const void *w, int w_dtype, const v
 int32_t launch_bmm_generic(const void *a, const void *w, int w_dtype, void *out, int out_dtype, int64_t batch, int64_t M, int64_t K,
                            int64_t N, cudaStream_t stream);
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N);
-int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N);
+int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N, bool smem_operand);
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
                              int64_t rows, int64_t K, int64_t N, int act, int flags, void *workspace,
                              int64_t workspace_bytes, bool counters_are_zero, bool compact, cudaStream_t stream,
@@ -98,7 +98,7 @@ int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, in
     const int n = plan_rows(w_dtype, rows, K, N, chunks);
     int64_t bytes = 0;
     for (int i = 0; i < n; ++i) {
-        const int64_t b = chunks[i].prefill ? prefill_workspace_bytes(chunks[i].rows, K) : decode_workspace_bytes(chunks[i].rows, K, N);
+        const int64_t b = chunks[i].prefill ? prefill_workspace_bytes(chunks[i].rows, K) : decode_workspace_bytes(chunks[i].rows, K, N, (flags & TTB_MM_DECODE_SMEM_OPERAND) != 0);
         bytes = b > bytes ? b : bytes;
     }
     return bytes;

@@ -21,7 +21,7 @@ static constexpr int64_t kCounterBytes = 65536;
 // partials / other scratch]. The compact layout (built-in scratch of the allocation-free entry point) has no middle part.
 static constexpr int64_t kAccumBytes = 16 << 20;
 
-int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream);
+int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int nb, int *sync, bool overlap, cudaStream_t stream);
 // The tail of the counter region belongs to the launch as a whole (matmul_decode_tmem.cu: blocks that have finished, tiles
 // each stage has stored); the per-tile counters stay below it.
 static constexpr int kSyncInts = 16;
@@ -43,7 +43,12 @@ int32_t status_word_address(int **out) {
 }
 
 // Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
-static int decode_rows_per_block(int64_t rows) { return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32; }
+// Rows per block. The tensor-memory kernel takes one or two tile rows (32 or 64 rows); the shared-memory-operand kernel (on
+// request) the largest of 128 / 64 / 32 that divides the row count.
+static int decode_rows_per_block(int64_t rows, bool smem_operand = false) {
+    if (smem_operand) return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32;
+    return rows % 64 == 0 ? 64 : 32;
+}
 
 // 128-column tiles of a weight of N columns. The last one may hold 32, 64 or 96 columns (one tile row per block only: its
 // missing packed tiles read as zeros and the epilogue stores no column beyond N).
@@ -89,10 +94,10 @@ static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a pi
 //  * whole tiles round by round, the tiles left after the last full round streamed evenly over all blocks - each block
 //    then has up to two shared segments, ~35 each for the exchange and the pipeline bubble around it.
 // Both pay ~25 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama / Mistral / Falcon shapes.
-static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N) {
+static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N, bool smem_operand = false) {
     const int kStreamBlocks = stream_blocks();
     StreamPlan sp;
-    sp.nb = decode_rows_per_block(rows);
+    sp.nb = decode_rows_per_block(rows, smem_operand);
     sp.rchunks = (int)(rows / sp.nb);
     sp.tiles_row = 0;
     for (int j = 0; j < nprob; ++j) sp.tiles_row += tiles128(N[j]);
@@ -165,8 +170,8 @@ static int64_t stream_partial_bytes(const StreamPlan &sp) { return (int64_t)sp.s
 // Gated pair: one fp32 tile per tile of either weight, where the first finisher of a pair leaves its values.
 static int64_t stream_gate_bytes(const StreamPlan &sp) { return (int64_t)sp.tiles_total * BN * sp.nb * 4; }
 
-int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const int64_t *N, bool compact, bool gated = false) {
-    const StreamPlan sp = stream_plan(rows, K, nprob, N);
+int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const int64_t *N, bool compact, bool gated = false, bool smem_operand = false) {
+    const StreamPlan sp = stream_plan(rows, K, nprob, N, smem_operand);
     if (gated) return kCounterBytes + kAccumBytes + stream_partial_bytes(sp) + stream_gate_bytes(sp);
     if (!sp.shared_tiles) return 0;
     return kCounterBytes + (compact ? 0 : kAccumBytes) + stream_partial_bytes(sp);
@@ -174,7 +179,7 @@ int64_t decode_workspace_bytes_multi(int64_t rows, int64_t K, int nprob, const i
 
 int64_t decode_workspace_bytes_compact(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes_multi(rows, K, 1, &N, true); }
 
-int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N) { return decode_workspace_bytes_multi(rows, K, 1, &N, false); }
+int64_t decode_workspace_bytes(int64_t rows, int64_t K, int64_t N, bool smem_operand) { return decode_workspace_bytes_multi(rows, K, 1, &N, false, false, smem_operand); }
 
 // Fills the launch arguments of one ttb_matmul_multi-shaped piece of work. `zero_bytes`: how much of the head of the
 // workspace must be zero before the launch (the caller clears it unless it is known to be).
@@ -196,9 +201,10 @@ static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_byt
     if (wait) {
         p.wait_arrived = wait->arrived; p.wait_expected = wait->expected;
     }
-    const int nb = decode_rows_per_block(rows);
+    const bool smem_operand = (flags & TTB_MM_DECODE_SMEM_OPERAND) != 0;
+    const int nb = decode_rows_per_block(rows, smem_operand);
     // streamed decomposition
-    const StreamPlan sp = stream_plan(rows, K, nprob, N);
+    const StreamPlan sp = stream_plan(rows, K, nprob, N, smem_operand);
     p.nprob = nprob;
     int t0 = 0;
     int64_t nsum = 0;
@@ -238,7 +244,7 @@ static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_byt
         p.launch_arrivals = (unsigned)(gather->ranks * (int)(N[0] / BN) * sp.rchunks);
     }
     if (sp.shared_tiles || gated) {
-        const int64_t need = decode_workspace_bytes_multi(rows, K, nprob, N, compact, gated);
+        const int64_t need = decode_workspace_bytes_multi(rows, K, nprob, N, compact, gated, smem_operand);
         if (!workspace || workspace_bytes < need)
             return fail(TTB_E_WORKSPACE, "ttb_matmul: this shape needs %lld bytes of workspace, got %lld", (long long)need,
                         (long long)workspace_bytes);
@@ -272,13 +278,12 @@ int32_t launch_matmul_decode_multi(const void *a, int nprob, const void *const *
         TTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)zero_bytes, stream));
         overlap = false;   // only kernels may separate a launch from the one it overlaps with
     }
-    // the weights of 32-row blocks reach the MMA through tensor memory; those of larger row blocks (and of any on request)
-    // through shared memory
+    // the weights reach the MMA through tensor memory (blocks of one or two tile rows), on request through shared memory
     for (int j = 0; j < nprob; ++j)
         if (N[j] % BN && (flags & TTB_MM_DECODE_SMEM_OPERAND))
             return fail(TTB_E_UNSUPPORTED, "ttb_matmul: the shared-memory-operand kernel needs column counts that are multiples of 128");
-    if (nb == 32 && !(flags & TTB_MM_DECODE_SMEM_OPERAND))
-        return launch_decode_tmem(&p, 1, w_dtype, p.counters ? p.counters + kSyncInt0 : nullptr, overlap, stream);
+    if (!(flags & TTB_MM_DECODE_SMEM_OPERAND))
+        return launch_decode_tmem(&p, 1, w_dtype, nb, p.counters ? p.counters + kSyncInt0 : nullptr, overlap, stream);
     return launch_decode_stream(p, w_dtype, nb, overlap, stream);
 }
 
@@ -332,7 +337,7 @@ int32_t launch_matmul_decode_sequence(const ttb_matmul_stage *st, int count, int
         if (zero_bytes > 0 && !zeroed) TTB_CUDA_TRY(cudaMemsetAsync(ws, 0, (size_t)zero_bytes, stream));
         ws += slice;
     }
-    return launch_decode_tmem(args, count, w_dtype, (int *)workspace, overlap, stream);
+    return launch_decode_tmem(args, count, w_dtype, 32, (int *)workspace, overlap, stream);
 }
 
 int32_t launch_matmul_decode(const void *a, const void *w, int w_dtype, const void *bias, void *out, int out_dtype,
@@ -418,7 +423,7 @@ extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, cons
 extern "C" int64_t ttb_matmul_peer_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N) {
     using namespace ttb;
     if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || !decode_supported(w_dtype, batch * M, K, N)) return 0;
-    return decode_workspace_bytes(batch * M, K, N);
+    return decode_workspace_bytes(batch * M, K, N, false);
 }
 
 extern "C" int32_t ttb_matmul_peer(const void *a, int32_t a_dtype, const void *w, int32_t w_dtype, const void *bias, void *out,

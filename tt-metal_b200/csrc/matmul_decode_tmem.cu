@@ -1,5 +1,5 @@
-// Streamed decode matmul for bfloat8_b / bfloat4_b weights and 32 activation rows per block, weight operand through
-// tensor memory, persistent form:
+// Streamed decode matmul for bfloat8_b / bfloat4_b weights and 32 or 64 activation rows per block (one or two tile rows,
+// template parameter NB), weight operand through tensor memory, persistent form:
 //   out_j[rows, N_j] = act(a[rows, K] x W_j[K, N_j] + bias_j)   for up to four weights W_j that share the activation,
 // optionally several such stages in one launch, the product of a gated pair, and the all-gather of the first result.
 //
@@ -56,19 +56,20 @@ constexpr int kEpiWarp0 = kExpandWarps;        // warps 12..15
 constexpr int kEpiThreads = 128;
 constexpr int kProducerWarp = kEpiWarp0 + 4, kMmaWarp = kProducerWarp + 1, kLoaderWarp = kProducerWarp + 3;   // two MMA issuers
 constexpr int kThreads = 32 * (kLoaderWarp + 1);
-constexpr int NB = 32;   // activation rows per block (MMA N): one tile row
+// (NB, a template parameter below: activation rows per block = the MMA's N, 32 or 64 - one or two tile rows)
 constexpr int kAColsPerStage = BK / 2;         // TMEM columns of one expanded stage (two bf16 per column)
 constexpr uint32_t kB_SBO = 256;               // activations: 32-byte rows, eight rows per swizzle atom
 
-template <int FMT>
+template <int FMT, int NB>
 struct Layout {
     static constexpr int kTile = FMT == TTB_BFLOAT8_B ? kBfp8TileBytes : kBfp4TileBytes;
     static constexpr int kStageBytes = 4 * kTile;                  // 4352 / 2304
     static constexpr int kRing = 6;                                // groups whose activations / expanded weights are in flight
     // Packed tiles in flight: the copies from HBM need ~100 KB per SM under way to keep the memory system busy, on top of
     // the groups that sit in shared memory while they are expanded, so this ring is deeper than the one above.
-    static constexpr int kWRing = FMT == TTB_BFLOAT8_B ? 9 : 15;
-    static constexpr int kBStageBytes = NB * BK * 2;
+    static constexpr int kWRing = FMT == TTB_BFLOAT8_B ? (NB == 32 ? 9 : 6) : (NB == 32 ? 15 : 12);
+    static constexpr int kBRowStage = 32 * BK * 2;                 // activations of one K block, one tile row (32 rows): 2 KiB
+    static constexpr int kBStageBytes = NB * BK * 2;               // ... of the block's NB rows (the tile rows lie one behind the other per group)
     static constexpr int pk = 0;
     static constexpr int b = pk + kWRing * kGroup * kStageBytes;   // (a multiple of 256: the swizzled operand needs it)
     static constexpr int stage = b + kRing * kGroup * kBStageBytes;   // [NB x 128] bf16 tiled slab for the gather epilogue
@@ -81,7 +82,10 @@ struct Layout {
     // alternate pairs of groups (six stages, twelve MMAs, one commit that frees the pair's ring slots), each into its own
     // accumulator, so that no ordering between the two is needed; the epilogue adds the accumulators.
     static constexpr int kAccs = 2;
-    static constexpr int kAccCols = 2 * kAccs * NB;                // two sets of kAccs accumulators
+    // Accumulator sets: two for one tile row per block (the epilogue of a segment runs while the next segment's MMAs fill the
+    // other set); with two tile rows tensor memory holds one set next to the ring of expanded weights.
+    static constexpr int kSets = NB == 32 ? 2 : 1;
+    static constexpr int kAccCols = kSets * kAccs * NB;
     static constexpr int kACol0 = kAccCols;                        // the A ring follows them
     static constexpr int kTmemColsUsed = kAccCols + kRing * kGroup * kAColsPerStage;
     static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;
@@ -90,6 +94,11 @@ struct Layout {
     // The teams wait on the ring barriers with different phase parities, which is only right while a waiter is at most
     // one phase behind, i.e. while the ring has at least as many groups as there are teams.
     static_assert(kTeams <= kRing && kRing % 2 == 0 && kTeams <= kWRing, "ring shorter than the number of teams");
+    // ... and only while every team meets every phase of the barriers it waits on: a team takes every kTeams-th group, so
+    // the rings' lengths must be multiples of kTeams (with a ring of four and three teams, a team came back to a pair of
+    // slots two phases later; when one MMA issuer lagged behind the other, its parity wait passed on the stale phase and
+    // the team overwrote expanded weights that had not been multiplied yet).
+    static_assert(kRing % kTeams == 0 && kWRing % kTeams == 0, "every team must see every phase of a ring slot");
 };
 
 struct Seg {
@@ -380,17 +389,17 @@ constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks e
 
 // Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
 // that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
-template <int FMT>
+template <int FMT, int NB>
 __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, const Seg s, const int seg_idx, const int g0, bool ok, int *done_counter) {
-    using L = Layout<FMT>;
+    using L = Layout<FMT, NB>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tid = threadIdx.x - 32 * kEpiWarp0;
     const int quad = warp & 3;
-    const int buf = seg_idx & 1;
+    const int buf = seg_idx % L::kSets;
     const uint32_t acc_full = c.acc_full0 + 8u * buf, acc_empty = c.acc_empty0 + 8u * buf;
     // one thread waits for the accumulator; the other 127 sleep in a hardware barrier instead of polling
     volatile int *const ready = c.last_flag + 1 + buf;
-    if (tid == 0) *ready = (ok && mbar_wait(acc_full, (uint32_t)((seg_idx >> 1) & 1), c.abort_flag, p.status, 15, c.lim)) ? 1 : 0;
+    if (tid == 0) *ready = (ok && mbar_wait(acc_full, (uint32_t)((seg_idx / L::kSets) & 1), c.abort_flag, p.status, 15, c.lim)) ? 1 : 0;
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     const bool eok = *ready != 0;
     if (tid == 0) { TL(5, seg_idx * 8); }
@@ -595,9 +604,9 @@ __device__ __forceinline__ bool epilogue(const DecodeArgs &p, const EpiCtx c, co
 #undef TTB_COL_OK
 }
 
-template <int FMT, int S>
+template <int FMT, int S, int NB>
 __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const __grid_constant__ Sequence<S> q) {
-    using L = Layout<FMT>;
+    using L = Layout<FMT, NB>;
     constexpr int kRing = L::kRing;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -736,11 +745,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                     if (leader) {
                         TL(4, tlg);
                         mbar_arrive_expect_tx(full_b(gs), kGroup * L::kBStageBytes);
-                        const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes;
-                        if (p.a_row_major)
-                            tma_load_3d_plain(dst, amap, 0, rchunk * NB, (s.kb0 + i0) * 2, full_b(gs));
-                        else
-                            tma_load_5d(dst, amap, 0, 0, 0, 0, rchunk * p.Kt + s.kb0 + i0, full_b(gs));
+                        // one copy per tile row of the block: [tile row][K block][16-column half][32 rows][16 values]
+#pragma unroll
+                        for (int t = 0; t < NB / 32; ++t) {
+                            const uint32_t dst = sbase + L::b + gs * kGroup * L::kBStageBytes + t * kGroup * L::kBRowStage;
+                            if (p.a_row_major)
+                                tma_load_3d_plain(dst, amap, 0, rchunk * NB + t * 32, (s.kb0 + i0) * 2, full_b(gs));
+                            else
+                                tma_load_5d(dst, amap, 0, 0, 0, 0, (rchunk * (NB / 32) + t) * p.Kt + s.kb0 + i0, full_b(gs));
+                        }
                     }
                     ++tlg;
                     if (++gs == kRing) { gs = 0; ph ^= 1; }
@@ -756,7 +769,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         {
             const bool leader = elect_one();
             const int h = warp - kMmaWarp;
-            constexpr uint32_t idesc = instr_desc_bf16_f32(BN, NB, /*a_mn_major=*/false, /*b_mn_major=*/false);
+            constexpr uint32_t idesc = instr_desc_bf16_f32(BN, 32, /*a_mn_major=*/false, /*b_mn_major=*/false);   // one MMA per tile row of the block
             const uint64_t b_desc0 = smem_desc_sw32(sbase + L::b, kB_SBO);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             const uint32_t a_col0 = tmem_base + (uint32_t)L::kACol0;
@@ -767,9 +780,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
             it.start(q, block);
             Seg s;
             for (; ok && it.next(q, block, s); ++seg_idx) {
-                const int buf = seg_idx & 1;
+                const int buf = seg_idx % L::kSets;
                 // (every decision the warp takes is taken by all its lanes together)
-                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx >> 1) & 1) ^ 1), abort_flag, status, 16, lim))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8u * buf, (uint32_t)(((seg_idx / L::kSets) & 1) ^ 1), abort_flag, status, 16, lim))) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)((buf * L::kAccs + h) * NB);
                 bool fresh = true;   // this issuer's accumulator holds nothing of this segment yet
@@ -790,8 +803,13 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
                             if (j < r) {
 #endif
                                 if (leader) {
-                                    mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage), mk(b_lo + (uint32_t)((j * L::kBStageBytes) >> 4), b_hi), idesc, !(fresh && j == 0));
-                                    mma_bf16_ts(d_tmem, a_col + (uint32_t)(j * kAColsPerStage + 8), mk(b_lo + (uint32_t)((j * L::kBStageBytes + L::kBStageBytes / 2) >> 4), b_hi), idesc, true);
+                                    // (the activations of a tile row are a K-major operand of 32 rows; its results are 32 columns of the accumulator)
+#pragma unroll
+                                    for (int t = 0; t < NB / 32; ++t) {
+                                        const uint32_t bt = b_lo + (uint32_t)((t * kGroup * L::kBRowStage + j * L::kBRowStage) >> 4);
+                                        mma_bf16_ts(d_tmem + (uint32_t)(t * 32), a_col + (uint32_t)(j * kAColsPerStage), mk(bt, b_hi), idesc, !(fresh && j == 0));
+                                        mma_bf16_ts(d_tmem + (uint32_t)(t * 32), a_col + (uint32_t)(j * kAColsPerStage + 8), mk(bt + (uint32_t)((L::kBRowStage / 2) >> 4), b_hi), idesc, true);
+                                    }
                                 }
                             }
                         }
@@ -817,7 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
         Seg s;
         for (; it.next(q, block, s); ++seg_idx) {
             const DecodeArgs &p = q.st[S == 1 ? 0 : it.si];
-            ok = epilogue<FMT>(p, ectx, s, seg_idx, g0, ok, (S > 1 && p.count_done) ? q.sync + 1 + it.si : nullptr);
+            ok = epilogue<FMT, NB>(p, ectx, s, seg_idx, g0, ok, (S > 1 && p.count_done) ? q.sync + 1 + it.si : nullptr);
             g0 += (s.nit + kGroup - 1) / kGroup;
         }
     } else {
@@ -957,15 +975,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_decode_tmem_kernel(const _
     }
 }
 
-template <int FMT, int S>
+template <int FMT, int S, int NB>
 int32_t launch_seq(const Sequence<S> &q, bool overlap, cudaStream_t stream) {
-    constexpr int smem_bytes = Layout<FMT>::total + 1024;
+    constexpr int smem_bytes = Layout<FMT, NB>::total + 1024;
     static_assert(smem_bytes <= 232448, "shared memory budget");
     static bool configured[64] = {};
     int dev = 0;
     TTB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<FMT, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        TTB_CUDA_TRY(cudaFuncSetAttribute(matmul_decode_tmem_kernel<FMT, S, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -978,13 +996,13 @@ int32_t launch_seq(const Sequence<S> &q, bool overlap, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<FMT, S>, q));
+    TTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, matmul_decode_tmem_kernel<FMT, S, NB>, q));
     TTB_LAUNCH_CHECK("matmul_decode_tmem");
     return TTB_OK;
 }
 
 template <int S>
-int32_t build_and_launch(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream) {
+int32_t build_and_launch(const DecodeArgs *stages, int n, int fmt, int nb, int *sync, bool overlap, cudaStream_t stream) {
     static Sequence<S> q;   // (large: kept out of the stack; one host thread per process drives the library)
     q.n = n;
     q.sync = sync;
@@ -993,10 +1011,16 @@ int32_t build_and_launch(const DecodeArgs *stages, int n, int fmt, int *sync, bo
         q.st[s] = stages[s];
         if (stages[s].sk_grid > q.grid) q.grid = stages[s].sk_grid;
         if (int32_t rc = make_weight_maps(stages[s], fmt, q.maps[s], kGroup)) return rc;
-        if (int32_t rc = make_act_map(stages[s], (int64_t)(stages[s].sk_tiles / stages[s].tstart[stages[s].nprob]) * 32, q.amap[s], kGroup)) return rc;
+        if (int32_t rc = make_act_map(stages[s], (int64_t)(stages[s].sk_tiles / stages[s].tstart[stages[s].nprob]) * nb, q.amap[s], kGroup)) return rc;
     }
-    if (fmt == TTB_BFLOAT8_B) return launch_seq<TTB_BFLOAT8_B, S>(q, overlap, stream);
-    return launch_seq<TTB_BFLOAT4_B, S>(q, overlap, stream);
+    if constexpr (S == 1) {
+        if (nb == 64) {
+            if (fmt == TTB_BFLOAT8_B) return launch_seq<TTB_BFLOAT8_B, S, 64>(q, overlap, stream);
+            return launch_seq<TTB_BFLOAT4_B, S, 64>(q, overlap, stream);
+        }
+    }
+    if (fmt == TTB_BFLOAT8_B) return launch_seq<TTB_BFLOAT8_B, S, 32>(q, overlap, stream);
+    return launch_seq<TTB_BFLOAT4_B, S, 32>(q, overlap, stream);
 }
 
 }  // namespace
@@ -1006,14 +1030,17 @@ extern "C" int32_t ttb_debug_timeline(void *host) {
     TTB_CUDA_TRY(cudaMemcpyFromSymbol(host, g_tl, sizeof(g_tl)));
     return TTB_OK;
 }
+
 #endif
 
-// `stages`: what launch_matmul_decode_multi prepared for each stage (32-row blocks, one weight format for the launch);
+// `stages`: what launch_matmul_decode_multi prepared for each stage (blocks of `nb` rows, one weight format for the launch);
 // `sync`: the launch's bookkeeping counters in the zeroed head of the workspace, or null for a single stage without scratch.
-int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int *sync, bool overlap, cudaStream_t stream) {
+int32_t launch_decode_tmem(const DecodeArgs *stages, int n, int fmt, int nb, int *sync, bool overlap, cudaStream_t stream) {
     if (n < 1 || n > kMaxSequenceStages) return fail(TTB_E_INVALID, "a launch holds 1..%d stages", kMaxSequenceStages);
-    if (n == 1) return build_and_launch<1>(stages, n, fmt, sync, overlap, stream);
-    return build_and_launch<kMaxSequenceStages>(stages, n, fmt, sync, overlap, stream);
+    if (nb != 32 && nb != 64) return fail(TTB_E_INVALID, "the tensor-memory decode kernel takes blocks of 32 or 64 rows");
+    if (n == 1) return build_and_launch<1>(stages, n, fmt, nb, sync, overlap, stream);
+    if (nb != 32) return fail(TTB_E_UNSUPPORTED, "several stages in one launch need one tile row per block");
+    return build_and_launch<kMaxSequenceStages>(stages, n, fmt, nb, sync, overlap, stream);
 }
 
 }  // namespace ttb
