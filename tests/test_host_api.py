@@ -224,3 +224,28 @@ def test_decode_plan_covers_every_k_block_exactly_once():
     out = (ctypes.c_int32 * 10)()
     assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 64, 64, 1, bad, out, 10) == -3   # two tile rows per block: whole column tiles only
     assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == 0
+
+
+def test_matmul_plan_names_the_kernels_without_a_gpu():
+    """ttb_matmul_plan: which tensor-core kernels a shape gets - decode up to 256 rows (any N % 32 == 0 for odd multiples of 32
+    rows), prefill for multiples of 128 from 512, two row ranges in between and for ragged counts, else the CUDA-core kernel."""
+    import ctypes
+    import cabi
+    lib = cabi.load()
+
+    def plan(M, K, N, w_dtype=cabi.BFLOAT8_B, flags=0):
+        out = (ctypes.c_int64 * 5)()
+        assert lib.cdll.ttb_matmul_plan(w_dtype, 1, M, K, N, flags, out, 5) == 0
+        return list(out)
+
+    assert plan(32, 4544, 18176) == [1, 32, 0, 0, 0]
+    assert plan(32, 4544, 4672) == [1, 32, 0, 0, 0]           # last column tile of 64 columns
+    assert plan(64, 4544, 4672)[0] == 0                        # two tile rows per block: whole column tiles only
+    assert plan(256, 4096, 14336) == [1, 256, 0, 0, 0]
+    assert plan(2048, 8192, 28672) == [1, 2048, 1, 0, 0]
+    assert plan(320, 1024, 512) == [2, 256, 0, 64, 0]
+    assert plan(608, 1024, 512) == [2, 512, 1, 96, 0]
+    assert plan(384, 1024, 512) == [2, 256, 0, 128, 0]
+    assert plan(32, 1024, 512, cabi.BFLOAT16)[0] == 0          # bf16 weights: the shape-generic kernel
+    assert plan(32, 4544, 18176, flags=cabi.MM_FORCE_GENERIC)[0] == 0
+    assert lib.cdll.ttb_matmul_plan(cabi.BFLOAT8_B, 1, 32, 64, 128, 0, None, 5) == -1
