@@ -316,7 +316,7 @@ def test_overlapped_launches_keep_their_dependencies(ttb, orc, tmem, M):
     the previous launch's output (and all share one workspace) must give exactly the results of the same chain launched
     without overlap; MM_DETERMINISTIC makes both chains bit-reproducible."""
     import torch
-    K = N = 2048
+    K = N = 4096      # (a shape whose K range is shared out among blocks under every plan: the launches share scratch)
     depth = 6
     x = vectors.randn(77, (M, K), 1.0).bfloat16()
     ws_list = []
@@ -324,9 +324,9 @@ def test_overlapped_launches_keep_their_dependencies(ttb, orc, tmem, M):
         _, w_dev, _ = make_case(ttb, orc, 80 + i, M, K, N, cabi.BFLOAT8_B, w_std=0.02)
         ws_list.append(w_dev)
     torch.cuda.synchronize()
-    nbytes = ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N, cabi.MM_DETERMINISTIC)
-    assert nbytes > 0
-    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    nbytes = ttb.matmul_workspace_bytes(cabi.BFLOAT8_B, 1, M, K, N, cabi.MM_DETERMINISTIC | tmem)
+    assert nbytes > 0 or (M == 128 and not tmem)      # (two tile rows per block: this shape needs no sharing of K)
+    ws = torch.zeros(max(nbytes, 65536), dtype=torch.uint8, device="cuda")
 
     def chain(extra):
         cur = ttb.tilize(x.cuda(), 1, M, K)

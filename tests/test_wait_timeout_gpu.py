@@ -48,7 +48,7 @@ def test_negative_limit_is_refused(ttb):
 
 
 @pytest.mark.parametrize("w_dtype", [cabi.BFLOAT8_B, cabi.BFLOAT4_B])
-@pytest.mark.parametrize("M,K,N", [(32, 2048, 512), (64, 4096, 256), (32, 256, 18176)])
+@pytest.mark.parametrize("M,K,N", [(32, 4096, 512), (64, 4096, 256), (32, 256, 18176)])
 def test_matmul_waiting_for_peers_gives_up_and_the_next_one_is_right(ttb, orc, short_waits, w_dtype, M, K, N):
     """A decode matmul whose activations "come from other GPUs" that never deliver: every role of every block leaves through
     the kernel's teardown, the status says so, and after clearing the workspace head (the header's rule after a timeout)
@@ -84,8 +84,8 @@ def test_host_layer_raises_on_a_timeout_and_clears_its_scratch(ttb, short_waits)
     import ttnn
     device = ttnn.open_device(device_id=0)
     torch.manual_seed(3)
-    x = torch.randn(1, 1, 32, 2048).bfloat16()
-    w = torch.randn(2048, 512) * 0.03
+    x = torch.randn(1, 1, 32, 4096).bfloat16()
+    w = torch.randn(4096, 512) * 0.03
     tx = ttnn.from_torch(x, layout=ttnn.TILE_LAYOUT, device=device)
     tw = ttnn.from_torch(w, dtype=ttnn.bfloat8_b, layout=ttnn.TILE_LAYOUT, device=device)
     want = ttnn.to_torch(ttnn.linear(tx, tw)).float()          # (split over K: uses the device's scratch)
@@ -95,4 +95,5 @@ def test_host_layer_raises_on_a_timeout_and_clears_its_scratch(ttb, short_waits)
         ttnn.synchronize_device(device)
     ttnn.synchronize_device(device)                              # reported once
     got = ttnn.to_torch(ttnn.linear(tx, tw)).float()
-    assert torch.equal(got, want)
+    # (sums over K may be added in another order from launch to launch: equal to the last bf16 digit, not to the bit)
+    assert torch.allclose(got, want, rtol=2 ** -6, atol=1e-3 * float(want.abs().max()))

@@ -33,7 +33,7 @@ def _static(ttb, a, w, w_dtype, M, K, N, out_fp32=True):
 
 @pytest.mark.parametrize("M,K,N,w_dtype", [(32, 4096, 1024, cabi.BFLOAT8_B),     # K split over many blocks: uses the scratch
                                            (32, 4096, 4096, cabi.BFLOAT8_B),
-                                           (64, 2048, 512, cabi.BFLOAT4_B),
+                                           (64, 4096, 512, cabi.BFLOAT4_B),
                                            (32, 256, 18176, cabi.BFLOAT8_B)])    # one block per tile: no scratch needed
 def test_static_scratch_variant_matches_regular_entry_point_twice_in_a_row(ttb, M, K, N, w_dtype):
     import torch
@@ -88,20 +88,26 @@ def test_static_scratch_variant_refuses_what_it_cannot_serve(ttb):
     rc = ttb.cdll.ttb_matmul_decode_static(a.data_ptr(), cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
                                            1, 512, 256, 128, 0, 0, None)
     assert rc == -3 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
-    # Scratch: the compact layout of every decode shape fits the built-in array (at most one partial-sum slot per block and
-    # shared tile, 32 KiB each), so the refusal for size (TTB_E_WORKSPACE) is a guard that no present shape reaches; the
-    # library's own figure says so for the largest ones, and one of them runs through the entry point.
-    for M2, K2, N2 in [(256, 16384, 7680), (256, 65536, 4096), (224, 32768, 16384), (32, 8192, 28672), (128, 28672, 8192)]:
-        need = ttb.matmul_decode_static_scratch_bytes(cabi.BFLOAT8_B, 1, M2, K2, N2)
-        assert 0 <= need <= (16 << 20) + 65536, (M2, K2, N2, need)
-    M2, K2, N2 = 256, 16384, 7680
+    # A reduction that needs more scratch than the built-in array is refused before anything is launched. The library's own
+    # figure is checked first, and the operands are full-sized for the shape, so that a planner change can neither turn
+    # this into a launch that the test did not expect nor into one that leaves its buffers.
+    M2, K2, N2 = 256, 65536, 4096
+    assert ttb.matmul_decode_static_scratch_bytes(cabi.BFLOAT8_B, 1, M2, K2, N2) > (16 << 20) + 65536
     a2, w2 = _operands(ttb, M2, K2, N2, cabi.BFLOAT8_B, 72)
     out2 = torch.empty(M2 * N2, dtype=torch.bfloat16, device="cuda")
-    ttb.check(ttb.cdll.ttb_matmul_decode_static(a2.data_ptr(), cabi.BFLOAT16, w2.data_ptr(), cabi.BFLOAT8_B, None, out2.data_ptr(), cabi.BFLOAT16,
-                                                1, M2, K2, N2, 0, 0, None))
+    rc = ttb.cdll.ttb_matmul_decode_static(a2.data_ptr(), cabi.BFLOAT16, w2.data_ptr(), cabi.BFLOAT8_B, None, out2.data_ptr(), cabi.BFLOAT16,
+                                           1, M2, K2, N2, 0, 0, None)
+    assert rc == -4 and b"ttb_matmul" in ttb.cdll.ttb_last_error()
+    # a large shape that fits runs through the entry point
+    M3, K3, N3 = 256, 16384, 7680
+    assert 0 < ttb.matmul_decode_static_scratch_bytes(cabi.BFLOAT8_B, 1, M3, K3, N3) <= (16 << 20) + 65536
+    a3, w3 = _operands(ttb, M3, K3, N3, cabi.BFLOAT8_B, 73)
+    out3 = torch.empty(M3 * N3, dtype=torch.bfloat16, device="cuda")
+    ttb.check(ttb.cdll.ttb_matmul_decode_static(a3.data_ptr(), cabi.BFLOAT16, w3.data_ptr(), cabi.BFLOAT8_B, None, out3.data_ptr(), cabi.BFLOAT16,
+                                                1, M3, K3, N3, 0, 0, None))
     ttb.check(ttb.check_status(None))
-    ref2 = ttb.matmul(a2, w2, cabi.BFLOAT8_B, 1, M2, K2, N2)
-    assert torch.allclose(out2.float(), ref2.float(), rtol=2 ** -6, atol=1e-3 * float(ref2.float().abs().max()))
+    ref3 = ttb.matmul(a3, w3, cabi.BFLOAT8_B, 1, M3, K3, N3)
+    assert torch.allclose(out3.float(), ref3.float(), rtol=2 ** -6, atol=1e-3 * float(ref3.float().abs().max()))
     rc = ttb.cdll.ttb_matmul_decode_static(None, cabi.BFLOAT16, w.data_ptr(), cabi.BFLOAT8_B, None, out.data_ptr(), cabi.BFLOAT16,
                                            1, 32, 256, 128, 0, 0, None)
     assert rc == -1

@@ -87,13 +87,16 @@ static int stream_blocks() {
 }
 static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a piece of a tile shorter than this
 
-// Picks the cheaper of two decompositions by a small cost model in units of one K-block's streaming time (~0.155 us):
-//  * pieces: every tile cut into s equal parts along K, taken round by round - cost rounds * (K-blocks per part + 6,
-//    + 13 + 4.5 s for the partial-sum exchange when s > 1: ~2 us until a block knows its ticket, ~0.7 us per partial
-//    the last arriver reads);
-//  * whole tiles round by round, the tiles left after the last full round streamed evenly over all blocks - each block
-//    then has up to two shared segments, ~35 each for the exchange and the pipeline bubble around it.
-// Both pay ~25 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama / Mistral / Falcon shapes.
+// Picks the cheaper of two decompositions by a small cost model in units of one K-block's streaming time (~0.083 us per
+// block of the tensor-memory kernel):
+//  * pieces: every tile cut into s equal parts along K, taken round by round - cost rounds * (K-blocks per part, rounded
+//    up to whole groups of four, + 6, + 20 when s > 1) + 45 once when s > 1 for the partial-sum exchange of the last round
+//    (~4-5 us from the last reduction to the finished tile, nearly independent of s);
+//  * whole tiles round by round, the tiles left after the last full round streamed evenly over all blocks (1.15 per
+//    K-block: all multiprocessors pull on HBM) - each block then has up to two shared segments, ~45 / ~80 for their
+//    exchanges and the pipeline bubbles around them.
+// Both pay ~50 once for filling and draining the pipeline. Calibrated on B200 timings of the Llama-70B shapes and their
+// 2-, 4- and 8-way column shards (sweeps over s and both forms per shape).
 static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N, bool smem_operand = false) {
     const int kStreamBlocks = stream_blocks();
     StreamPlan sp;
@@ -114,7 +117,7 @@ static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t 
         if ((nkb + kbps - 1) / kbps != s) continue;
         if (s > 1 && kbps < 8) break;
         const int rounds = (T * s + kStreamBlocks - 1) / kStreamBlocks;
-        const double cost = rounds * (kbps + 6.0 + (s > 1 ? 13.0 + 4.5 * s : 0.0));
+        const double cost = rounds * ((kbps + 3) / 4 * 4 + 6.0 + (s > 1 ? 20.0 : 0.0)) + (s > 1 ? 45.0 : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; }
     }
     // whole tiles + streamed remainder
@@ -122,7 +125,7 @@ static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t 
     double stream_cost = 1e30;
     if (rem > 0 && (long long)rem * sp.upt >= 2) {
         const double share = (double)rem * nkb / kStreamBlocks;
-        stream_cost = full * (nkb + 6.0) + share + (full > 0 ? 35.0 : 70.0);   // after whole tiles a block has one shared segment, else two
+        stream_cost = full * (nkb + 6.0) + 1.15 * share + (full > 0 ? 45.0 : 80.0);   // after whole tiles a block has one shared segment, else two
     }
     if (stream_cost < best_cost) {
         sp.pieces = 1; sp.kbps = nkb;

@@ -385,7 +385,7 @@ struct EpiCtx {
     long long lim;
 };
 
-constexpr int kPartialsUpTo = 4;   // tiles shared by at most this many blocks exchange plain partial tiles (fixed order)
+constexpr int kPartialsUpTo = 1;   // plain partial tiles (fixed order) only on request: measured ~2 us per launch slower than the reductions even for two sharers
 
 // Epilogue of segment `seg_idx`, run by warps 12..15 together. Always runs through the same barriers, also after a wait
 // that ran out (then it moves no data), so that the four warps never part ways at a named barrier.
