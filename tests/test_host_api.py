@@ -226,6 +226,42 @@ def test_decode_plan_covers_every_k_block_exactly_once():
     assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == 0
 
 
+def _check_plan(lib, fmt, M, K, Ns):
+    import ctypes
+    arr = (ctypes.c_int64 * len(Ns))(*Ns)
+    out = (ctypes.c_int32 * 10)()
+    assert lib.cdll.ttb_matmul_decode_plan(fmt, 1, M, K, len(Ns), arr, out, 10) == 0, (M, K, Ns)
+    plan = list(out)
+    nb, tiles, grid, pieces, kbps, waves, rem0, units, upt, slots = plan
+    nkb = K // 32
+    assert nb in (32, 64) and M % nb == 0 and tiles == sum((n + 127) // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148, (M, K, Ns, plan)
+    cover = _walk_plan(plan, nkb)
+    assert sorted(cover) == list(range(tiles)), (M, K, Ns, plan)
+    shared = 0
+    for tile, segs in cover.items():
+        segs.sort()
+        assert segs[0][0] == 0 and segs[-1][1] == nkb and all(a[1] == b[0] for a, b in zip(segs, segs[1:])), (M, K, Ns, plan, tile, segs)
+        assert all(s[1] > s[0] for s in segs), (M, K, Ns, plan, tile, segs)
+        shared += len(segs) if len(segs) > 1 else 0
+    assert shared <= slots or shared == 0, (M, K, Ns, plan, shared)
+
+
+def test_decode_plan_covers_every_k_block_for_seeded_random_shapes():
+    """The same property over a seeded sweep of shapes in both formats: 1 to 4 weights, 32 to 256 rows, K from one K block to
+    32768, column counts from one tile to 32768 (ragged last tiles where blocks of one tile row allow them)."""
+    import random
+    import cabi
+    lib = cabi.load()
+    rng = random.Random(20240229)
+    for _ in range(600):
+        M = 32 * rng.randint(1, 8)
+        K = 32 * rng.choice([1, 2, 3, 7, 8, 9, 33, 64, 100, 128, 142, 256, 257, 512, 896, 1024])
+        count = rng.randint(1, 4)
+        step = 32 if (M // 32) % 2 == 1 else 128
+        Ns = [step * rng.randint(1, rng.choice([4, 36, 256]) * 128 // step) for _ in range(count)]
+        _check_plan(lib, rng.choice([cabi.BFLOAT8_B, cabi.BFLOAT4_B]), M, K, Ns)
+
+
 def test_matmul_plan_names_the_kernels_without_a_gpu():
     """ttb_matmul_plan: which tensor-core kernels a shape gets - decode up to 256 rows (any N % 32 == 0 for odd multiples of 32
     rows), prefill for multiples of 128 from 512, two row ranges in between and for ragged counts, else the CUDA-core kernel."""
