@@ -173,11 +173,12 @@ int32_t ttb_unpack_bfp(const void *src_dev, int32_t fmt, void *dst_dev, int32_t 
  * per-output-tile arrival counters that must be zero when the kernel starts: ttb_matmul clears them with a
  * memset on `stream` unless TTB_MM_WORKSPACE_ZEROED is given. */
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags);
-/* Which kernels ttb_matmul uses for a shape (no GPU needed): out[0] = launches (0: the shape-generic CUDA-core kernel; 1 or
- * 2 tensor-core launches over consecutive row ranges), then per launch its row count and 1 for the prefill kernel, 0 for
- * a decode kernel. Decode kernels take up to 256 rows, in blocks of one or two tile rows (any N that is a multiple of 32 when the
- * row count is an odd multiple of 32, else multiples of 128); the prefill kernel multiples of 128 rows from 512 up; other row counts are
- * served as two ranges. */
+/* Which kernels ttb_matmul uses for a shape (no GPU needed): out[0] = launches (0: the shape-generic CUDA-core kernel;
+ * else tensor-core launches over consecutive row ranges), then per launch its row count and 1 for the prefill kernel, 0
+ * for a decode kernel - for as many launches as `out` has room for (out_len >= 5). Decode kernels take up to 256 rows and
+ * any N that is a multiple of 32 (blocks of two tile rows when the row count is a multiple of 64 and N a multiple of 128,
+ * else of one); the prefill kernel multiples of 128 rows from 512 up with N a multiple of 128; other row counts are served
+ * as two ranges, and large row counts with an N the prefill kernel does not take as up to 16 decode launches of 256 rows. */
 int32_t ttb_matmul_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags, int64_t *out, int32_t out_len);
 int32_t ttb_matmul(const void *a_dev, int32_t a_dtype, const void *w_dev, int32_t w_dtype, const void *bias_dev,
                    void *out_dev, int32_t out_dtype, int64_t batch, int64_t M, int64_t K, int64_t N,

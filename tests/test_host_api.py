@@ -220,10 +220,12 @@ def test_decode_plan_covers_every_k_block_exactly_once():
             assert all(s[1] > s[0] for s in segs)
             shared += len(segs) if len(segs) > 1 else 0
         assert shared <= slots or shared == 0, (M, K, Ns, plan, shared)
-    bad = (ctypes.c_int64 * 1)(96)
+    ragged = (ctypes.c_int64 * 1)(96)
     out = (ctypes.c_int32 * 10)()
-    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 64, 64, 1, bad, out, 10) == -3   # two tile rows per block: whole column tiles only
-    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, bad, out, 10) == 0
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 64, 64, 1, ragged, out, 10) == 0 and out[0] == 32   # a partial column tile: one tile row per block
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 32, 64, 1, ragged, out, 10) == 0 and out[0] == 32
+    whole = (ctypes.c_int64 * 1)(128)
+    assert lib.cdll.ttb_matmul_decode_plan(cabi.BFLOAT8_B, 1, 64, 64, 1, whole, out, 10) == 0 and out[0] == 64
 
 
 def _check_plan(lib, fmt, M, K, Ns):
@@ -234,7 +236,7 @@ def _check_plan(lib, fmt, M, K, Ns):
     plan = list(out)
     nb, tiles, grid, pieces, kbps, waves, rem0, units, upt, slots = plan
     nkb = K // 32
-    assert nb in (32, 64) and M % nb == 0 and tiles == sum((n + 127) // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148, (M, K, Ns, plan)
+    assert nb == (64 if M % 64 == 0 and all(n % 128 == 0 for n in Ns) else 32) and tiles == sum((n + 127) // 128 for n in Ns) * (M // nb) and 1 <= grid <= 148, (M, K, Ns, plan)
     cover = _walk_plan(plan, nkb)
     assert sorted(cover) == list(range(tiles)), (M, K, Ns, plan)
     shared = 0
@@ -248,7 +250,7 @@ def _check_plan(lib, fmt, M, K, Ns):
 
 def test_decode_plan_covers_every_k_block_for_seeded_random_shapes():
     """The same property over a seeded sweep of shapes in both formats: 1 to 4 weights, 32 to 256 rows, K from one K block to
-    32768, column counts from one tile to 32768 (ragged last tiles where blocks of one tile row allow them)."""
+    32768, column counts from one tile to 32768, with and without a partial last column tile."""
     import random
     import cabi
     lib = cabi.load()
@@ -257,14 +259,15 @@ def test_decode_plan_covers_every_k_block_for_seeded_random_shapes():
         M = 32 * rng.randint(1, 8)
         K = 32 * rng.choice([1, 2, 3, 7, 8, 9, 33, 64, 100, 128, 142, 256, 257, 512, 896, 1024])
         count = rng.randint(1, 4)
-        step = 32 if (M // 32) % 2 == 1 else 128
+        step = rng.choice([32, 128])
         Ns = [step * rng.randint(1, rng.choice([4, 36, 256]) * 128 // step) for _ in range(count)]
         _check_plan(lib, rng.choice([cabi.BFLOAT8_B, cabi.BFLOAT4_B]), M, K, Ns)
 
 
 def test_matmul_plan_names_the_kernels_without_a_gpu():
-    """ttb_matmul_plan: which tensor-core kernels a shape gets - decode up to 256 rows (any N % 32 == 0 for odd multiples of 32
-    rows), prefill for multiples of 128 from 512, two row ranges in between and for ragged counts, else the CUDA-core kernel."""
+    """ttb_matmul_plan: which tensor-core kernels a shape gets - decode up to 256 rows (any N % 32 == 0), prefill for multiples
+    of 128 from 512 (N % 128 == 0), two row ranges in between and for ragged counts, ranges of 256 rows on the decode kernel
+    where N has a partial last tile, else the CUDA-core kernel."""
     import ctypes
     import cabi
     lib = cabi.load()
@@ -276,12 +279,21 @@ def test_matmul_plan_names_the_kernels_without_a_gpu():
 
     assert plan(32, 4544, 18176) == [1, 32, 0, 0, 0]
     assert plan(32, 4544, 4672) == [1, 32, 0, 0, 0]           # last column tile of 64 columns
-    assert plan(64, 4544, 4672)[0] == 0                        # two tile rows per block: whole column tiles only
+    assert plan(64, 4544, 4672) == [1, 64, 0, 0, 0]           # ... also with several tile rows
     assert plan(256, 4096, 14336) == [1, 256, 0, 0, 0]
     assert plan(2048, 8192, 28672) == [1, 2048, 1, 0, 0]
     assert plan(320, 1024, 512) == [2, 256, 0, 64, 0]
     assert plan(608, 1024, 512) == [2, 512, 1, 96, 0]
     assert plan(384, 1024, 512) == [2, 256, 0, 128, 0]
+    assert plan(512, 4544, 4672) == [2, 256, 0, 256, 0]       # a partial last column tile: decode launches over row ranges
+    out = (ctypes.c_int64 * 33)()
+    assert lib.cdll.ttb_matmul_plan(cabi.BFLOAT8_B, 1, 2080, 4544, 4544, 0, out, 33) == 0
+    assert list(out)[:19] == [9] + [256, 0] * 8 + [32, 0] and not any(list(out)[19:])
+    for M in range(32, 4097, 32):                              # every row count up to 4096 stays on the tensor cores
+        for N in (512, 4672, 96):
+            assert lib.cdll.ttb_matmul_plan(cabi.BFLOAT8_B, 1, M, 1024, N, 0, out, 33) == 0
+            assert out[0] > 0 and sum(list(out)[1::2]) == M, (M, N, list(out))
+    assert plan(4128, 1024, 96)[0] == 0                        # more than 16 ranges: the shape-generic kernel
     assert plan(32, 1024, 512, cabi.BFLOAT16)[0] == 0          # bf16 weights: the shape-generic kernel
     assert plan(32, 4544, 18176, flags=cabi.MM_FORCE_GENERIC)[0] == 0
     assert lib.cdll.ttb_matmul_plan(cabi.BFLOAT8_B, 1, 32, 64, 128, 0, None, 5) == -1

@@ -393,8 +393,8 @@ def test_multi_arguments_are_validated(ttb):
     import torch
     buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     ptrs = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
-    ns = (ctypes.c_int64 * 2)(128, 96)                    # 96 is not a multiple of 128: with 64 rows not a decode shape
-    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 2, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 64, 64, ns, 0, 0,
+    ns = (ctypes.c_int64 * 2)(128, 96)
+    rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 2, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 288, 64, ns, 0, 0,   # 288 rows: not a decode shape
                                    buf.data_ptr(), 1 << 20, None, None, None)
     assert rc == -3
     rc = ttb.cdll.ttb_matmul_multi(buf.data_ptr(), cabi.BFLOAT16, 5, ptrs, cabi.BFLOAT8_B, None, ptrs, cabi.BFLOAT16, 1, 32, 64, ns, 0, 0,
@@ -462,6 +462,8 @@ def _plan(ttb, w_dtype, M, K, N, flags=0):
     (32, 18176, 4544),     # Falcon-7B 4h_to_h
     (96, 512, 160),        # 32 columns in the last tile, three tile rows
     (32, 256, 96),         # a single, partial column tile
+    (64, 4544, 4672),      # row counts divisible by 64 fall back to one tile row per block
+    (256, 512, 160),
 ])
 def test_last_column_tile_of_fewer_than_128_columns(ttb, orc, w_dtype, M, K, N):
     """N a multiple of 32 but not of 128 stays on the tensor-core decode kernel (one launch, decode kind): the missing packed
@@ -507,6 +509,31 @@ def test_row_counts_between_the_kernels_run_as_two_ranges(ttb, orc, M, kinds):
         y = ttb.matmul(a, w_dev, w_dtype, 1, M, K, N, act=cabi.ACT_RELU, flags=flags, out_fp32=True)
         y = y if flags else ttb.untilize(y, 1, M, N)
         check(y.reshape(M, N), torch.relu(x.float().cuda() @ w_ref.cuda()))
+
+
+@pytest.mark.parametrize("M,K,N,launches", [(512, 512, 416, 2), (1056, 1024, 4672, 5)])
+def test_large_row_counts_with_a_partial_column_tile_run_as_decode_ranges(ttb, orc, M, K, N, launches):
+    """What the prefill kernel does not take (N not a multiple of 128) runs as decode launches over ranges of 256 rows - not on
+    the CUDA-core kernel - with tiled and with row-major operands, and no byte behind the output is touched."""
+    import ctypes
+    import torch
+    w_dtype = cabi.BFLOAT8_B
+    out = (ctypes.c_int64 * 33)()
+    assert ttb.cdll.ttb_matmul_plan(w_dtype, 1, M, K, N, 0, out, 33) == 0
+    assert out[0] == launches and sum(list(out)[1::2]) == M and not any(list(out)[2::2])
+    x, w_dev, w_ref = make_case(ttb, orc, 23, M, K, N, w_dtype)
+    ref = torch.relu(x.float().cuda() @ w_ref.cuda())
+    for flags in (0, cabi.MM_A_ROW_MAJOR | cabi.MM_OUT_ROW_MAJOR):
+        a = x.cuda().reshape(-1) if flags else ttb.tilize(x.cuda(), 1, M, K)
+        buf = torch.full((M * N + 4096,), 7.0, dtype=torch.bfloat16, device="cuda")
+        nbytes = ttb.matmul_workspace_bytes(w_dtype, 1, M, K, N, flags)
+        ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        ttb.check(ttb.cdll.ttb_matmul(a.data_ptr(), cabi.BFLOAT16, w_dev.data_ptr(), w_dtype, None, buf.data_ptr(), cabi.BFLOAT16, 1, M, K, N,
+                                      cabi.ACT_RELU, flags | cabi.MM_WORKSPACE_ZEROED, ws.data_ptr(), nbytes, None))
+        ttb.check(ttb.check_status(None))
+        assert bool((buf[M * N:] == 7.0).all())
+        y = buf[: M * N] if flags else ttb.untilize(buf[: M * N].clone(), 1, M, N)
+        check(y.reshape(M, N), ref)
 
 
 @pytest.mark.parametrize("M,K,N", [(64, 1024, 37888), (128, 2048, 18944), (256, 1024, 9472)])

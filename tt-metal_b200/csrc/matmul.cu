@@ -54,14 +54,17 @@ int32_t validate(const void *a, int a_dtype, const void *w, int w_dtype, void *o
 }
 
 // Row ranges of one matmul and the tensor-core kernel that takes each: the decode kernels serve up to 256 rows, the prefill
-// kernel multiples of 128 from 512 up. Row counts in between run as two decode launches (256 rows + the rest); a ragged
-// count above 512 as the prefill kernel on the whole 128-row blocks plus a decode launch on the last 32 to 96 rows. (Rows are
+// kernel multiples of 128 from 512 up (column counts that are multiples of 128). Row counts in between run as two decode
+// launches (256 rows + the rest); a ragged count above 512 as the prefill kernel on the whole 128-row blocks plus a decode
+// launch on the last 32 to 96 rows; and what the prefill kernel cannot take at all (a last column tile of fewer than 128
+// columns) as decode launches over ranges of 256 rows, up to kMaxRowChunks of them. (Rows are
 // contiguous in both layouts - a tile row of a tiled tensor is 32 whole rows - so a range is just an offset.)
 struct RowChunk {
     int64_t row0, rows;
     bool prefill;
 };
-int plan_rows(int w_dtype, int64_t rows, int64_t K, int64_t N, RowChunk (&out)[2]) {
+constexpr int kMaxRowChunks = 16;
+int plan_rows(int w_dtype, int64_t rows, int64_t K, int64_t N, RowChunk (&out)[kMaxRowChunks]) {
     if (decode_supported(w_dtype, rows, K, N)) {
         out[0] = {0, rows, false};
         return 1;
@@ -81,6 +84,12 @@ int plan_rows(int w_dtype, int64_t rows, int64_t K, int64_t N, RowChunk (&out)[2
         out[1] = {whole, rows - whole, false};
         return 2;
     }
+    const int64_t last = rows % 256;
+    if (rows >= 512 && rows <= 256 * kMaxRowChunks && decode_supported(w_dtype, 256, K, N) && (last == 0 || decode_supported(w_dtype, last, K, N))) {
+        int n = 0;
+        for (int64_t r0 = 0; r0 < rows; r0 += 256) out[n++] = {r0, rows - r0 < 256 ? rows - r0 : 256, false};
+        return n;
+    }
     return 0;
 }
 
@@ -94,7 +103,7 @@ extern "C" {
 int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags) {
     const int64_t rows = batch * M;
     if (flags & TTB_MM_FORCE_GENERIC) return 0;
-    RowChunk chunks[2];
+    RowChunk chunks[kMaxRowChunks];
     const int n = plan_rows(w_dtype, rows, K, N, chunks);
     int64_t bytes = 0;
     for (int i = 0; i < n; ++i) {
@@ -105,13 +114,13 @@ int64_t ttb_matmul_workspace_bytes(int32_t w_dtype, int64_t batch, int64_t M, in
 }
 
 /* Which kernels ttb_matmul would use: out[0] = launches (0: the shape-generic CUDA-core kernel), then per launch its rows
- * and 1 for the prefill kernel, 0 for a decode kernel. */
+ * and 1 for the prefill kernel, 0 for a decode kernel - for as many launches as `out` has room for (at least two). */
 int32_t ttb_matmul_plan(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N, int32_t flags, int64_t *out, int32_t out_len) {
     if (!out || out_len < 5) return fail(TTB_E_INVALID, "ttb_matmul_plan: needs room for 5 values");
-    RowChunk chunks[2];
+    RowChunk chunks[kMaxRowChunks];
     const int n = (flags & TTB_MM_FORCE_GENERIC) ? 0 : plan_rows(w_dtype, batch * M, K, N, chunks);
     out[0] = n;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; 2 + 2 * i < out_len && i < kMaxRowChunks; ++i) {
         out[1 + 2 * i] = i < n ? chunks[i].rows : 0;
         out[2 + 2 * i] = i < n && chunks[i].prefill ? 1 : 0;
     }
@@ -124,7 +133,7 @@ int32_t ttb_matmul(const void *a, int32_t a_dtype, const void *w, int32_t w_dtyp
     if (int32_t rc = validate(a, a_dtype, w, w_dtype, out, out_dtype, batch, M, K, N, act)) return rc;
     const int64_t rows = batch * M;  // tiled [batch, M, K] with M % 32 == 0 is the same buffer as tiled [batch*M, K]
     auto s = (cudaStream_t)stream;
-    RowChunk chunks[2];
+    RowChunk chunks[kMaxRowChunks];
     const int n = (flags & TTB_MM_FORCE_GENERIC) ? 0 : plan_rows(w_dtype, rows, K, N, chunks);
     if (n == 0) return launch_matmul_generic(a, w, w_dtype, bias, out, out_dtype, rows, K, N, act, flags, s);
     const int64_t out_elem = out_dtype == TTB_FLOAT32 ? 4 : 2;

@@ -42,22 +42,28 @@ int32_t status_word_address(int **out) {
     return TTB_OK;
 }
 
-// Rows handled per block: the largest of 128 / 64 / 32 that divides `rows`.
 // Rows per block. The tensor-memory kernel takes one or two tile rows (32 or 64 rows); the shared-memory-operand kernel (on
-// request) the largest of 128 / 64 / 32 that divides the row count.
-static int decode_rows_per_block(int64_t rows, bool smem_operand = false) {
+// request) the largest of 128 / 64 / 32 that divides the row count. A weight whose last column tile holds fewer than 128
+// columns (`ragged`) is served by blocks of one tile row only.
+static int decode_rows_per_block(int64_t rows, bool smem_operand, bool ragged) {
+    if (ragged) return 32;
     if (smem_operand) return rows % 128 == 0 ? 128 : rows % 64 == 0 ? 64 : 32;
     return rows % 64 == 0 ? 64 : 32;
 }
 
-// 128-column tiles of a weight of N columns. The last one may hold 32, 64 or 96 columns (one tile row per block only: its
-// missing packed tiles read as zeros and the epilogue stores no column beyond N).
+// 128-column tiles of a weight of N columns. The last one may hold 32, 64 or 96 columns (its missing packed tiles read as
+// zeros and the epilogue stores no column beyond N).
 static int tiles128(int64_t N) { return (int)((N + BN - 1) / BN); }
-static bool columns_ok(int64_t rows, int64_t N) { return N > 0 && N % 32 == 0 && (N % BN == 0 || decode_rows_per_block(rows) == 32); }
+static bool columns_ok(int64_t N) { return N > 0 && N % 32 == 0; }
+static bool any_ragged(int nprob, const int64_t *N) {
+    for (int j = 0; j < nprob; ++j)
+        if (N[j] % BN) return true;
+    return false;
+}
 
 bool decode_supported(int w_dtype, int64_t rows, int64_t K, int64_t N) {
     return (w_dtype == TTB_BFLOAT8_B || w_dtype == TTB_BFLOAT4_B) && rows > 0 && rows <= 256 && rows % 32 == 0 &&
-           K % BK == 0 && columns_ok(rows, N) && tiles128(N) * (rows / 32) <= kSyncInt0;
+           K % BK == 0 && columns_ok(N) && tiles128(N) * (rows / 32) <= kSyncInt0;
 }
 
 // ---- streamed decomposition (matmul_decode_stream.cu) ----------------------------------------------------------------
@@ -100,7 +106,7 @@ static constexpr int kStreamGran = 8;   // K-blocks per unit: no block gets a pi
 static StreamPlan stream_plan(int64_t rows, int64_t K, int nprob, const int64_t *N, bool smem_operand = false) {
     const int kStreamBlocks = stream_blocks();
     StreamPlan sp;
-    sp.nb = decode_rows_per_block(rows, smem_operand);
+    sp.nb = decode_rows_per_block(rows, smem_operand, any_ragged(nprob, N));
     sp.rchunks = (int)(rows / sp.nb);
     sp.tiles_row = 0;
     for (int j = 0; j < nprob; ++j) sp.tiles_row += tiles128(N[j]);
@@ -156,7 +162,7 @@ bool decode_supported_multi(int w_dtype, int64_t rows, int64_t K, int nprob, con
     if (nprob < 1 || nprob > TTB_MAX_GROUP) return false;
     int64_t tiles = 0;
     for (int j = 0; j < nprob; ++j) {
-        if (!columns_ok(rows, N[j])) return false;
+        if (!columns_ok(N[j])) return false;
         tiles += tiles128(N[j]);
     }
     return tiles * (rows / 32) <= kSyncInt0;
@@ -205,7 +211,7 @@ static int32_t prepare_decode_args(DecodeArgs &p, int &nb_out, int64_t &zero_byt
         p.wait_arrived = wait->arrived; p.wait_expected = wait->expected;
     }
     const bool smem_operand = (flags & TTB_MM_DECODE_SMEM_OPERAND) != 0;
-    const int nb = decode_rows_per_block(rows, smem_operand);
+    const int nb = decode_rows_per_block(rows, smem_operand, any_ragged(nprob, N));
     // streamed decomposition
     const StreamPlan sp = stream_plan(rows, K, nprob, N, smem_operand);
     p.nprob = nprob;
@@ -305,7 +311,7 @@ int64_t decode_sequence_workspace_bytes(int64_t rows, int count, const ttb_matmu
 int32_t launch_matmul_decode_sequence(const ttb_matmul_stage *st, int count, int w_dtype, int64_t rows, int flags, void *workspace,
                                       int64_t workspace_bytes, cudaStream_t stream) {
     if (count < 1 || count > kMaxSequenceStages) return fail(TTB_E_INVALID, "ttb_matmul_sequence: 1..%d stages, got %d", kMaxSequenceStages, count);
-    if (decode_rows_per_block(rows) != 32)
+    if (rows % 64 == 0)
         return fail(TTB_E_UNSUPPORTED, "ttb_matmul_sequence: serves row counts that are odd multiples of 32 (32, 96, 160, 224)");
     const int64_t need = decode_sequence_workspace_bytes(rows, count, st);
     if (!workspace || workspace_bytes < need)
@@ -373,7 +379,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[TTB_STATIC_SCRAT
 
 extern "C" int64_t ttb_matmul_decode_static_scratch_bytes(int32_t w_dtype, int64_t batch, int64_t M, int64_t K, int64_t N) {
     using namespace ttb;
-    if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || !decode_supported(w_dtype, batch * M, K, N)) return -1;
+    if (batch <= 0 || M <= 0 || K <= 0 || N <= 0 || N % BN || !decode_supported(w_dtype, batch * M, K, N)) return -1;
     return decode_workspace_bytes_compact(batch * M, K, N);
 }
 
@@ -391,7 +397,7 @@ extern "C" int32_t ttb_matmul_decode_static(const void *a, int32_t a_dtype, cons
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(TTB_E_INVALID, "ttb_matmul_decode_static: tensors must be 16-byte aligned");
     const int64_t rows = batch * M;
-    if (!decode_supported(w_dtype, rows, K, N))
+    if (N % BN || !decode_supported(w_dtype, rows, K, N))
         return fail(TTB_E_UNSUPPORTED,
                     "ttb_matmul_decode_static: only the decode shapes are served without allocation (bfloat8_b / bfloat4_b weights, "
                     "at most 256 rows, N a multiple of 128); use ttb_matmul for [%lld x %lld x %lld]",
