@@ -86,7 +86,7 @@ def _fused_linear(input_tensor, weights, biases, activation, gather_first, ring_
 def linear_multi(input_tensor, weights, *, biases=None, activation=None, all_gather_first=False):
     """[ttnn.linear(x, w, bias=b, activation=activation) for w, b in zip(weights, biases)] as ONE launch: the weights share
     the activation (q / k / v projections; w1 / w3 of a gated MLP) and stay separate tensors. Decode shapes (at most 256
-    rows, every N a multiple of 128, block-float weights). Results equal those of the separate calls. With
+    rows, block-float weights; a gathered first result needs an N that is a multiple of 128). Results equal those of the separate calls. With
     all_gather_first the first result is gathered along its last dimension over the mesh by the kernel's own epilogue
     (see linear_all_gather)."""
     return _fused_linear(input_tensor, weights, biases, activation, all_gather_first)
